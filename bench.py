@@ -1,0 +1,351 @@
+#!/usr/bin/env python
+"""Decode benchmark: one layer of single-query GQA attention over the paged k4v4 cache.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--batch B] [--ctx N]
+
+Workload (N=1): Mistral-7B head geometry (32 query heads, 8 KV heads, d=128, GQA 4), k4v4, B=32 sequences of
+N=65536 tokens, block size 16, 144-byte slots, seeded synthetic data (N(0,1) fp16 with x8 outlier channels in K),
+block table = seeded random permutation of the pages.  At N>1 GPUs the 8 KV heads (and their query heads) are
+sharded across ranks, total work fixed ("strong" scaling); no collective is on the data path.
+
+A step is one decode call (split kernel + merge kernel) replayed from a CUDA graph, as the reference times it.  The
+metric is achieved HBM GB/s over ALGORITHMIC bytes (136-byte slot payloads + Q/out + block table), whole job.
+`e2e` is the same metric through the public wrappers with host buffers: pinned H2D of the step's inputs (Q, the new
+token's K/V, slot mapping, block table, sequence lengths), paged encode of the new token, decode, D2H of the output.
+
+`--impl reference` times the reference algorithm's CPU restatement (oracle/) on the host cores, on a bounded sample.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+H_KV, GROUP, BLOCK = 8, 4, 16
+METRIC = "cda_decode_k4v4_hbm_gbs"
+UNIT = "GB/s"
+
+
+def algorithmic_bytes(B, N, H_kv, H_q, k_bits=4, v_bits=4, block=BLOCK):
+    payload = 16 * k_bits + 16 * v_bits + 8
+    return B * H_kv * N * payload + B * H_q * 128 * 2 * 2 + B * (-(-N // block)) * 4 + B * 4
+
+
+def config(args, n_gpus):
+    return {"workload": f"decode k4v4 B={args.batch} N={args.ctx} H_q={H_KV * GROUP} H_kv={H_KV} d=128 block={BLOCK}",
+            "timing": "CUDA-graph replay, CUDA events, max over ranks", "sharding": f"kv-head x{n_gpus}",
+            "l2": "inputs (cache) larger than L2; no flush needed", "page_order": "seeded random permutation"}
+
+
+# ---- clocks ---------------------------------------------------------------------------------------------------------------
+
+class ClockSampler:
+    """Poll SM clock, power and throttle reasons through NVML (read-only) while a region runs."""
+
+    def __init__(self, index: int):
+        self.samples, self.reasons = [], set()
+        self.max_mhz, self._stop, self._thr = None, threading.Event(), None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _loop(self):
+        nv = self.nv
+        names = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40,
+                 "hw_power_brake": 0x80}
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                bits = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                self.reasons.update(k for k, v in names.items() if bits & v)
+            except Exception:
+                pass
+            time.sleep(0.004)
+
+    def start(self):
+        if self.nv is not None:
+            self._thr = threading.Thread(target=self._loop, daemon=True)
+            self._thr.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._thr is not None:
+            self._thr.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+# ---- reference arm (CPU) ----------------------------------------------------------------------------------------------------
+
+def cpu_sample_case(args, n_seq):
+    """n_seq sequences of the workload built entirely on the CPU with the oracle's encoder."""
+    import torch
+    from oracle import cda_oracle as O
+    cb = O.default_codebook(16)
+    N, blocks = args.ctx, -(-args.ctx // BLOCK)
+    cache = torch.zeros(n_seq * blocks * BLOCK, H_KV, 144, dtype=torch.uint8)
+    gen = torch.Generator().manual_seed(0xCDA + N + 97 * args.batch)
+    bt = torch.randperm(n_seq * blocks, generator=gen).view(n_seq, blocks).to(torch.int32)
+    Q = torch.randn(n_seq, H_KV * GROUP, 128, generator=gen).half()
+    for b in range(n_seq):
+        K = torch.randn(N, H_KV, 128, generator=gen)
+        K[..., [3, 37, 64, 101]] *= 8.0
+        V = torch.randn(N, H_KV, 128, generator=gen)
+        O.pack_slots(cache, O.slots_of_sequence(bt[b], N, BLOCK).to(torch.int32), O.encode(K.half(), cb), O.encode(V.half(), cb))
+    return Q, cache, bt, torch.full((n_seq,), N, dtype=torch.int32), cb
+
+
+def time_oracle(Q, cache, bt, seq, cb, steps, warmup):
+    import torch
+    from oracle import cda_oracle as O
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        O.paged_decode(Q, cache, bt, seq, cb_K=cb, cb_V=cb, group=GROUP, block_size=BLOCK)
+        if i >= warmup:
+            times.append(time.perf_counter() - t0)
+    return times
+
+
+def run_reference(args):
+    import torch
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    # Bounded sample: one sequence, all 8 KV heads, truncated to a context that keeps the whole run near 90 s of CPU
+    # work.  CPU time is linear in the context length, so the GB/s figure does not depend on the truncation.
+    probe = argparse.Namespace(**vars(args))
+    probe.ctx = min(args.ctx, 8192)
+    case = cpu_sample_case(probe, 1)
+    per_token = min(time_oracle(*case, 2, 1)) / probe.ctx
+    budget = 90.0 / (args.steps + args.warmup)
+    ctx = int(max(1024, min(args.ctx, budget / per_token))) // 16 * 16
+    samp = argparse.Namespace(**vars(args))
+    samp.ctx = ctx
+    Q, cache, bt, seq, cb = cpu_sample_case(samp, 1)
+    times = time_oracle(Q, cache, bt, seq, cb, args.steps, args.warmup)
+    t = sum(times) / len(times)
+    gbs = algorithmic_bytes(1, ctx, H_KV, H_KV * GROUP) / t / 1e9
+    sample = (f"1 of {args.batch} sequences, first {ctx} of {args.ctx} tokens, all 8 KV heads, per step; "
+              "CPU restatement (oracle/) of cda.algorithm.attention.attention_compressed, torch CPU")
+    line = {"impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic", "config": config(args, args.gpus),
+            "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+# ---- our arm ---------------------------------------------------------------------------------------------------------------------
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from sub0_b200 import ops
+    from sub0_b200.kernels_cuda.wrappers import decode_hmma_v1, paged_encode_fused_cuda
+    from sub0_b200.synth import build_decode_workload, sequence_tensors
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run --nproc-per-node {args.gpus}")
+    if H_KV % world:
+        raise SystemExit("the 8 KV heads must divide evenly over the ranks")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    B, N = args.batch, args.ctx
+    hpr = H_KV // world
+    wl = build_decode_workload(B, N, H_kv=H_KV, group=GROUP, device=dev, head_lo=rank * hpr, head_hi=(rank + 1) * hpr)
+    out = torch.empty_like(wl.Q)
+    ws = ops.new_workspace(ops.decode_workspace_bytes(B, hpr * GROUP, hpr, N), dev)
+
+    def call():
+        decode_hmma_v1(wl.Q, wl.cache, wl.block_table, wl.seq_lens, out, cb_K=wl.cb_K, cb_V=wl.cb_V, group_size=GROUP,
+                       block_size=BLOCK, max_seq_len=N, workspace=ws)
+
+    # warm-up (untimed) + capture
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(max(args.warmup, 3)):
+            call()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        call()
+    for _ in range(3):
+        graph.replay()
+
+    sampler = ClockSampler(local)
+    barrier()
+    sampler.start()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    ev[0].record()
+    for i in range(args.steps):
+        graph.replay()
+        ev[i + 1].record()
+    barrier()
+    per_step = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]        # ms, device clock, launching stream
+    total_ms = ev[0].elapsed_time(ev[-1])
+    if len(sampler.samples) < 5:                                                     # short run: keep the same load going
+        t_end = time.perf_counter() + 0.3
+        while time.perf_counter() < t_end:
+            for _ in range(20):
+                graph.replay()
+            torch.cuda.synchronize()
+    sampler.stop()
+
+    t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms = float(t.item())
+    ms_step = total_ms / args.steps
+    bytes_job = algorithmic_bytes(B, N, H_KV, H_KV * GROUP)
+    value = bytes_job / (ms_step * 1e-3) / 1e9
+
+    # ---- e2e: host buffers in, host buffer out, every step ----------------------------------------------------------------
+    pin = lambda t_: t_.cpu().pin_memory()
+    hQ, hbt, hsl = pin(wl.Q), pin(wl.block_table), pin(wl.seq_lens)
+    _, Kall, Vall = sequence_tensors(0xCDA + 7, 0, B, H_KV, GROUP, dev)           # one new token per sequence
+    hK, hV = pin(Kall[:, rank * hpr:(rank + 1) * hpr].contiguous()), pin(Vall[:, rank * hpr:(rank + 1) * hpr].contiguous())
+    pos = N - 1
+    hslots = pin((wl.block_table[:, pos // BLOCK].long() * BLOCK + pos % BLOCK).to(torch.int32))
+    hout = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+    dQ, dbt, dsl = torch.empty_like(wl.Q), torch.empty_like(wl.block_table), torch.empty_like(wl.seq_lens)
+    dK, dV = torch.empty(hK.shape, dtype=hK.dtype, device=dev), torch.empty(hV.shape, dtype=hV.dtype, device=dev)
+    dslots = torch.empty(B, dtype=torch.int32, device=dev)
+    h2d = sum(x.numel() * x.element_size() for x in (hQ, hbt, hsl, hK, hV, hslots))
+    d2h = hout.numel() * hout.element_size()
+
+    def e2e_step():
+        dQ.copy_(hQ, non_blocking=True); dbt.copy_(hbt, non_blocking=True); dsl.copy_(hsl, non_blocking=True)
+        dK.copy_(hK, non_blocking=True); dV.copy_(hV, non_blocking=True); dslots.copy_(hslots, non_blocking=True)
+        paged_encode_fused_cuda(dK, dV, dslots, wl.cache, cb_K=wl.cb_K, cb_V=wl.cb_V)
+        decode_hmma_v1(dQ, wl.cache, dbt, dsl, out, cb_K=wl.cb_K, cb_V=wl.cb_V, group_size=GROUP, block_size=BLOCK,
+                       max_seq_len=N, workspace=ws)
+        hout.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t.item()) / args.steps
+    e2e_val = bytes_job / (e2e_ms * 1e-3) / 1e9
+
+    line = None
+    if rank == 0:
+        peaks_path = ROOT / "MEASURED_PEAKS.json"
+        peak, peak_src = 6650.0, "fallback"
+        if peaks_path.exists():
+            try:
+                peak, peak_src = float(json.loads(peaks_path.read_text())["hbm_gbs"]), "measured"
+            except Exception:
+                pass
+        rank_bytes = algorithmic_bytes(B, N, hpr, hpr * GROUP)
+        launch_ms = statistics.mean(per_step)
+        achieved = rank_bytes / (launch_ms * 1e-3) / 1e9
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": ms_step, "us_per_layer_median": statistics.median(per_step) * 1e3,
+                "us_per_layer_min": min(per_step) * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                "dtype": "f16", "data": "synthetic", "config": config(args, world),
+                "frac_of_8000_gbs_nominal": value / (8000.0 * world),
+                "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": UNIT, "frac": achieved / peak,
+                             "peak_source": peak_src, "traffic": None,
+                             "note": "rank-0 launch = split kernel + merge kernel (merge < 3 % of the time); algorithmic bytes of this rank's shard"},
+                "e2e": {"value": e2e_val, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d * world,
+                        "d2h_bytes_per_step": d2h * world,
+                        "what": "pinned H2D of Q/new K,V/slots/block table/seq lens + paged encode + decode + D2H of the output, synchronised every step; the KV cache is resident state"},
+                "gpu_launches": 2 * args.steps, "clocks": sampler.summary()}
+
+    # ---- CPU baseline + parity on a bounded sample (rank 0, N=1 only) ----------------------------------------------------------------
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        from oracle import cda_oracle as O
+        cores = os.cpu_count() or 1
+        torch.set_num_threads(cores)
+        n_seq = 1
+        blocks = -(-N // BLOCK)
+        sel = [B - 1]
+        rows = wl.block_table[sel].long().flatten()
+        slot_ids = (rows[:, None] * BLOCK + torch.arange(BLOCK, device=dev)[None, :]).flatten()
+        sub_cache = wl.cache[slot_ids].cpu()
+        sub_bt = torch.arange(n_seq * blocks, dtype=torch.int32).view(n_seq, blocks)
+        cb = wl.cb_K.cpu()
+        Qs = wl.Q[sel].cpu()
+        seq = torch.full((n_seq,), N, dtype=torch.int32)
+        graph.replay()
+        torch.cuda.synchronize()
+        times = time_oracle(Qs, sub_cache, sub_bt, seq, cb, 2, 1)
+        want = O.paged_decode(Qs, sub_cache, sub_bt, seq, cb_K=cb, cb_V=cb, group=GROUP, block_size=BLOCK)
+        got = out[sel].cpu()
+        err = (got.float() - want.float()).abs()
+        ok = bool((err <= 1e-3 + 2e-3 * want.float().abs()).all())
+        tcpu = sum(times) / len(times)
+        line["cpu_baseline"] = {"value": algorithmic_bytes(n_seq, N, H_KV, H_KV * GROUP) / tcpu / 1e9, "unit": UNIT, "cores": cores,
+                                "kind": "port", "ms_per_sample": tcpu * 1e3,
+                                "sample": f"{n_seq} of {B} sequences (N={N}, all 8 KV heads), the bytes the GPU encoded; oracle port, torch CPU"}
+        line["parity_sample"] = {"ok": ok, "max_abs_err": float(err.max()), "rows": int(got.shape[0] * got.shape[1])}
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=32)
+    ap.add_argument("--ctx", type=int, default=65536)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,139 @@
+// Shared device helpers for the sm_100a compressed-domain attention kernels.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/cda_b200.h"
+
+namespace cda {
+
+constexpr int kHeadDim = 128;
+constexpr float kRsqrtD = 0.08838834764831845f;   // 1/sqrt(128)
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+constexpr float kNormFloor = 1e-12f;               // Compressor.encode, compression.py:328
+
+// ---- host-side status plumbing -----------------------------------------------------------------
+void set_error(const char* fmt, ...);
+int fail(int code, const char* fmt, ...);
+int check_launch(const char* what);
+int device_sm_count(int device);   // cached cudaDevAttrMultiProcessorCount (device < 0: current)
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline int index_bytes(int bits) { return kHeadDim * bits / 8; }
+inline int payload_bytes(int kb, int vb) { return index_bytes(kb) + index_bytes(vb) + 8; }
+inline int slot_bytes_for(int kb, int vb) { return (payload_bytes(kb, vb) + 15) / 16 * 16; }
+inline bool bits_ok(int b) { return b == 4 || b == 2; }
+
+// ---- warp-level 128-point Walsh-Hadamard transform ---------------------------------------------
+// Lane `lane` holds elements 4*lane .. 4*lane+3 of a 128-vector.  Natural (Sylvester) order,
+// unnormalised: y[j] = sum_i x[i] * (-1)^popcount(i & j).
+__device__ __forceinline__ void fht128_warp(float (&v)[4], int lane) {
+  float a0 = v[0] + v[1], a1 = v[0] - v[1], a2 = v[2] + v[3], a3 = v[2] - v[3];
+  v[0] = a0 + a2; v[1] = a1 + a3; v[2] = a0 - a2; v[3] = a1 - a3;
+#pragma unroll
+  for (int mask = 1; mask < 32; mask <<= 1) {
+    const bool upper = (lane & mask) != 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float other = __shfl_xor_sync(0xffffffffu, v[i], mask);
+      v[i] = upper ? other - v[i] : v[i] + other;
+    }
+  }
+}
+
+__device__ __forceinline__ float warp_sum(float x) {
+#pragma unroll
+  for (int mask = 16; mask > 0; mask >>= 1) x += __shfl_xor_sync(0xffffffffu, x, mask);
+  return x;
+}
+
+// Four fp16 values <-> 8 bytes.
+__device__ __forceinline__ void load_half4(const __half* p, float (&v)[4]) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const __half2 lo = *reinterpret_cast<const __half2*>(&raw.x);
+  const __half2 hi = *reinterpret_cast<const __half2*>(&raw.y);
+  v[0] = __low2float(lo); v[1] = __high2float(lo); v[2] = __low2float(hi); v[3] = __high2float(hi);
+}
+__device__ __forceinline__ uint2 pack_half4(const float (&v)[4]) {
+  const __half2 lo = __floats2half2_rn(v[0], v[1]);
+  const __half2 hi = __floats2half2_rn(v[2], v[3]);
+  uint2 raw;
+  raw.x = *reinterpret_cast<const uint32_t*>(&lo);
+  raw.y = *reinterpret_cast<const uint32_t*>(&hi);
+  return raw;
+}
+__device__ __forceinline__ float round_to_half(float x) { return __half2float(__float2half_rn(x)); }
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// ---- asynchronous 16-byte copies global -> shared ------------------------------------------------
+__device__ __forceinline__ uint32_t smem_addr(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// ---- tensor-core primitives ------------------------------------------------------------------------
+// D(16x8,f32) += A(16x16,f16,row) * B(16x8,f16,col).  Fragment ownership for lane = 4*r + c:
+//   a0:(row r,   k 2c..2c+1)  a1:(row r+8, k 2c..2c+1)  a2:(row r,   k 2c+8..2c+9)  a3:(row r+8, k 2c+8..2c+9)
+//   b0:(k 2c..2c+1, col r)    b1:(k 2c+8..2c+9, col r)
+//   d0:(row r, col 2c) d1:(row r, col 2c+1) d2:(row r+8, col 2c) d3:(row r+8, col 2c+1)
+__device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                          uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Transpose an 8x8 matrix of 16-bit elements held one row-pair per lane: lane 4r+c holds (M[r][2c], M[r][2c+1])
+// and receives (M[2c][r], M[2c+1][r]).
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
+  uint32_t y;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
+  return y;
+}
+
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
+  const __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// ---- codebook look-up tables in shared memory ----------------------------------------------------
+// A table maps a code (one byte holding two 4-bit indices, or one nibble holding two 2-bit indices) to
+// the fp16 pair (level[first index], level[second index]); the first index is the higher bits, i.e.
+// the lower coordinate.  Every entry is replicated once per lane (entry e of lane l at word e*32+l) so
+// that a warp-wide gather with arbitrary codes never has a bank conflict.
+template <int BITS>
+struct Lut {
+  static constexpr int kEntries = BITS == 4 ? 256 : 16;
+  static constexpr int kWords = kEntries * 32;
+  static constexpr int kBytes = kWords * 4;
+};
+
+template <int BITS>
+__device__ __forceinline__ void build_lut(uint32_t* lut, const float* __restrict__ cb, int tid, int nthreads) {
+  constexpr int L = BITS == 4 ? 16 : 4;
+  constexpr int E = Lut<BITS>::kEntries;
+  for (int w = tid; w < E * 32; w += nthreads) {
+    const int e = w >> 5;
+    const int first = BITS == 4 ? (e >> 4) : (e >> 2);
+    const int second = BITS == 4 ? (e & 15) : (e & 3);
+    lut[w] = pack_half2(__ldg(cb + (first & (L - 1))), __ldg(cb + (second & (L - 1))));
+  }
+}
+
+}  // namespace cda

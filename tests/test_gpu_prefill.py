@@ -1,0 +1,130 @@
+"""GPU parity of the prefill path (dense loader, fused causal varlen attention) against the CPU oracle."""
+import pytest
+import torch
+
+from oracle import cda_oracle as O
+from tests import _cases as Cs
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def to_dev(case):
+    return {k: (v.to(DEV) if isinstance(v, torch.Tensor) else v) for k, v in case.items()}
+
+
+def assert_close(got, want, what=""):
+    ok, ratio, cos = Cs.close(got, want)
+    assert not bool(got.isnan().any()), f"{what}: NaN in output"
+    assert ok and cos >= 0.9999, f"{what}: worst error/tolerance {ratio:.3f}, cosine {cos:.6f}"
+
+
+def prefill_inputs(case, q_lens, seed):
+    gen = torch.Generator().manual_seed(seed)
+    cu = torch.zeros(len(q_lens) + 1, dtype=torch.int32)
+    cu[1:] = torch.tensor(q_lens).cumsum(0)
+    Q = Cs.rows(gen, int(cu[-1]), case["H_kv"] * case["group"])
+    return Q, cu
+
+
+@pytest.mark.parametrize("kb,vb", [(4, 4), (4, 2), (2, 2)])
+def test_dense_loader_matches_oracle(kb, vb):
+    from sub0_b200.kernels_cuda.fa2_cda import paged_cache_to_dense_rotated
+    lens = [40, 1, 0, 129]
+    case = Cs.paged_case(lens, H_kv=3, group=4, k_bits=kb, v_bits=vb, seed=kb + vb)
+    d = to_dev(case)
+    k, v = paged_cache_to_dense_rotated(d["cache"], d["block_table"], d["seq_lens"], cb_K=d["cb_K"], cb_V=d["cb_V"],
+                                        block_size=16, max_seq_len=144, k4v2=(kb, vb) == (4, 2))
+    kw, vw = O.dense_rotated(case["cache"], case["block_table"], case["seq_lens"], cb_K=case["cb_K"], cb_V=case["cb_V"],
+                             block_size=16, max_seq_len=144, k_bits=kb, v_bits=vb)
+    assert k.shape == (4 * 144, 3, 128)
+    assert torch.equal(k.cpu(), kw) and torch.equal(v.cpu(), vw)      # fp32 multiply + one rounding: bit-exact
+
+
+@pytest.mark.parametrize("kb,vb,group,H_kv", [(4, 4, 4, 2), (4, 4, 8, 1), (4, 2, 4, 2), (2, 2, 4, 1)])
+def test_full_prompt_prefill(kb, vb, group, H_kv):
+    """q_len == seq_len (whole prompt), lengths that are not multiples of 16 / 64 / 128, including length 1."""
+    from sub0_b200.kernels_cuda.fa2_cda import fa2_cda_prefill_varlen_v1
+    lens = [1, 63, 64, 65, 200, 333]
+    case = Cs.paged_case(lens, H_kv=H_kv, group=group, k_bits=kb, v_bits=vb, seed=77 + kb + vb + group)
+    Q, cu = prefill_inputs(case, lens, 5)
+    want = O.paged_prefill(Q, case["cache"], case["block_table"], cu, case["seq_lens"], cb_K=case["cb_K"], cb_V=case["cb_V"],
+                           group=group, block_size=16, k_bits=kb, v_bits=vb)
+    d = to_dev(case)
+    out = torch.full_like(Q, float("nan"), device=DEV)
+    fa2_cda_prefill_varlen_v1(Q.to(DEV), d["cache"], d["block_table"], cu.to(DEV), d["seq_lens"], out, cb_K=d["cb_K"],
+                              cb_V=d["cb_V"], rotation_fp32=None, group_size=group, block_size=16, max_query_len=max(lens),
+                              max_seq_len=max(lens), fuse_fa2_epilogue=True)
+    torch.cuda.synchronize()
+    assert_close(out.cpu(), want, f"k{kb}v{vb} g{group}")
+
+
+def test_chunked_prefill_with_compressed_past():
+    """q_len < seq_len: bottom-right causal alignment, k <= seq_len - q_len + q."""
+    from sub0_b200.kernels_cuda.fa2_cda import fa2_cda_prefill_varlen_v1
+    lens, q_lens = [300, 129, 64, 500], [45, 129, 1, 130]
+    case = Cs.paged_case(lens, H_kv=2, group=4, seed=99)
+    Q, cu = prefill_inputs(case, q_lens, 6)
+    want = O.paged_prefill(Q, case["cache"], case["block_table"], cu, case["seq_lens"], cb_K=case["cb_K"], cb_V=case["cb_V"],
+                           group=4, block_size=16)
+    d = to_dev(case)
+    out = torch.full_like(Q, float("nan"), device=DEV)
+    fa2_cda_prefill_varlen_v1(Q.to(DEV), d["cache"], d["block_table"], cu.to(DEV), d["seq_lens"], out, cb_K=d["cb_K"],
+                              cb_V=d["cb_V"], group_size=4, block_size=16, max_query_len=max(q_lens), max_seq_len=max(lens))
+    torch.cuda.synchronize()
+    assert_close(out.cpu(), want, "chunked")
+
+
+def test_prefill_golden_fixture(golden):
+    g = golden("prefill_g4_k4v4")
+    B, Hkv, grp, Mq, N, causal, q_off = (int(v) for v in g["meta"][:7])
+    T = torch.from_numpy
+    cache = torch.zeros(48, Hkv, 144, dtype=torch.uint8)
+    bt = torch.tensor([[2, 0, 1]], dtype=torch.int32)
+    slots = O.slots_of_sequence(bt[0], N, 16).to(torch.int32)
+    Ks = O.Slot(T(g["K_idx"])[0].permute(1, 0, 2).contiguous(), T(g["K_norm"])[0].permute(1, 0).contiguous())
+    Vs = O.Slot(T(g["V_idx"])[0].permute(1, 0, 2).contiguous(), T(g["V_norm"])[0].permute(1, 0).contiguous())
+    O.pack_slots(cache, slots, Ks, Vs)
+    from sub0_b200 import ops
+    Q = T(g["Q"])[0].permute(1, 0, 2).contiguous()                      # (Mq, H_q, 128)
+    out = torch.empty_like(Q, device=DEV)
+    ops.prefill_varlen(Q.to(DEV), cache.to(DEV), bt.to(DEV), torch.tensor([0, Mq], dtype=torch.int32, device=DEV),
+                       torch.tensor([N], dtype=torch.int32, device=DEV), out, cb_K=T(g["cb_K"]), cb_V=T(g["cb_V"]),
+                       block_size=16, max_query_len=Mq, max_seq_len=N)
+    torch.cuda.synchronize()
+    assert q_off == N - Mq and causal == 1
+    assert_close(out.cpu(), T(g["out"])[0].permute(1, 0, 2), "golden prefill")
+
+
+def test_dense_source_and_raw_kv_paths():
+    """cda_fa2_varlen_fwd_hadamard on dense rotated K/V (the reference's two-kernel route) and the raw-KV wrappers."""
+    from sub0_b200.kernels_cuda import fa2_cda
+    from sub0_b200.kernels_cuda.hmma_loader import load_fa2_cda_varlen_fused
+    lens = [100, 37]
+    case = Cs.paged_case(lens, H_kv=2, group=4, seed=123)
+    Q, cu = prefill_inputs(case, lens, 7)
+    want = O.paged_prefill(Q, case["cache"], case["block_table"], cu, case["seq_lens"], cb_K=case["cb_K"], cb_V=case["cb_V"],
+                           group=4, block_size=16)
+    d = to_dev(case)
+    max_len = 112
+    k_rot, v_rot = fa2_cda.paged_cache_to_dense_rotated(d["cache"], d["block_table"], d["seq_lens"], cb_K=d["cb_K"],
+                                                        cb_V=d["cb_V"], block_size=16, max_seq_len=max_len)
+    out = torch.full_like(Q, float("nan"), device=DEV)
+    cu_k = torch.arange(3, dtype=torch.int32, device=DEV) * max_len
+    load_fa2_cda_varlen_fused().cda_fa2_varlen_fwd_hadamard(Q.to(DEV), k_rot, v_rot, out, cu.to(DEV), cu_k, d["seq_lens"],
+                                                            100, max_len, 1.0 / 128 ** 0.5)
+    torch.cuda.synchronize()
+    assert_close(out.cpu(), want, "dense source")
+    # raw (uncompressed) K/V: the rotation cancels, so the result is plain causal attention on the raw rows
+    K = torch.cat([kv[0] for kv in case["raw"]]).to(DEV)
+    V = torch.cat([kv[1] for kv in case["raw"]]).to(DEV)
+    out2 = torch.full_like(Q, float("nan"), device=DEV)
+    fa2_cda.fa2_raw_prefill_varlen_v1(Q.to(DEV), K, V, cu.to(DEV), out2, group_size=4, max_query_len=100)
+    torch.cuda.synchronize()
+    ref = torch.zeros_like(Q)
+    for b in range(2):
+        q0, q1 = int(cu[b]), int(cu[b + 1])
+        k, v = case["raw"][b]
+        ref[q0:q1] = O.gqa_attention(Q[q0:q1].permute(1, 0, 2)[None], k.permute(1, 0, 2)[None], v.permute(1, 0, 2)[None],
+                                     group=4, causal=True)[0].permute(1, 0, 2)
+    torch.testing.assert_close(out2.cpu().float(), ref.float(), rtol=1e-2, atol=1e-2)
