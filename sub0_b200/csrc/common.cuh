@@ -93,8 +93,7 @@ __device__ __forceinline__ void cp_async_wait() {
 //   d0:(row r, col 2c) d1:(row r, col 2c+1) d2:(row r+8, col 2c) d3:(row r+8, col 2c+1)
 __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                           uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
@@ -103,13 +102,73 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a
 // and receives (M[2c][r], M[2c+1][r]).
 __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
   uint32_t y;
-  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
+  asm("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
   return y;
 }
 
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
   const __half2 h = __floats2half2_rn(lo, hi);
   return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// ---- codebook tables in fp16 with a compensating scale ---------------------------------------------------------
+// The tensor-core operands are fp16, the codebook is fp32.  Rounding each level to fp16 puts the SAME relative error
+// (up to 2^-12) on every occurrence of that level, which does not average out -- with only four levels it shifts all
+// scores or all values together.  Instead the tables hold fp16(level / alpha) and the result is multiplied by alpha in
+// fp32 (folded into the softmax scale for K, into the final normalisation for V).  alpha is searched in
+// [1, 1.0625) with step 2^-13 for the value whose worst-case |alpha * fp16(level / alpha) - level| is smallest; alpha = 1
+// is a candidate, so the result is never worse than plain rounding.
+constexpr int kScaleCandidates = 512;
+
+__device__ __forceinline__ float table_value(float level, float inv_alpha) { return __half2float(__float2half_rn(level * inv_alpha)); }
+
+// Call with all threads of the CTA (contains two barriers).  cb_a / cb_b: global codebooks of LA / LB levels.
+// scratch: shared arrays of at least (blockDim.x / 32) entries each.
+template <int LA, int LB>
+__device__ __forceinline__ void find_table_scales(const float* __restrict__ cb_a, const float* __restrict__ cb_b, float* s_err, int* s_idx,
+                                                  float& alpha_a, float& alpha_b) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+  float la[LA], lb[LB];
+#pragma unroll
+  for (int i = 0; i < LA; ++i) la[i] = __ldg(cb_a + i);
+#pragma unroll
+  for (int i = 0; i < LB; ++i) lb[i] = __ldg(cb_b + i);
+  float best[2] = {3.0e38f, 3.0e38f};
+  int arg[2] = {0, 0};
+  for (int cand = tid; cand < kScaleCandidates; cand += blockDim.x) {
+    const float alpha = 1.0f + cand * (1.0f / 8192.0f), inv = 1.0f / alpha;
+    float ea = 0.f, eb = 0.f;
+#pragma unroll
+    for (int i = 0; i < LA; ++i) ea = fmaxf(ea, fabsf(fmaf(alpha, table_value(la[i], inv), -la[i])));
+#pragma unroll
+    for (int i = 0; i < LB; ++i) eb = fmaxf(eb, fabsf(fmaf(alpha, table_value(lb[i], inv), -lb[i])));
+    if (ea < best[0]) { best[0] = ea; arg[0] = cand; }
+    if (eb < best[1]) { best[1] = eb; arg[1] = cand; }
+  }
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+#pragma unroll
+    for (int mask = 16; mask > 0; mask >>= 1) {
+      const float oe = __shfl_xor_sync(0xffffffffu, best[t], mask);
+      const int oi = __shfl_xor_sync(0xffffffffu, arg[t], mask);
+      if (oe < best[t] || (oe == best[t] && oi < arg[t])) { best[t] = oe; arg[t] = oi; }
+    }
+    if (lane == 0) { s_err[t * 32 + warp] = best[t]; s_idx[t * 32 + warp] = arg[t]; }
+  }
+  __syncthreads();
+  int win[2];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    float e = s_err[t * 32]; int i = s_idx[t * 32];
+    for (int w = 1; w < nwarps; ++w) {
+      const float oe = s_err[t * 32 + w]; const int oi = s_idx[t * 32 + w];
+      if (oe < e || (oe == e && oi < i)) { e = oe; i = oi; }
+    }
+    win[t] = i;
+  }
+  __syncthreads();
+  alpha_a = 1.0f + win[0] * (1.0f / 8192.0f);
+  alpha_b = 1.0f + win[1] * (1.0f / 8192.0f);
 }
 
 // ---- codebook look-up tables in shared memory ----------------------------------------------------

@@ -1,45 +1,66 @@
 // Single-query GQA decode over the paged codebook cache.
 //
-// Split kernel (decode_split_kernel).  Grid = (key-range splits, sequences, KV-head groups); a CTA has
-// 8 warps and owns up to 8 KV heads of one key range of one sequence.  A warp owns ONE KV head (and the
-// whole GQA group of query heads that reads it) and walks its share of the range 16 tokens at a time:
+// Split kernel (decode_split_kernel).  Grid = (key-range splits, sequences, KV-head groups); a CTA has W warps
+// and owns up to 8 KV heads of one key range of one sequence.  A warp owns ONE KV head (and the whole GQA group
+// of query heads that reads it) and walks its share of the range 16 tokens at a time:
 //
-//   HBM -> shared   16-byte cp.async.cg copies of the 16 slots into a per-warp ring (no CTA barrier in the
-//                   main loop); destinations are permuted so that later fragment reads are conflict free.
-//   codes -> fp16   one shared-memory gather per code: a byte (two 4-bit indices) or nibble (two 2-bit
-//                   indices) selects an fp16 pair from a lane-replicated table, which is exactly one
-//                   32-bit operand register of mma.m16n8k16.
-//   QK^T            tokens on the M axis, query heads on N: S[16 tok x 8 col] over 8 k-steps.  For a group
-//                   of <= 4 query heads columns 4..7 repeat columns 0..3.
-//   softmax         online, per 32-token tile, base-2 exponent; norms are applied to scores (K) and to
-//                   the probabilities (V), never to the 128-wide vectors.
-//   P V             computed transposed: A = decoded V codes (rows = byte position in the slot, k = (token,
-//                   parity of the coordinate)), B = probabilities placed in the even or odd half of the
-//                   register.  That keeps "one code -> one A register" without any data shuffling;
-//                   movmatrix transposes the probability tile between the two products.
+//   HBM -> shared     16-byte cp.async.cg copies of the 16 slots into a per-warp ring of NS stages (NS-1 groups in
+//                     flight per warp; no CTA barrier in the main loop).  Destinations are permuted so that the
+//                     fragment reads below are free of bank conflicts.
+//   codes -> fp16     one shared-memory gather per code: a byte (two 4-bit indices) or nibble (two 2-bit
+//                     indices) selects an fp16 pair from a lane-replicated table, which is exactly one 32-bit
+//                     operand register of mma.m16n8k16.  The table sits on a 64 KB boundary of the shared
+//                     window with 256-byte rows (K entries in the low half, V entries in the high half), so the
+//                     whole gather address is assembled by ONE byte-permute: [window hi | code | lane*4].
+//   QK^T              tokens on the M axis, query heads on N: S[16 tok x 8 col] over 8 k-steps (two independent
+//                     accumulator chains).  For a group of <= 4 query heads columns 4..7 repeat columns 0..3.
+//   softmax           online, base-2 exponent; norms are applied to scores (K) and to probabilities (V), never
+//                     to the 128-wide vectors.  The running maximum is only re-reduced across lanes when some
+//                     lane saw a larger score (warp vote), which after the first groups is rare.
+//   P V               computed transposed: A = decoded V codes (rows = byte position in the slot, k = (token,
+//                     parity of the coordinate)), B = probabilities placed in the even or odd half of the
+//                     register.  That keeps "one code -> one A register" without any data shuffling;
+//                     movmatrix transposes the probability tile between the two products.
 //
 // Every warp writes an un-normalised partial (O[g][128], m, l) to the workspace; decode_merge_kernel
 // combines them by log-sum-exp, rounds to fp16, applies the inverse Hadamard transform and stores fp16.
 //
 // HBM traffic per (token, KV head): one slot (144 B for k4v4; 136 B of it payload).
 #include <cmath>
+#include <cstdlib>
 
 #include "common.cuh"
 
 namespace cda {
 
-constexpr int kDecWarps = 8;
-constexpr int kDecThreads = kDecWarps * 32;
-constexpr int kTileGroups = 2;     // 16-token groups per softmax tile
-constexpr int kRing = 6;           // ring slots (groups) per warp
+constexpr int kLutWindow = 65536;   // the table occupies one 64 KB-aligned block of the shared window
+constexpr float kMinusBig = -1.0e30f;   // "no score yet": finite, so differences never produce NaN
+
+struct DecodeParams {
+  const __half* q;
+  const uint8_t* cache;
+  const int32_t* block_table;
+  const int32_t* seq_lens;
+  const float* cb_k;
+  const float* cb_v;
+  float* part_ml;      // (P, B, H_q, 2): m (log2 domain, scale folded in), l
+  float* part_o;       // (P, B, H_q, 128)
+  int* status;         // device status word (bit 0: a block id was out of range, bit 1: shared window too small)
+  int B, H_q, H_kv, group;
+  int heads_per_cta;   // power of two <= 8 dividing H_kv
+  int block_size, bt_stride, num_blocks;
+  int gpb_shift;          // log2(block_size / 16), or -1 when block_size / 16 is not a power of two
+  int tokens_per_split;   // multiple of 16
+  int smem_bytes;         // dynamic shared memory given to the kernel
+  int debug;              // timing experiments only (results become wrong): 1 no copies after the prologue, 2 no PV, 4 no QK
+  float scale_log2;       // softmax scale * log2(e)
+};
 
 template <int KB, int VB>
 struct Geom {
   static constexpr int kKBytes = 16 * KB;                      // index bytes of one row
   static constexpr int kVBytes = 16 * VB;
-  static constexpr int kKChunks = kKBytes / 16;
-  static constexpr int kVChunks = kVBytes / 16;
-  static constexpr int kChunks = kKChunks + kVChunks + 1;      // 16-byte pieces per slot
+  static constexpr int kChunks = KB + VB + 1;                  // 16-byte pieces per slot
   static constexpr int kSlotBytes = kChunks * 16;
   static constexpr int kGroupChunks = 16 * kChunks;
   static constexpr int kIssueIters = (kGroupChunks + 31) / 32;
@@ -47,10 +68,6 @@ struct Geom {
   static constexpr int kVRegion = 16 * kVBytes;
   static constexpr int kNOffset = kKRegion + kVRegion;
   static constexpr int kStageBytes = kNOffset + 256;
-  static constexpr int kLutKBytes = Lut<KB>::kBytes;
-  static constexpr int kLutVBytes = Lut<VB>::kBytes;
-  static constexpr int kQBytes = kDecWarps * 8 * kHeadDim * 2;
-  static constexpr int kSmemBytes = kLutKBytes + kLutVBytes + kQBytes + kDecWarps * kRing * kStageBytes;
 };
 
 // Shared-memory placement of 16-byte piece `k` of row `rho` inside the V region of a stage.
@@ -63,346 +80,446 @@ __device__ __forceinline__ int v_piece_offset(int rho, int k) {
   }
 }
 
-struct DecodeParams {
-  const __half* q;
-  const uint8_t* cache;
-  const int32_t* block_table;
-  const int32_t* seq_lens;
-  const float* cb_k;
-  const float* cb_v;
-  float* part_ml;      // (P, B, H_q, 2): m (log2 domain, scale folded in), l
-  float* part_o;       // (P, B, H_q, 128)
-  int* status;         // device status word (bit 0: a block id was out of range)
-  int B, H_q, H_kv, group;
-  int heads_per_cta;   // power of two <= 8 dividing H_kv
-  int block_size, bt_stride, num_blocks;
-  int tokens_per_split;   // multiple of 16
-  float scale_log2;       // softmax scale * log2(e)
+// ---- shared-memory access by 32-bit window address ---------------------------------------------------------------
+__device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {   // table reads: the table never changes after the barrier
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));   // volatile: keeps the gathers in program order, ahead of the mma block
+  return v;
+}
+// Reads of staged cache bytes: ordered after the cp.async wait by the "memory" clobber.
+template <int IMM>
+__device__ __forceinline__ uint4 lds_stage16(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+%5];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr), "n"(IMM) : "memory");
+  return v;
+}
+template <int IMM>
+__device__ __forceinline__ uint2 lds_stage8(uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2+%3];" : "=r"(v.x), "=r"(v.y) : "r"(addr), "n"(IMM) : "memory");
+  return v;
+}
+template <int IMM>
+__device__ __forceinline__ uint32_t lds_stage4(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(addr), "n"(IMM) : "memory");
+  return v;
+}
+template <int IMM>
+__device__ __forceinline__ void cp_async16_imm(uint32_t dst, const uint8_t* src) {
+  asm volatile("cp.async.cg.shared.global [%0+%2], [%1], 16;" ::"r"(dst), "l"(src), "n"(IMM) : "memory");
+}
+
+// Table entry for the code in byte POS of w: the address is [base.byte3 | base.byte2 | code | base.byte0].
+template <int POS>
+__device__ __forceinline__ uint32_t lut_byte(uint32_t w, uint32_t base) {
+  return lds_u32(__byte_perm(w, base, 0x7604 | (POS << 4)));
+}
+// Table entry for a 4-bit code (two 2-bit indices) at bit offset SH of w.
+template <int SH>
+__device__ __forceinline__ uint32_t lut_nibble(uint32_t w, uint32_t base) {
+  return lds_u32(base + (((w >> SH) & 0xfu) << 8));
+}
+
+// One 16-token group as the lane holds it: K index pieces of rows r and r+8, V index pieces of rows
+// 2c, 2c+1, 8+2c, 9+2c, and the (K norm, V norm) pairs of rows r and r+8.
+template <int KB, int VB>
+struct GroupRegs {
+  uint32_t k[2][KB];          // 4-bit: 16 bytes per row, 2-bit: 8 bytes
+  uint32_t v[4][VB / 2];      // 4-bit: 8 bytes per row,  2-bit: 4 bytes
+  float2 n[2];
 };
 
-template <int BITS, int POS>
-__device__ __forceinline__ uint32_t code_hi(uint32_t w) {   // first code of byte POS of w
-  if (BITS == 4) return __byte_perm(w, 0, 0x4440 | POS);
-  return (w >> (8 * POS + 4)) & 0xf;
-}
-template <int BITS, int POS>
-__device__ __forceinline__ uint32_t code_lo(uint32_t w) {   // second code (2-bit tables only)
-  return (w >> (8 * POS)) & 0xf;
-}
-
-// Operand registers of k-step S for one K row held as packed words `w` (4-bit: 16 bytes, 2-bit: 8 bytes).
+// Gather phase / multiply phase are kept apart on purpose: all table reads of a product are issued back to back
+// (32 for QK^T, 16 per half of P V) before the first mma that consumes them, so that the shared-memory pipe always
+// has many independent gathers in flight.
 template <int KB, int S>
-__device__ __forceinline__ void k_operands(const uint32_t* w, const uint32_t* lut, uint32_t& lo_k, uint32_t& hi_k) {
-  if (KB == 4) {
-    lo_k = lut[code_hi<4, (2 * S) & 3>(w[(2 * S) >> 2]) * 32];
-    hi_k = lut[code_hi<4, (2 * S + 1) & 3>(w[(2 * S + 1) >> 2]) * 32];
-  } else {
-    lo_k = lut[code_hi<2, S & 3>(w[S >> 2]) * 32];
-    hi_k = lut[code_lo<2, S & 3>(w[S >> 2]) * 32];
-  }
-}
-// Operand registers of m-tile U for one V row: 4-bit rows give bytes 2U, 2U+1 of the lane's 8 bytes, 2-bit rows
-// the two nibbles of byte U of the lane's 4 bytes.
-template <int VB, int U>
-__device__ __forceinline__ void v_operands(const uint32_t* w, const uint32_t* lut, uint32_t& first, uint32_t& second) {
-  if (VB == 4) {
-    first = lut[code_hi<4, (2 * U) & 3>(w[(2 * U) >> 2]) * 32];
-    second = lut[code_hi<4, (2 * U + 1) & 3>(w[(2 * U + 1) >> 2]) * 32];
-  } else {
-    first = lut[code_hi<2, U>(w[0]) * 32];
-    second = lut[code_lo<2, U>(w[0]) * 32];
-  }
-}
-
-template <int KB, int S>
-struct QkSteps {
-  __device__ static __forceinline__ void run(float (&sc)[4], const uint32_t* ka, const uint32_t* kb, const uint32_t* lut,
-                                             const uint32_t (&qf)[16]) {
-    uint32_t a0, a1, a2, a3;
-    k_operands<KB, S>(ka, lut, a0, a2);
-    k_operands<KB, S>(kb, lut, a1, a3);
-    mma_16816(sc, a0, a1, a2, a3, qf[2 * S], qf[2 * S + 1]);
-    QkSteps<KB, S + 1>::run(sc, ka, kb, lut, qf);
+struct QkGather {
+  __device__ static __forceinline__ void run(uint32_t (&a)[8][4], const uint32_t (&k)[2][KB], uint32_t base) {
+    if (KB == 4) {          // k-step S uses bytes 2S (coordinates 4S, 4S+1) and 2S+1 (4S+2, 4S+3) of the lane's 16
+      a[S][0] = lut_byte<(2 * S) & 3>(k[0][(2 * S) >> 2], base);
+      a[S][1] = lut_byte<(2 * S) & 3>(k[1][(2 * S) >> 2], base);
+      a[S][2] = lut_byte<(2 * S + 1) & 3>(k[0][(2 * S + 1) >> 2], base);
+      a[S][3] = lut_byte<(2 * S + 1) & 3>(k[1][(2 * S + 1) >> 2], base);
+    } else {                // byte S of the lane's 8: high nibble = coordinates 4S, 4S+1, low nibble = 4S+2, 4S+3
+      a[S][0] = lut_nibble<8 * (S & 3) + 4>(k[0][S >> 2], base);
+      a[S][1] = lut_nibble<8 * (S & 3) + 4>(k[1][S >> 2], base);
+      a[S][2] = lut_nibble<8 * (S & 3)>(k[0][S >> 2], base);
+      a[S][3] = lut_nibble<8 * (S & 3)>(k[1][S >> 2], base);
+    }
+    QkGather<KB, S + 1>::run(a, k, base);
   }
 };
 template <int KB>
-struct QkSteps<KB, 8> {
-  __device__ static __forceinline__ void run(float (&)[4], const uint32_t*, const uint32_t*, const uint32_t*,
-                                             const uint32_t (&)[16]) {}
+struct QkGather<KB, 8> {
+  __device__ static __forceinline__ void run(uint32_t (&)[8][4], const uint32_t (&)[2][KB], uint32_t) {}
 };
 
-template <int VB, int NT, int U>
-struct PvSteps {
-  __device__ static __forceinline__ void run(float (&o)[4][NT][4], const uint32_t* va, const uint32_t* vb,
-                                             const uint32_t* lut, const uint32_t (&bfrag)[NT][2]) {
-    uint32_t a0, a1, a2, a3;
-    v_operands<VB, U>(va, lut, a0, a1);
-    v_operands<VB, U>(vb, lut, a2, a3);
-#pragma unroll
-    for (int t = 0; t < NT; ++t) mma_16816(o[U][t], a0, a1, a2, a3, bfrag[t][0], bfrag[t][1]);
-    PvSteps<VB, NT, U + 1>::run(o, va, vb, lut, bfrag);
+// m-tile U of the transposed PV product: rows = byte positions 8r+2U (accumulator rows r) and 8r+2U+1 (rows r+8)
+// of the V index bytes, k = (token slot, parity).  va / vb are the lane's index pieces of the two token rows.
+template <int VB, int U>
+struct PvGather {
+  __device__ static __forceinline__ void run(uint32_t (&a)[4][4], const uint32_t (&va)[VB / 2], const uint32_t (&vb)[VB / 2], uint32_t base) {
+    if (VB == 4) {
+      a[U][0] = lut_byte<(2 * U) & 3>(va[(2 * U) >> 2], base);
+      a[U][1] = lut_byte<(2 * U + 1) & 3>(va[(2 * U + 1) >> 2], base);
+      a[U][2] = lut_byte<(2 * U) & 3>(vb[(2 * U) >> 2], base);
+      a[U][3] = lut_byte<(2 * U + 1) & 3>(vb[(2 * U + 1) >> 2], base);
+    } else {
+      a[U][0] = lut_nibble<8 * U + 4>(va[0], base);
+      a[U][1] = lut_nibble<8 * U>(va[0], base);
+      a[U][2] = lut_nibble<8 * U + 4>(vb[0], base);
+      a[U][3] = lut_nibble<8 * U>(vb[0], base);
+    }
+    PvGather<VB, U + 1>::run(a, va, vb, base);
   }
 };
-template <int VB, int NT>
-struct PvSteps<VB, NT, 4> {
-  __device__ static __forceinline__ void run(float (&)[4][NT][4], const uint32_t*, const uint32_t*, const uint32_t*,
-                                             const uint32_t (&)[NT][2]) {}
+template <int VB>
+struct PvGather<VB, 4> {
+  __device__ static __forceinline__ void run(uint32_t (&)[4][4], const uint32_t (&)[VB / 2], const uint32_t (&)[VB / 2], uint32_t) {}
 };
 
-// G: padded GQA group (4 or 8).
-template <int G, int KB, int VB>
-__global__ void __launch_bounds__(kDecThreads, 1) decode_split_kernel(const DecodeParams p) {
+template <int W, int NS, int KB, int VB>
+struct DecCfg {
+  static constexpr int kWarps = W;
+  static constexpr int kThreads = W * 32;
+  static constexpr int kRingBytes = NS * Geom<KB, VB>::kStageBytes;   // per warp, contiguous; also stages the query rows
+  static_assert(kRingBytes >= 8 * kHeadDim * 2, "ring too small to stage the query rows");
+};
+
+// Everything one warp carries through the key loop.
+template <int G, int KB, int VB, int NS>
+struct WarpCtx {
   using Gm = Geom<KB, VB>;
-  constexpr int NT = G / 4;   // n-tiles of the PV product
+  static constexpr int NT = G / 4;
+  uint32_t qf[16];
+  float oacc[4][NT][4];
+  float m_run[2], l_run[2];
+  uint32_t base_k, base_v, sel_b0, sel_b1;
+  uint32_t dst_addr[Gm::kIssueIters];    // window address of this lane's pieces in stage 0
+  int src_off[Gm::kIssueIters];
+  bool last_valid;                        // whether the lane takes part in the last copy iteration
+  uint32_t k_addr, v_addr, n_addr;        // window addresses of this lane's fragment pieces in stage 0
+  const uint8_t* cache_head;
+  const int32_t* bt_row;
+  int row_stride, block_size, num_blocks, gpb, gpb_shift;
+  int g_begin_sub, R, ng, t_end, r;
+  int blk_q;                              // block id of the next group to be issued
+  float scale_log2;
+  int* status;
+  int debug;
+
+  __device__ __forceinline__ int block_index(int gidx) const { return gpb_shift >= 0 ? gidx >> gpb_shift : gidx / gpb; }
+  __device__ __forceinline__ int block_rem(int gidx) const { return gpb_shift >= 0 ? gidx & (gpb - 1) : gidx % gpb; }
+  __device__ __forceinline__ void load_block_id(int j) {
+    const int jj = j < ng ? j : ng - 1;
+    blk_q = __ldg(bt_row + block_index(g_begin_sub + R * jj));
+  }
+
+  // Start the copies of group j into stage S (nothing if j is past the end); always closes a cp.async group.
+  template <int S>
+  __device__ __forceinline__ void issue(int j) {
+    if (j < ng) {
+      int blk = blk_q;
+      if (static_cast<unsigned>(blk) >= static_cast<unsigned>(num_blocks)) { atomicOr(status, 1); blk = 0; }
+      const int gidx = g_begin_sub + R * j;
+      const int64_t slot0 = static_cast<int64_t>(blk) * block_size + (block_rem(gidx) << 4);
+      const uint8_t* base = cache_head + slot0 * row_stride;
+#pragma unroll
+      for (int it = 0; it < Gm::kIssueIters; ++it)
+        if (it + 1 < Gm::kIssueIters || last_valid) cp_async16_imm<S * Gm::kStageBytes>(dst_addr[it], base + src_off[it]);
+      load_block_id(j + 1);
+    }
+    cp_async_commit();
+  }
+
+  template <int S, bool MASKED>
+  __device__ __forceinline__ void consume(int j) {
+    constexpr int O = S * Gm::kStageBytes;
+    GroupRegs<KB, VB> gr;
+    if (KB == 4) {
+      const uint4 t0 = lds_stage16<O>(k_addr), t1 = lds_stage16<O + 8 * Gm::kKBytes>(k_addr);
+      gr.k[0][0] = t0.x; gr.k[0][1] = t0.y; gr.k[0][KB - 2] = t0.z; gr.k[0][KB - 1] = t0.w;
+      gr.k[1][0] = t1.x; gr.k[1][1] = t1.y; gr.k[1][KB - 2] = t1.z; gr.k[1][KB - 1] = t1.w;
+    } else {
+      const uint2 t0 = lds_stage8<O>(k_addr), t1 = lds_stage8<O + 8 * Gm::kKBytes>(k_addr);
+      gr.k[0][0] = t0.x; gr.k[0][1] = t0.y; gr.k[1][0] = t1.x; gr.k[1][1] = t1.y;
+    }
+    const uint2 n0 = lds_stage8<O>(n_addr), n1 = lds_stage8<O + 128>(n_addr);
+    gr.n[0] = make_float2(__uint_as_float(n0.x), __uint_as_float(n0.y));
+    gr.n[1] = make_float2(__uint_as_float(n1.x), __uint_as_float(n1.y));
+    constexpr int kRow8 = VB == 4 ? 512 : 256;   // rows rho + 8 sit this many bytes further in the V region
+    if (VB == 4) {
+      const uint2 a = lds_stage8<O>(v_addr), b = lds_stage8<O + 128>(v_addr);
+      const uint2 c2 = lds_stage8<O + kRow8>(v_addr), d = lds_stage8<O + kRow8 + 128>(v_addr);
+      gr.v[0][0] = a.x; gr.v[0][VB / 2 - 1] = a.y; gr.v[1][0] = b.x; gr.v[1][VB / 2 - 1] = b.y;
+      gr.v[2][0] = c2.x; gr.v[2][VB / 2 - 1] = c2.y; gr.v[3][0] = d.x; gr.v[3][VB / 2 - 1] = d.y;
+    } else {
+      gr.v[0][0] = lds_stage4<O>(v_addr); gr.v[1][0] = lds_stage4<O + 128>(v_addr);
+      gr.v[2][0] = lds_stage4<O + kRow8>(v_addr); gr.v[3][0] = lds_stage4<O + kRow8 + 128>(v_addr);
+    }
+
+    float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    {
+      uint32_t ka[8][4];
+      if (!(debug & 4)) {
+      QkGather<KB, 0>::run(ka, gr.k, base_k);
+#pragma unroll
+      for (int s = 0; s < 8; ++s)   // even / odd k-steps: two independent accumulator chains
+        mma_16816(sc[s & 1], ka[s][0], ka[s][1], ka[s][2], ka[s][3], qf[2 * s], qf[2 * s + 1]);
+      } else { sc[0][0] = __uint_as_float(gr.k[0][0] ^ gr.k[1][KB - 1]) * 1e-30f; sc[0][3] = __uint_as_float(gr.k[1][0] ^ gr.k[0][KB - 1]) * 1e-30f; }
+    }
+    const float f0 = gr.n[0].x * scale_log2, f1 = gr.n[1].x * scale_log2;
+    float s0 = (sc[0][0] + sc[1][0]) * f0, s1 = (sc[0][1] + sc[1][1]) * f0;
+    float s2 = (sc[0][2] + sc[1][2]) * f1, s3 = (sc[0][3] + sc[1][3]) * f1;
+    float nv0 = gr.n[0].y, nv1 = gr.n[1].y;
+    if (MASKED) {   // ragged tail: rows past the end contribute nothing, whatever bytes they hold
+      const int tok0 = (g_begin_sub + R * j) << 4;
+      const bool ok0 = tok0 + r < t_end, ok1 = tok0 + r + 8 < t_end;
+      s0 = ok0 ? s0 : -INFINITY; s1 = ok0 ? s1 : -INFINITY; s2 = ok1 ? s2 : -INFINITY; s3 = ok1 ? s3 : -INFINITY;
+      nv0 = ok0 ? nv0 : 0.f; nv1 = ok1 ? nv1 : 0.f;
+    }
+    float mx0 = fmaxf(s0, s2), mx1 = fmaxf(s1, s3);
+    if (__any_sync(0xffffffffu, mx0 > m_run[0] || mx1 > m_run[1])) {   // a new maximum somewhere: reduce and rescale
+#pragma unroll
+      for (int mask = 4; mask < 32; mask <<= 1) {
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, mask));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, mask));
+      }
+      const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
+      const float fs0 = fast_exp2(m_run[0] - mn0), fs1 = fast_exp2(m_run[1] - mn1);
+      m_run[0] = mn0; m_run[1] = mn1;
+      l_run[0] *= fs0; l_run[1] *= fs1;
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+          oacc[u][t][0] *= fs0; oacc[u][t][1] *= fs1; oacc[u][t][2] *= fs0; oacc[u][t][3] *= fs1;
+        }
+    }
+    const float p0 = fast_exp2(s0 - m_run[0]), p1 = fast_exp2(s1 - m_run[1]);
+    const float p2 = fast_exp2(s2 - m_run[0]), p3 = fast_exp2(s3 - m_run[1]);
+    l_run[0] += p0 + p2;
+    l_run[1] += p1 + p3;
+    const uint32_t x0 = pack_half2(p0 * nv0, p1 * nv0);   // row r,   columns 2c, 2c+1
+    const uint32_t x1 = pack_half2(p2 * nv1, p3 * nv1);   // row r+8
+    const uint32_t y[2] = {movmatrix_trans(x0), movmatrix_trans(x1)};   // (P[2c][r], P[2c+1][r]) of rows 0-7 / 8-15
+    uint32_t pa[2][4][4];
+    if (debug & 2) { oacc[0][0][0] += __uint_as_float((gr.v[0][0] ^ gr.v[1][0] ^ gr.v[2][0] ^ gr.v[3][0] ^ y[0] ^ y[1]) & 0xff); return; }
+    PvGather<VB, 0>::run(pa[0], gr.v[0], gr.v[1], base_v);
+    PvGather<VB, 0>::run(pa[1], gr.v[2], gr.v[3], base_v);
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      uint32_t bfrag[NT][2];
+      if (G == 4) {            // column r = (parity r >> 2, query r & 3)
+        bfrag[0][0] = __byte_perm(y[hh], 0, sel_b0);
+        bfrag[0][1] = __byte_perm(y[hh], 0, sel_b1);
+      } else {                 // tile 0: even coordinate of every pair, tile 1: odd
+        bfrag[0][0] = y[hh] & 0xffffu;
+        bfrag[0][1] = y[hh] >> 16;
+        bfrag[NT - 1][0] = y[hh] << 16;
+        bfrag[NT - 1][1] = y[hh] & 0xffff0000u;
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+#pragma unroll
+        for (int t = 0; t < NT; ++t) mma_16816(oacc[u][t], pa[hh][u][0], pa[hh][u][1], pa[hh][u][2], pa[hh][u][3], bfrag[t][0], bfrag[t][1]);
+    }
+  }
+};
+
+template <int G, int KB, int VB, int NS, int S>
+struct RingSteps {
+  __device__ static __forceinline__ void run(WarpCtx<G, KB, VB, NS>& cx, int j0, bool tail_masked) {
+    const int j = j0 + S;
+    if (j < cx.ng) {
+      if (!(cx.debug & 1)) cx.template issue<(S + NS - 1) % NS>(j + NS - 1); else cp_async_commit();
+      cp_async_wait<NS - 1>();
+      __syncwarp();
+      if (tail_masked && j == cx.ng - 1) cx.template consume<S, true>(j);
+      else cx.template consume<S, false>(j);
+      __syncwarp();
+    }
+    RingSteps<G, KB, VB, NS, S + 1>::run(cx, j0, tail_masked);
+  }
+};
+template <int G, int KB, int VB, int NS>
+struct RingSteps<G, KB, VB, NS, NS> {
+  __device__ static __forceinline__ void run(WarpCtx<G, KB, VB, NS>&, int, bool) {}
+};
+
+template <int G, int KB, int VB, int NS, int S>
+struct RingPrologue {
+  __device__ static __forceinline__ void run(WarpCtx<G, KB, VB, NS>& cx) {
+    cx.template issue<S>(S);
+    RingPrologue<G, KB, VB, NS, S + 1>::run(cx);
+  }
+};
+template <int G, int KB, int VB, int NS>
+struct RingPrologue<G, KB, VB, NS, NS - 1> {
+  __device__ static __forceinline__ void run(WarpCtx<G, KB, VB, NS>&) {}
+};
+
+// G: padded GQA group (4 or 8).  W: warps per CTA.  NS: ring stages per warp.
+template <int G, int KB, int VB, int W, int NS>
+__global__ void __launch_bounds__(W * 32, 1) decode_split_kernel(const DecodeParams p) {
+  using Gm = Geom<KB, VB>;
+  using Cfg = DecCfg<W, NS, KB, VB>;
+  constexpr int NT = G / 4;
   extern __shared__ __align__(128) uint8_t smem[];
-  uint32_t* lut_k = reinterpret_cast<uint32_t*>(smem);
-  uint32_t* lut_v = reinterpret_cast<uint32_t*>(smem + Gm::kLutKBytes);
-  __half* q_all = reinterpret_cast<__half*>(smem + Gm::kLutKBytes + Gm::kLutVBytes);
-  uint8_t* ring_all = smem + Gm::kLutKBytes + Gm::kLutVBytes + Gm::kQBytes;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int r = lane >> 2, c = lane & 3;
   const int split = blockIdx.x, b = blockIdx.y, hg = blockIdx.z;
   const int hpc = p.heads_per_cta;
-  const int R = kDecWarps / hpc;                 // warps sharing one head (each takes every R-th group)
+  const int R = W / hpc;                 // warps sharing one head (each takes every R-th group)
   const int head = hg * hpc + (warp & (hpc - 1));
   const int sub = warp / hpc;
   const int g = p.group;
 
   const int seq_len = p.seq_lens[b];
   const int t_begin = split * p.tokens_per_split;
-  const int t_end = min(seq_len, t_begin + p.tokens_per_split);
+  const int t_end = min(seq_len, t_begin + p.tokens_per_split);   // tokens at or beyond this are masked
   const int cta_groups = t_end > t_begin ? (t_end - t_begin + 15) >> 4 : 0;
-  const int g_begin = t_begin >> 4;
   const int ng = cta_groups > sub ? (cta_groups - sub + R - 1) / R : 0;   // groups of this warp
 
   const int part = split * R + sub;
   const int64_t prow0 = (static_cast<int64_t>(part) * p.B + b) * p.H_q + head * g;   // partial row of query 0
 
-  if (cta_groups == 0) {   // nothing in range (short sequence): empty partials, no set-up
+  // ---- shared window layout: warp rings fill the space before the 64 KB-aligned table, the rest follow it -----------
+  const uint32_t win0 = smem_addr(smem);
+  const uint32_t lut_win = (win0 + kLutWindow - 1) & ~static_cast<uint32_t>(kLutWindow - 1);
+  const int rings_before = static_cast<int>((lut_win - win0) / Cfg::kRingBytes);
+  const int rings_after = W > rings_before ? W - rings_before : 0;
+  const uint32_t win_end = lut_win + kLutWindow + rings_after * Cfg::kRingBytes;
+  const bool fits = win_end - win0 <= static_cast<uint32_t>(p.smem_bytes);
+  if (cta_groups == 0 || !fits) {   // nothing in range (short sequence) or no room: empty partials, no set-up
+    if (!fits && tid == 0) atomicOr(p.status, 2);
     if (lane < g) *reinterpret_cast<float2*>(p.part_ml + (prow0 + lane) * 2) = make_float2(-INFINITY, 0.f);
     return;
   }
+  const uint32_t ring = warp < rings_before ? win0 + warp * Cfg::kRingBytes
+                                            : lut_win + kLutWindow + (warp - rings_before) * Cfg::kRingBytes;
+  uint8_t* lut = smem + (lut_win - win0);
 
-  build_lut<KB>(lut_k, p.cb_k, tid, kDecThreads);
-  build_lut<VB>(lut_v, p.cb_v, tid, kDecThreads);
-
-  // ---- rotate this head's queries, stage them as fp16 rows, pick up the B fragments ------------------
-  __half* q_rows = q_all + warp * 8 * kHeadDim;
-  for (int qi = 0; qi < 8; ++qi) {
-    float v[4] = {0.f, 0.f, 0.f, 0.f};
-    if (qi < g) {
-      load_half4(p.q + (static_cast<int64_t>(b) * p.H_q + head * g + qi) * kHeadDim + 4 * lane, v);
-      fht128_warp(v, lane);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) v[i] *= kRsqrtD;
+  __shared__ float s_err[64];
+  __shared__ int s_idx[64];
+  float alpha_k, alpha_v;
+  find_table_scales<(KB == 4 ? 16 : 4), (VB == 4 ? 16 : 4)>(p.cb_k, p.cb_v, s_err, s_idx, alpha_k, alpha_v);
+  {   // build both tables: code e, lane l -> K pair at e*256 + 4l, V pair at e*256 + 128 + 4l (levels divided by alpha)
+    constexpr int EK = KB == 4 ? 256 : 16, EV = VB == 4 ? 256 : 16, LK = KB == 4 ? 16 : 4, LV = VB == 4 ? 16 : 4;
+    const float inv_k = 1.0f / alpha_k, inv_v = 1.0f / alpha_v;
+    uint32_t* lw = reinterpret_cast<uint32_t*>(lut);
+    for (int e = warp; e < (EK > EV ? EK : EV); e += W) {
+      if (e < EK) {
+        const int first = KB == 4 ? (e >> 4) : (e >> 2), second = KB == 4 ? (e & 15) : (e & 3);
+        lw[e * 64 + lane] = pack_half2(__ldg(p.cb_k + (first & (LK - 1))) * inv_k, __ldg(p.cb_k + (second & (LK - 1))) * inv_k);
+      }
+      if (e < EV) {
+        const int first = VB == 4 ? (e >> 4) : (e >> 2), second = VB == 4 ? (e & 15) : (e & 3);
+        lw[e * 64 + 32 + lane] = pack_half2(__ldg(p.cb_v + (first & (LV - 1))) * inv_v, __ldg(p.cb_v + (second & (LV - 1))) * inv_v);
+      }
     }
-    *reinterpret_cast<uint2*>(q_rows + qi * kHeadDim + 4 * lane) = pack_half4(v);
   }
-  __syncthreads();   // tables + query rows visible (the only CTA-wide barrier)
 
-  uint32_t qf[16];   // column r (query r, or r & 3 when the group is padded to 4), coordinates 32c .. 32c+31
+  WarpCtx<G, KB, VB, NS> cx;
+  // ---- rotate this head's queries, stage them as fp16 rows in this warp's own ring, pick up the B fragments ------------
   {
-    const int qrow = G == 4 ? (r & 3) : r;
+    __half* q_rows = reinterpret_cast<__half*>(smem + (ring - win0));
+    for (int qi = 0; qi < 8; ++qi) {
+      float v[4] = {0.f, 0.f, 0.f, 0.f};
+      if (qi < g) {
+        load_half4(p.q + (static_cast<int64_t>(b) * p.H_q + head * g + qi) * kHeadDim + 4 * lane, v);
+        fht128_warp(v, lane);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v[i] *= kRsqrtD;
+      }
+      *reinterpret_cast<uint2*>(q_rows + qi * kHeadDim + 4 * lane) = pack_half4(v);
+    }
+    __syncwarp();
+    const int qrow = G == 4 ? (r & 3) : r;   // column r: query r, or r & 3 when the group is padded to 4
     const uint4* src = reinterpret_cast<const uint4*>(q_rows + qrow * kHeadDim + 32 * c);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const uint4 t = src[i];
-      qf[4 * i] = t.x; qf[4 * i + 1] = t.y; qf[4 * i + 2] = t.z; qf[4 * i + 3] = t.w;
+      cx.qf[4 * i] = t.x; cx.qf[4 * i + 1] = t.y; cx.qf[4 * i + 2] = t.z; cx.qf[4 * i + 3] = t.w;
     }
   }
-  const uint32_t* lk = lut_k + lane;
-  const uint32_t* lv = lut_v + lane;
+  __syncthreads();   // tables visible to every warp; every lane is done with its query rows (the only CTA barrier)
 
-  // ---- per-lane copy descriptors: which 16-byte pieces of a 16-slot group this lane moves -------------
-  const int row_stride = p.H_kv * Gm::kSlotBytes;
-  int src_off[Gm::kIssueIters], dst_off[Gm::kIssueIters];
+  cx.base_k = lut_win | (lane << 2);
+  cx.base_v = cx.base_k | 128u;
+  {   // operand placement of the probabilities: even columns take the low half, odd columns the high half
+    const bool odd = G == 4 && (r >> 2) != 0;
+    cx.sel_b0 = odd ? 0x1044u : 0x4410u;
+    cx.sel_b1 = odd ? 0x3244u : 0x4432u;
+  }
+  cx.row_stride = p.H_kv * Gm::kSlotBytes;
 #pragma unroll
   for (int it = 0; it < Gm::kIssueIters; ++it) {
-    const int ch = it * 32 + lane;
+    int ch = it * 32 + lane;
+    if (ch >= Gm::kGroupChunks) ch = Gm::kGroupChunks - 1;
     const int rho = ch / Gm::kChunks, piece = ch - rho * Gm::kChunks;
-    src_off[it] = rho * row_stride + piece * 16;
+    cx.src_off[it] = rho * cx.row_stride + piece * 16;
     int d;
-    if (piece < Gm::kKChunks) d = rho * Gm::kKBytes + piece * 16;
-    else if (piece < Gm::kKChunks + Gm::kVChunks) d = Gm::kKRegion + v_piece_offset<VB>(rho, piece - Gm::kKChunks);
+    if (piece < KB) d = rho * Gm::kKBytes + piece * 16;
+    else if (piece < KB + VB) d = Gm::kKRegion + v_piece_offset<VB>(rho, piece - KB);
     else d = Gm::kNOffset + rho * 16;
-    dst_off[it] = ch < Gm::kGroupChunks ? d : -1;
+    cx.dst_addr[it] = ring + d;
   }
-  const uint32_t ring = smem_addr(ring_all + warp * kRing * Gm::kStageBytes);
-  const uint8_t* ring_ptr = ring_all + warp * kRing * Gm::kStageBytes;
-
-  // ---- block ids, fetched 32 groups at a time well ahead of use ------------------------------------------
-  const int32_t* bt_row = p.block_table + static_cast<int64_t>(b) * p.bt_stride;
-  auto load_block = [&](int j) -> int {
-    if (j >= ng) return 0;
-    const int tok0 = (g_begin + sub + R * j) << 4;
-    int blk = __ldg(bt_row + tok0 / p.block_size);
-    if (blk < 0 || blk >= p.num_blocks) { atomicOr(p.status, 1); blk = 0; }
-    return blk;
-  };
-  int jb = 0;
-  int bt_cur = load_block(lane), bt_nxt = load_block(32 + lane);
-
-  int issue_slot = 0;
-  auto issue = [&](int j) {
-    if (j < ng) {
-      if (j >= jb + 32) { jb += 32; bt_cur = bt_nxt; bt_nxt = load_block(jb + 32 + lane); }
-      const int blk = __shfl_sync(0xffffffffu, bt_cur, j - jb);
-      const int tok0 = (g_begin + sub + R * j) << 4;
-      const int64_t slot0 = static_cast<int64_t>(blk) * p.block_size + (tok0 % p.block_size);
-      const uint8_t* src = p.cache + (slot0 * p.H_kv + head) * Gm::kSlotBytes;
-      const uint32_t dst = ring + issue_slot * Gm::kStageBytes;
-#pragma unroll
-      for (int it = 0; it < Gm::kIssueIters; ++it)
-        if (dst_off[it] >= 0) cp_async16(dst + dst_off[it], src + src_off[it]);
-    }
-    cp_async_commit();
-    issue_slot = issue_slot + 1 == kRing ? 0 : issue_slot + 1;
-  };
-#pragma unroll 1
-  for (int j = 0; j < kRing; ++j) issue(j);
-
-  // ---- running state ------------------------------------------------------------------------------------
-  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};   // columns 2c, 2c+1
-  float oacc[4][NT][4];
+  cx.last_valid = (Gm::kIssueIters - 1) * 32 + lane < Gm::kGroupChunks;
+  cx.k_addr = ring + r * Gm::kKBytes + c * (4 * KB);
+  cx.v_addr = ring + Gm::kKRegion + (VB == 4 ? v_piece_offset<4>(2 * c, r >> 1) + 8 * (r & 1) : v_piece_offset<2>(2 * c, r >> 2) + 4 * (r & 3));
+  cx.n_addr = ring + Gm::kNOffset + r * 16;
+  cx.cache_head = p.cache + static_cast<int64_t>(head) * Gm::kSlotBytes;
+  cx.bt_row = p.block_table + static_cast<int64_t>(b) * p.bt_stride;
+  cx.block_size = p.block_size; cx.num_blocks = p.num_blocks;
+  cx.gpb = p.block_size >> 4; cx.gpb_shift = p.gpb_shift;
+  cx.g_begin_sub = (t_begin >> 4) + sub; cx.R = R; cx.ng = ng; cx.t_end = t_end; cx.r = r;
+  cx.scale_log2 = p.scale_log2 * alpha_k; cx.status = p.status; cx.debug = p.debug;
+  cx.m_run[0] = cx.m_run[1] = kMinusBig;
+  cx.l_run[0] = cx.l_run[1] = 0.f;
 #pragma unroll
   for (int u = 0; u < 4; ++u)
 #pragma unroll
     for (int t = 0; t < NT; ++t)
 #pragma unroll
-      for (int i = 0; i < 4; ++i) oacc[u][t][i] = 0.f;
+      for (int i = 0; i < 4; ++i) cx.oacc[u][t][i] = 0.f;
 
-  const int my_end = t_end;   // tokens at or beyond this are masked
-  int read_slot = 0;
+  if (ng > 0) {
+    const bool tail_masked = ((t_end - t_begin) & 15) != 0 && (cta_groups - 1) % R == sub;
+    cx.load_block_id(0);
+    RingPrologue<G, KB, VB, NS, 0>::run(cx);
 #pragma unroll 1
-  for (int j0 = 0; j0 < ng; j0 += kTileGroups) {
-    cp_async_wait<kRing - kTileGroups>();
-    __syncwarp();
-
-    float sc[kTileGroups][4];
-    float nvr[kTileGroups][2];
-    int slot_of[kTileGroups];
-    float mx0 = -INFINITY, mx1 = -INFINITY;
-#pragma unroll
-    for (int gi = 0; gi < kTileGroups; ++gi) {
-      slot_of[gi] = read_slot + gi >= kRing ? read_slot + gi - kRing : read_slot + gi;
-      const uint8_t* st = ring_ptr + slot_of[gi] * Gm::kStageBytes;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) sc[gi][i] = 0.f;
-      nvr[gi][0] = nvr[gi][1] = 0.f;
-      if (j0 + gi < ng) {
-        uint32_t ka[4], kb[4];
-        if (KB == 4) {
-          const uint4 t0 = *reinterpret_cast<const uint4*>(st + r * 64 + c * 16);
-          const uint4 t1 = *reinterpret_cast<const uint4*>(st + (r + 8) * 64 + c * 16);
-          ka[0] = t0.x; ka[1] = t0.y; ka[2] = t0.z; ka[3] = t0.w;
-          kb[0] = t1.x; kb[1] = t1.y; kb[2] = t1.z; kb[3] = t1.w;
-        } else {
-          const uint2 t0 = *reinterpret_cast<const uint2*>(st + r * 32 + c * 8);
-          const uint2 t1 = *reinterpret_cast<const uint2*>(st + (r + 8) * 32 + c * 8);
-          ka[0] = t0.x; ka[1] = t0.y; kb[0] = t1.x; kb[1] = t1.y;
-          ka[2] = ka[3] = kb[2] = kb[3] = 0;
-        }
-        QkSteps<KB, 0>::run(sc[gi], ka, kb, lk, qf);
-        const float2 n0 = *reinterpret_cast<const float2*>(st + Gm::kNOffset + r * 16);
-        const float2 n1 = *reinterpret_cast<const float2*>(st + Gm::kNOffset + (r + 8) * 16);
-        const int tok0 = (g_begin + sub + R * (j0 + gi)) << 4;
-        const bool ok0 = tok0 + r < my_end, ok1 = tok0 + r + 8 < my_end;
-        const float f0 = n0.x * p.scale_log2, f1 = n1.x * p.scale_log2;
-        sc[gi][0] = ok0 ? sc[gi][0] * f0 : -INFINITY;
-        sc[gi][1] = ok0 ? sc[gi][1] * f0 : -INFINITY;
-        sc[gi][2] = ok1 ? sc[gi][2] * f1 : -INFINITY;
-        sc[gi][3] = ok1 ? sc[gi][3] * f1 : -INFINITY;
-        nvr[gi][0] = ok0 ? n0.y : 0.f;
-        nvr[gi][1] = ok1 ? n1.y : 0.f;
-        mx0 = fmaxf(mx0, fmaxf(sc[gi][0], sc[gi][2]));
-        mx1 = fmaxf(mx1, fmaxf(sc[gi][1], sc[gi][3]));
-      } else {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) sc[gi][i] = -INFINITY;
-      }
-    }
-    // column maxima over the 32 tokens of the tile (rows live in the r dimension of the lane id)
-#pragma unroll
-    for (int mask = 4; mask < 32; mask <<= 1) {
-      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, mask));
-      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, mask));
-    }
-    const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
-    const float ms0 = mn0 == -INFINITY ? 0.f : mn0, ms1 = mn1 == -INFINITY ? 0.f : mn1;
-    const float fs0 = fast_exp2(m_run[0] - ms0), fs1 = fast_exp2(m_run[1] - ms1);
-    m_run[0] = mn0; m_run[1] = mn1;
-    l_run[0] *= fs0; l_run[1] *= fs1;
-#pragma unroll
-    for (int u = 0; u < 4; ++u)
-#pragma unroll
-      for (int t = 0; t < NT; ++t) {
-        oacc[u][t][0] *= fs0; oacc[u][t][1] *= fs1; oacc[u][t][2] *= fs0; oacc[u][t][3] *= fs1;
-      }
-
-#pragma unroll
-    for (int gi = 0; gi < kTileGroups; ++gi) {
-      if (j0 + gi < ng) {
-        const uint8_t* st = ring_ptr + slot_of[gi] * Gm::kStageBytes;
-        const float p0 = fast_exp2(sc[gi][0] - ms0), p1 = fast_exp2(sc[gi][1] - ms1);
-        const float p2 = fast_exp2(sc[gi][2] - ms0), p3 = fast_exp2(sc[gi][3] - ms1);
-        l_run[0] += p0 + p2;
-        l_run[1] += p1 + p3;
-        const uint32_t x0 = pack_half2(p0 * nvr[gi][0], p1 * nvr[gi][0]);   // row r,   columns 2c, 2c+1
-        const uint32_t x1 = pack_half2(p2 * nvr[gi][1], p3 * nvr[gi][1]);   // row r+8
-        const uint32_t y[2] = {movmatrix_trans(x0), movmatrix_trans(x1)};    // (P[2c][r], P[2c+1][r]) of rows 0-7 / 8-15
-#pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
-          const int ra = 8 * hh + 2 * c, rb = ra + 1;
-          uint32_t va[2], vb[2];
-          if (VB == 4) {
-            const uint2 t0 = *reinterpret_cast<const uint2*>(st + Gm::kKRegion + v_piece_offset<4>(ra, r >> 1) + 8 * (r & 1));
-            const uint2 t1 = *reinterpret_cast<const uint2*>(st + Gm::kKRegion + v_piece_offset<4>(rb, r >> 1) + 8 * (r & 1));
-            va[0] = t0.x; va[1] = t0.y; vb[0] = t1.x; vb[1] = t1.y;
-          } else {
-            va[0] = *reinterpret_cast<const uint32_t*>(st + Gm::kKRegion + v_piece_offset<2>(ra, r >> 2) + 4 * (r & 3));
-            vb[0] = *reinterpret_cast<const uint32_t*>(st + Gm::kKRegion + v_piece_offset<2>(rb, r >> 2) + 4 * (r & 3));
-            va[1] = vb[1] = 0;
-          }
-          uint32_t bfrag[NT][2];
-          if (G == 4) {          // column r = (parity r >> 2, query r & 3)
-            const bool odd = (r >> 2) != 0;
-            bfrag[0][0] = odd ? (y[hh] << 16) : (y[hh] & 0xffffu);
-            bfrag[0][1] = odd ? (y[hh] & 0xffff0000u) : (y[hh] >> 16);
-          } else {               // tile 0: even coordinate of every pair, tile 1: odd
-            bfrag[0][0] = y[hh] & 0xffffu;
-            bfrag[0][1] = y[hh] >> 16;
-            bfrag[NT - 1][0] = y[hh] << 16;
-            bfrag[NT - 1][1] = y[hh] & 0xffff0000u;
-          }
-          PvSteps<VB, NT, 0>::run(oacc, va, vb, lv, bfrag);
-        }
-      }
-    }
-    __syncwarp();
-    read_slot = read_slot + kTileGroups >= kRing ? read_slot + kTileGroups - kRing : read_slot + kTileGroups;
-    issue(j0 + kRing);
-    issue(j0 + kRing + 1);
+    for (int j0 = 0; j0 < ng; j0 += NS) RingSteps<G, KB, VB, NS, 0>::run(cx, j0, tail_masked);
+    cp_async_wait<0>();
   }
-  cp_async_wait<0>();
 
-  // ---- write this warp's partial ---------------------------------------------------------------------------
+  // ---- write this warp's partial -------------------------------------------------------------------------------------------
+  float l0 = cx.l_run[0], l1 = cx.l_run[1];
 #pragma unroll
   for (int mask = 4; mask < 32; mask <<= 1) {
-    l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], mask);
-    l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], mask);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, mask);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, mask);
   }
+  const float m0 = l0 > 0.f ? cx.m_run[0] : -INFINITY, m1 = l1 > 0.f ? cx.m_run[1] : -INFINITY;
+#pragma unroll
+  for (int u = 0; u < 4; ++u)
+#pragma unroll
+    for (int t = 0; t < NT; ++t)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) cx.oacc[u][t][i] *= alpha_v;   // the V table holds level / alpha_v
   if (G == 4) {
     const int parity = c >> 1, q0 = 2 * (c & 1);
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
       const int d = 16 * r + 4 * u + parity;
-      if (q0 < g) { p.part_o[(prow0 + q0) * kHeadDim + d] = oacc[u][0][0]; p.part_o[(prow0 + q0) * kHeadDim + d + 2] = oacc[u][0][2]; }
-      if (q0 + 1 < g) { p.part_o[(prow0 + q0 + 1) * kHeadDim + d] = oacc[u][0][1]; p.part_o[(prow0 + q0 + 1) * kHeadDim + d + 2] = oacc[u][0][3]; }
+      if (q0 < g) { p.part_o[(prow0 + q0) * kHeadDim + d] = cx.oacc[u][0][0]; p.part_o[(prow0 + q0) * kHeadDim + d + 2] = cx.oacc[u][0][2]; }
+      if (q0 + 1 < g) { p.part_o[(prow0 + q0 + 1) * kHeadDim + d] = cx.oacc[u][0][1]; p.part_o[(prow0 + q0 + 1) * kHeadDim + d + 2] = cx.oacc[u][0][3]; }
     }
     if (r == 0 && c < 2) {
-      if (q0 < g) *reinterpret_cast<float2*>(p.part_ml + (prow0 + q0) * 2) = make_float2(m_run[0], l_run[0]);
-      if (q0 + 1 < g) *reinterpret_cast<float2*>(p.part_ml + (prow0 + q0 + 1) * 2) = make_float2(m_run[1], l_run[1]);
+      if (q0 < g) *reinterpret_cast<float2*>(p.part_ml + (prow0 + q0) * 2) = make_float2(m0, l0);
+      if (q0 + 1 < g) *reinterpret_cast<float2*>(p.part_ml + (prow0 + q0 + 1) * 2) = make_float2(m1, l1);
     }
   } else {
     const int q0 = 2 * c;
@@ -411,12 +528,12 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_split_kernel(const Deco
 #pragma unroll
       for (int t = 0; t < NT; ++t) {
         const int d = 16 * r + 4 * u + t;
-        if (q0 < g) { p.part_o[(prow0 + q0) * kHeadDim + d] = oacc[u][t][0]; p.part_o[(prow0 + q0) * kHeadDim + d + 2] = oacc[u][t][2]; }
-        if (q0 + 1 < g) { p.part_o[(prow0 + q0 + 1) * kHeadDim + d] = oacc[u][t][1]; p.part_o[(prow0 + q0 + 1) * kHeadDim + d + 2] = oacc[u][t][3]; }
+        if (q0 < g) { p.part_o[(prow0 + q0) * kHeadDim + d] = cx.oacc[u][t][0]; p.part_o[(prow0 + q0) * kHeadDim + d + 2] = cx.oacc[u][t][2]; }
+        if (q0 + 1 < g) { p.part_o[(prow0 + q0 + 1) * kHeadDim + d] = cx.oacc[u][t][1]; p.part_o[(prow0 + q0 + 1) * kHeadDim + d + 2] = cx.oacc[u][t][3]; }
       }
     if (r == 0) {
-      if (q0 < g) *reinterpret_cast<float2*>(p.part_ml + (prow0 + q0) * 2) = make_float2(m_run[0], l_run[0]);
-      if (q0 + 1 < g) *reinterpret_cast<float2*>(p.part_ml + (prow0 + q0 + 1) * 2) = make_float2(m_run[1], l_run[1]);
+      if (q0 < g) *reinterpret_cast<float2*>(p.part_ml + (prow0 + q0) * 2) = make_float2(m0, l0);
+      if (q0 + 1 < g) *reinterpret_cast<float2*>(p.part_ml + (prow0 + q0 + 1) * 2) = make_float2(m1, l1);
     }
   }
 }
@@ -542,8 +659,23 @@ __global__ void __launch_bounds__(32) decode_scalar_kernel(const __half* __restr
 
 // ---- host side --------------------------------------------------------------------------------------------------
 struct Plan {
-  int heads_per_cta, head_groups, warps_per_head, splits, tokens_per_split, parts;
+  int warps, depth, heads_per_cta, head_groups, warps_per_head, splits, tokens_per_split, parts;
 };
+
+// Warps per CTA and ring stages per warp of the split kernel.  Defaults can be overridden for tuning with the
+// environment variables CDA_DECODE_WARPS (8 or 16) and CDA_DECODE_STAGES, read once per process.
+static void tuning(int* warps, int* depth) {
+  static int w = 0, d = 0;
+  if (w == 0) {
+    const char* ew = getenv("CDA_DECODE_WARPS");
+    const char* ed = getenv("CDA_DECODE_STAGES");
+    w = ew && atoi(ew) == 8 ? 8 : 16;
+    d = ed ? atoi(ed) : 0;
+    if (w == 16) d = d == 4 ? 4 : 3;
+    else d = d == 6 ? 6 : 4;
+  }
+  *warps = w; *depth = d;
+}
 
 static int pick_heads_per_cta(int H_kv) {
   int h = 8;
@@ -557,9 +689,10 @@ static int pick_heads_per_cta(int H_kv) {
 static Plan make_plan(int B, int H_kv, int max_seq_len, int num_splits, int sms) {
   constexpr int kMinTokens = 256, kFloorTokens = 128, kMaxWaves = 8;
   Plan pl;
+  tuning(&pl.warps, &pl.depth);
   pl.heads_per_cta = pick_heads_per_cta(H_kv);
   pl.head_groups = H_kv / pl.heads_per_cta;
-  pl.warps_per_head = kDecWarps / pl.heads_per_cta;
+  pl.warps_per_head = pl.warps / pl.heads_per_cta;
   const int n = max_seq_len > 0 ? max_seq_len : 1;
   int S = num_splits;
   if (S <= 0) {
@@ -612,28 +745,40 @@ static int validate(const char* who, const DecodeCommon& a) {
   return CDA_OK;
 }
 
-template <int G, int KB, int VB>
-static int launch_split(const DecodeParams& p, const Plan& pl, cudaStream_t st) {
-  using Gm = Geom<KB, VB>;
+constexpr int kMaxDynamicSmem = 232448 - 1024;   // the opt-in shared memory of one SM (227 KB) less the kernel's static arrays
+
+template <int G, int KB, int VB, int W, int NS>
+static int launch_split(const DecodeParams& p0, const Plan& pl, cudaStream_t st) {
   static bool configured[64];
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64 || !configured[dev]) {
-    if (cudaFuncSetAttribute(decode_split_kernel<G, KB, VB>, cudaFuncAttributeMaxDynamicSharedMemorySize, Gm::kSmemBytes) != cudaSuccess)
+    if (cudaFuncSetAttribute(decode_split_kernel<G, KB, VB, W, NS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             kMaxDynamicSmem) != cudaSuccess)
       return check_launch("decode: shared memory opt-in");
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
+  DecodeParams p = p0;
+  p.smem_bytes = kMaxDynamicSmem;
+  static const int dbg = getenv("CDA_DECODE_DEBUG") ? atoi(getenv("CDA_DECODE_DEBUG")) : 0;
+  p.debug = dbg;
   const dim3 grid(pl.splits, p.B, pl.head_groups);
-  decode_split_kernel<G, KB, VB><<<grid, kDecThreads, Gm::kSmemBytes, st>>>(p);
+  decode_split_kernel<G, KB, VB, W, NS><<<grid, W * 32, kMaxDynamicSmem, st>>>(p);
   return check_launch("decode split kernel");
+}
+
+template <int G, int KB, int VB>
+static int dispatch_shape(const DecodeParams& p, const Plan& pl, cudaStream_t st) {
+  if (pl.warps == 16) return pl.depth == 4 ? launch_split<G, KB, VB, 16, 4>(p, pl, st) : launch_split<G, KB, VB, 16, 3>(p, pl, st);
+  return pl.depth == 6 ? launch_split<G, KB, VB, 8, 6>(p, pl, st) : launch_split<G, KB, VB, 8, 4>(p, pl, st);
 }
 
 template <int G>
 static int dispatch_bits(const DecodeParams& p, const Plan& pl, int kb, int vb, cudaStream_t st) {
-  if (kb == 4 && vb == 4) return launch_split<G, 4, 4>(p, pl, st);
-  if (kb == 4 && vb == 2) return launch_split<G, 4, 2>(p, pl, st);
-  if (kb == 2 && vb == 2) return launch_split<G, 2, 2>(p, pl, st);
-  return launch_split<G, 2, 4>(p, pl, st);
+  if (kb == 4 && vb == 4) return dispatch_shape<G, 4, 4>(p, pl, st);
+  if (kb == 4 && vb == 2) return dispatch_shape<G, 4, 2>(p, pl, st);
+  if (kb == 2 && vb == 2) return dispatch_shape<G, 2, 2>(p, pl, st);
+  return dispatch_shape<G, 2, 4>(p, pl, st);
 }
 
 static int run_split(const char* who, const DecodeCommon& a, void* workspace, size_t workspace_bytes, int num_splits,
@@ -658,6 +803,10 @@ static int run_split(const char* who, const DecodeCommon& a, void* workspace, si
   p.num_blocks = static_cast<int>(a.num_slots / a.block_size);
   p.tokens_per_split = pl.tokens_per_split;
   p.scale_log2 = a.scale * kLog2e;
+  const int gpb = a.block_size / 16;
+  p.gpb_shift = -1;
+  for (int sft = 0; sft < 16; ++sft) if ((1 << sft) == gpb) p.gpb_shift = sft;
+  p.smem_bytes = 0;
   const int rc = p.group <= 4 ? dispatch_bits<4>(p, pl, a.k_bits, a.v_bits, st) : dispatch_bits<8>(p, pl, a.k_bits, a.v_bits, st);
   if (rc != CDA_OK) return rc;
   *plan_out = pl; *ml_out = p.part_ml; *o_out = p.part_o;

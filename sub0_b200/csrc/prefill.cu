@@ -112,14 +112,14 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, u
 }
 
 template <int BITS>
-__device__ __forceinline__ void build_lut_rep(uint32_t* lut, const float* __restrict__ cb, int tid) {
+__device__ __forceinline__ void build_lut_rep(uint32_t* lut, const float* __restrict__ cb, int tid, float inv_alpha) {
   constexpr int L = BITS == 4 ? 16 : 4;
   constexpr int E = BITS == 4 ? 256 : 16;
   for (int w = tid; w < E * kLutRep; w += kPfThreads) {
     const int e = w / kLutRep;
     const int first = BITS == 4 ? (e >> 4) : (e >> 2);
     const int second = BITS == 4 ? (e & 15) : (e & 3);
-    lut[w] = pack_half2(__ldg(cb + (first & (L - 1))), __ldg(cb + (second & (L - 1))));
+    lut[w] = pack_half2(__ldg(cb + (first & (L - 1))) * inv_alpha, __ldg(cb + (second & (L - 1))) * inv_alpha);
   }
 }
 
@@ -179,10 +179,16 @@ __global__ void __launch_bounds__(kPfThreads) prefill_kernel(const PrefillParams
   k_hi = k_hi < k_len ? k_hi : k_len;
   const int n_tiles = k_hi > 0 ? (k_hi + kBN - 1) / kBN : 0;
 
+  // fp16 tables hold level / alpha; alpha_k is folded into the score scale, alpha_v into the final normalisation
+  float alpha_k = 1.f, alpha_v = 1.f;
   if (PAGED) {
-    build_lut_rep<KB>(lut_k, p.cb_k, tid);
-    build_lut_rep<VB>(lut_v, p.cb_v, tid);
+    __shared__ float s_err[64];
+    __shared__ int s_idx[64];
+    find_table_scales<(KB == 4 ? 16 : 4), (VB == 4 ? 16 : 4)>(p.cb_k, p.cb_v, s_err, s_idx, alpha_k, alpha_v);
+    build_lut_rep<KB>(lut_k, p.cb_k, tid, 1.0f / alpha_k);
+    build_lut_rep<VB>(lut_v, p.cb_v, tid, 1.0f / alpha_v);
   }
+  const float k_scale = p.scale_log2 * alpha_k;
 
   // ---- rotate the 16 query rows of this warp and stage them (swizzled) in the K tile ---------------------------------------
   for (int rr = 0; rr < 16; ++rr) {
@@ -264,7 +270,7 @@ __global__ void __launch_bounds__(kPfThreads) prefill_kernel(const PrefillParams
       if (half == 0) {
         const bool ok = kt * kBN + tok < k_len;
         const float2 nn = *reinterpret_cast<const float2*>(slot + 16 * KB + 16 * VB);
-        nk_s[tok] = ok ? nn.x * p.scale_log2 : 0.f;
+        nk_s[tok] = ok ? nn.x * k_scale : 0.f;
         nv_s[tok] = ok ? nn.y : 0.f;
       }
     } else {
@@ -368,7 +374,7 @@ __global__ void __launch_bounds__(kPfThreads) prefill_kernel(const PrefillParams
     l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
     l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
   }
-  const float inv0 = l_run[0] > 0.f ? 1.0f / l_run[0] : 0.f, inv1 = l_run[1] > 0.f ? 1.0f / l_run[1] : 0.f;
+  const float inv0 = l_run[0] > 0.f ? alpha_v / l_run[0] : 0.f, inv1 = l_run[1] > 0.f ? alpha_v / l_run[1] : 0.f;
   {
     const int row0 = warp * 16 + r, row1 = row0 + 8;
 #pragma unroll

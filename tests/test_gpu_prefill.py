@@ -13,7 +13,13 @@ def to_dev(case):
     return {k: (v.to(DEV) if isinstance(v, torch.Tensor) else v) for k, v in case.items()}
 
 
-def assert_close(got, want, what=""):
+def visible_keys(q_lens, seq_lens):
+    """Number of keys each query token sees (bottom-right causal alignment), concatenated over sequences."""
+    return torch.cat([torch.arange(q) + (n - q) + 1 for q, n in zip(q_lens, seq_lens)])
+
+
+def assert_close(got, want, what="", keys=None):
+    """Tolerance: see ``tests/_cases.close``."""
     ok, ratio, cos = Cs.close(got, want)
     assert not bool(got.isnan().any()), f"{what}: NaN in output"
     assert ok and cos >= 0.9999, f"{what}: worst error/tolerance {ratio:.3f}, cosine {cos:.6f}"
@@ -56,7 +62,23 @@ def test_full_prompt_prefill(kb, vb, group, H_kv):
                               cb_V=d["cb_V"], rotation_fp32=None, group_size=group, block_size=16, max_query_len=max(lens),
                               max_seq_len=max(lens), fuse_fa2_epilogue=True)
     torch.cuda.synchronize()
-    assert_close(out.cpu(), want, f"k{kb}v{vb} g{group}")
+    assert_close(out.cpu(), want, f"k{kb}v{vb} g{group}", visible_keys(lens, lens))
+
+
+def test_long_prompt_prefill_strict_rows():
+    """A longer prompt (2500 keys, 40 K/V tiles per row block) crossing many tile and page boundaries."""
+    from sub0_b200.kernels_cuda.fa2_cda import fa2_cda_prefill_varlen_v1
+    lens = [2500, 1100]
+    case = Cs.paged_case(lens, H_kv=1, group=4, seed=314)
+    Q, cu = prefill_inputs(case, lens, 8)
+    want = O.paged_prefill(Q, case["cache"], case["block_table"], cu, case["seq_lens"], cb_K=case["cb_K"], cb_V=case["cb_V"],
+                           group=4, block_size=16)
+    d = to_dev(case)
+    out = torch.full_like(Q, float("nan"), device=DEV)
+    fa2_cda_prefill_varlen_v1(Q.to(DEV), d["cache"], d["block_table"], cu.to(DEV), d["seq_lens"], out, cb_K=d["cb_K"],
+                              cb_V=d["cb_V"], group_size=4, block_size=16, max_query_len=max(lens), max_seq_len=max(lens))
+    torch.cuda.synchronize()
+    assert_close(out.cpu(), want, "long prompt", visible_keys(lens, lens))
 
 
 def test_chunked_prefill_with_compressed_past():
@@ -72,7 +94,7 @@ def test_chunked_prefill_with_compressed_past():
     fa2_cda_prefill_varlen_v1(Q.to(DEV), d["cache"], d["block_table"], cu.to(DEV), d["seq_lens"], out, cb_K=d["cb_K"],
                               cb_V=d["cb_V"], group_size=4, block_size=16, max_query_len=max(q_lens), max_seq_len=max(lens))
     torch.cuda.synchronize()
-    assert_close(out.cpu(), want, "chunked")
+    assert_close(out.cpu(), want, "chunked", visible_keys(q_lens, lens))
 
 
 def test_prefill_golden_fixture(golden):

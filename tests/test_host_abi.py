@@ -94,9 +94,9 @@ def test_split_planning_properties(lib):
         assert 1 <= s <= max(1, -(-n // 16))
         ws = L.cda_b200_decode_workspace_bytes(B, Hkv * 4, Hkv, n, 0, -1)
         heads_per_cta = max(h for h in (1, 2, 4, 8) if h <= Hkv and Hkv % h == 0)
-        parts = s * (8 // heads_per_cta)
+        parts = s * (16 // heads_per_cta)
         assert ws == 256 + parts * B * Hkv * 4 * 130 * 4
-        assert L.cda_b200_decode_workspace_bytes(B, Hkv * 4, Hkv, n, 3, -1) <= 256 + 3 * (8 // heads_per_cta) * B * Hkv * 4 * 520
+        assert L.cda_b200_decode_workspace_bytes(B, Hkv * 4, Hkv, n, 3, -1) <= 256 + 3 * (16 // heads_per_cta) * B * Hkv * 4 * 520
     assert L.cda_b200_decode_plan_splits(32, 8, 65536, -1) == 37      # 32 x 37 CTAs = 8 waves of 148 SMs
     assert L.cda_b200_decode_plan_splits(0, 8, 16, -1) == lib.CDA_ERR_BAD_ARG
 
