@@ -123,6 +123,25 @@ int cda_b200_decode_partial(const void* Q, const void* kv_cache, const int32_t* 
 int cda_b200_merge_partials(const float* O, const float* m, const float* l, int S, int64_t R, void* out,
                             int unrotate, void* stream);
 
+/* cda_b200_decode for callers that cannot hand over a workspace: the split-KV scratch is an 8 MiB array compiled into
+ * the library (file-scope device memory; every GPU that loads the library holds it until the process exits).  Meant for
+ * hosts where device allocation is off limits at call time -- a runtime whose memory pool is fixed at start-up and
+ * handed out in full, a plugin that may only touch the buffers it is given, code running while the allocator is
+ * locked.  The call itself allocates nothing (no cudaMalloc / cudaFree, no library that allocates): it clears the
+ * 256-byte status block with a stream-ordered memset and launches the same two kernels as cda_b200_decode.
+ *   num_splits   0 = planned count; whatever is asked, the count is lowered until the partials fit in 8 MiB.
+ *   returns      CDA_ERR_WORKSPACE (with the sizes in the message) when even an unsplit pass does not fit, i.e.
+ *                when B * H_q * 520 B * (16 / min(H_kv, 8)) + 256 exceeds 8 MiB.
+ * The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device current);
+ * make that first call outside any stream capture.  All calls share the one array and it keeps the previous call's
+ * contents: calls whose kernels may overlap on the GPU (different streams, or graphs replayed concurrently) race on
+ * it -- serialise them or use cda_b200_decode with separate workspaces.
+ * Has no counterpart in the reference (its decode kernel allocates its scratch on every call, wrappers.py:97-99). */
+int cda_b200_decode_static(const void* Q, const void* kv_cache, const int32_t* block_table, const int32_t* seq_lens,
+                           const float* cb_K, const float* cb_V, void* out, int B, int H_q, int H_kv, int block_size,
+                           int block_table_stride, int max_seq_len, int64_t num_slots, int slot_bytes, int k_bits,
+                           int v_bits, float scale, int num_splits, void* stream);
+
 /* Slow one-warp-per-query-head decode without tensor cores or splitting; decodes K/V exactly as
  * Compressor.decode does (cb[idx]*norm rounded to fp16).  A device-side cross-check, same arguments
  * and result as cda_b200_decode minus the workspace.  Contract: cda/algorithm/attention.py:426-482. */

@@ -813,6 +813,30 @@ static int run_split(const char* who, const DecodeCommon& a, void* workspace, si
   return CDA_OK;
 }
 
+// ---- split-KV scratch that lives inside the library (for cda_b200_decode_static) ------------------------------------
+// 8 MiB per GPU that loads the library, held until the process exits.  Same layout as the caller-owned workspace:
+// a 256-byte status block, then the (m, l) rows and the un-normalised O rows of every partial.
+constexpr size_t kStaticScratchBytes = size_t(8) << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// Device address of g_static_scratch on the CURRENT device.  In host code the symbol's name is only a handle, so the
+// address is asked from the runtime once per device (with that device current) and remembered.
+static int static_scratch_address(uint8_t** out) {
+  static uint8_t* cached[64];
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) return check_launch("decode_static: cudaGetDevice");
+  if (dev >= 0 && dev < 64 && cached[dev]) { *out = cached[dev]; return CDA_OK; }
+  void* ptr = nullptr;
+  const cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+  if (e != cudaSuccess || ptr == nullptr) {
+    cudaGetLastError();
+    return fail(CDA_ERR_LAUNCH, "decode_static: cudaGetSymbolAddress failed on device %d: %s", dev, cudaGetErrorString(e));
+  }
+  if (dev >= 0 && dev < 64) cached[dev] = static_cast<uint8_t*>(ptr);
+  *out = static_cast<uint8_t*>(ptr);
+  return CDA_OK;
+}
+
 }  // namespace cda
 
 using namespace cda;
@@ -905,4 +929,41 @@ extern "C" int cda_b200_decode_scalar(const void* Q, const void* kv_cache, const
   else
     decode_scalar_kernel<2, 4><<<grid, 32, 0, st>>>(q, c, block_table, seq_lens, cb_K, cb_V, o, H_q, H_kv, grp, block_size, block_table_stride, nb, slot_bytes, scale);
   return check_launch("decode_scalar");
+}
+
+extern "C" int cda_b200_decode_static(const void* Q, const void* kv_cache, const int32_t* block_table, const int32_t* seq_lens,
+                                      const float* cb_K, const float* cb_V, void* out, int B, int H_q, int H_kv, int block_size,
+                                      int block_table_stride, int max_seq_len, int64_t num_slots, int slot_bytes, int k_bits,
+                                      int v_bits, float scale, int num_splits, void* stream) {
+  const DecodeCommon a{Q, kv_cache, block_table, seq_lens, cb_K, cb_V, B, H_q, H_kv, block_size, block_table_stride,
+                       max_seq_len, num_slots, slot_bytes, k_bits, v_bits, scale};
+  int rc = validate("decode_static", a);
+  if (rc != CDA_OK || B == 0) return rc;
+  if (!out) return fail(CDA_ERR_BAD_ARG, "decode_static: null output");
+  if (reinterpret_cast<uintptr_t>(out) & 7u) return fail(CDA_ERR_BAD_ALIGN, "decode_static: output must be 8-byte aligned");
+  if (num_splits < 0) return fail(CDA_ERR_BAD_ARG, "decode_static: negative num_splits");
+  const int64_t rows = static_cast<int64_t>(B) * H_q;
+  if (rows > 0x7fffffffLL) return fail(CDA_ERR_N_TOO_LARGE, "decode_static: B*H_q too large");
+  // Pick the split count: the planned (or requested) one if its partials fit in the built-in scratch, otherwise the
+  // largest count that does.  If not even one split fits, the problem is too large for this entry point.
+  const int sms = device_sm_count(-1);
+  int splits = make_plan(B, H_kv, max_seq_len, num_splits, sms).splits;
+  while (splits > 1 && ws_bytes(make_plan(B, H_kv, max_seq_len, splits, sms), B, H_q) > kStaticScratchBytes) --splits;
+  const size_t need = ws_bytes(make_plan(B, H_kv, max_seq_len, splits, sms), B, H_q);
+  if (need > kStaticScratchBytes)
+    return fail(CDA_ERR_WORKSPACE, "decode_static: B=%d, H_q=%d needs %zu bytes of scratch even unsplit; the built-in scratch holds %zu "
+                "(use cda_b200_decode with a caller-owned workspace)", B, H_q, need, kStaticScratchBytes);
+  uint8_t* scratch = nullptr;
+  rc = static_scratch_address(&scratch);
+  if (rc != CDA_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // The array keeps whatever the previous call left.  Only the status block has to start at zero; every (m, l) row and
+  // every O row that the merge reads is rewritten by this call's split kernel first.
+  if (cudaMemsetAsync(scratch, 0, 256, st) != cudaSuccess) return check_launch("decode_static: clearing the status block");
+  Plan pl; float* ml; float* po;
+  rc = run_split("decode_static", a, scratch, kStaticScratchBytes, splits, st, &pl, &ml, &po);
+  if (rc != CDA_OK) return rc;
+  decode_merge_kernel<<<static_cast<unsigned>(rows), 256, 0, st>>>(po, ml, ml + 1, 2, pl.parts, rows, 1.0f, 0, 1,
+                                                                  static_cast<__half*>(out), nullptr, nullptr, nullptr);
+  return check_launch("decode_static merge kernel");
 }
