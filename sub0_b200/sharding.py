@@ -1,0 +1,69 @@
+"""Multi-GPU decode: one process per GPU (``torch.distributed``), two ways to split the work.
+
+* **KV-head sharding** (:func:`head_shard`): rank r owns a contiguous slice of KV heads and the query heads that read
+  them, with its own paged cache ``(slots, H_kv / W, slot_bytes)`` and the full block table.  Heads never interact
+  (the reference's tensor-parallel split, ``cda/kernels_cuda/vllm_integration/cda_attn_v2.py:636-640``), so the data
+  path has **no collective**; outputs stay head-sharded.
+* **Sequence sharding** (:func:`sequence_shard`, :func:`decode_sequence_sharded`): for one very long sequence, rank r
+  owns a contiguous, block-aligned range of keys of every head.  Each rank produces the un-normalised partial
+  ``(O, m, l)`` of its keys, one all-gather moves ``(B, H_q, 130)`` fp32 per rank, and every rank merges locally --
+  the path the reference leaves as ``NotImplementedError`` (``cda_attn_v2.py:1697-1701``) with the contract of
+  ``cda/algorithm/attention.py:190-272``.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+import torch.distributed as dist
+from torch import Tensor
+
+PARTIAL_WIDTH = 130          # 128 un-normalised outputs, then m (natural log domain), then l
+
+
+def head_shard(rank: int, world: int, H_kv: int) -> Tuple[int, int]:
+    """KV heads [lo, hi) of ``rank``.  ``H_kv`` must divide evenly (8 heads -> world in {1, 2, 4, 8})."""
+    if world <= 0 or not 0 <= rank < world:
+        raise ValueError(f"bad rank/world {rank}/{world}")
+    if H_kv % world:
+        raise ValueError(f"H_kv={H_kv} does not divide over {world} ranks")
+    per = H_kv // world
+    return rank * per, (rank + 1) * per
+
+
+def sequence_shard(rank: int, world: int, seq_len: int, block_size: int) -> Tuple[int, int]:
+    """Token range [lo, hi) of ``rank``: contiguous, starting on a block boundary, sizes differing by at most one
+    block; ranks past the end get an empty range."""
+    if world <= 0 or not 0 <= rank < world:
+        raise ValueError(f"bad rank/world {rank}/{world}")
+    if block_size <= 0 or block_size % 16:
+        raise ValueError("block_size must be a positive multiple of 16")
+    blocks = -(-seq_len // block_size)
+    base, extra = divmod(blocks, world)
+    lo_blk = rank * base + min(rank, extra)
+    hi_blk = lo_blk + base + (1 if rank < extra else 0)
+    return min(lo_blk * block_size, seq_len), min(hi_blk * block_size, seq_len)
+
+
+def gather_partials(packed: Tensor, group: Optional[dist.ProcessGroup] = None) -> Tensor:
+    """All-gather packed partials ``(..., 130)`` from every rank into ``(world, ..., 130)`` (one collective)."""
+    if packed.shape[-1] != PARTIAL_WIDTH:
+        raise ValueError(f"packed partials must end in {PARTIAL_WIDTH} columns")
+    packed = packed.contiguous()
+    world = dist.get_world_size(group)
+    flat = packed.reshape(-1)
+    out = torch.empty(world * flat.numel(), dtype=packed.dtype, device=packed.device)
+    dist.all_gather_into_tensor(out, flat, group=group)
+    return out.view((world,) + tuple(packed.shape))
+
+
+def decode_sequence_sharded(Q: Tensor, local_cache: Tensor, local_block_table: Tensor, local_seq_lens: Tensor,
+                            output: Tensor, *, cb_K: Tensor, cb_V: Tensor, block_size: int, local_max_seq_len: int,
+                            scale: Optional[float] = None, group: Optional[dist.ProcessGroup] = None,
+                            workspace: Optional[Tensor] = None) -> None:
+    """Decode one step when every rank holds a different key range of the same sequences.  ``Q`` (full, identical on
+    every rank) and ``output`` are (B, H_q, 128) fp16; ``local_*`` describe this rank's keys only."""
+    from . import ops
+    packed = ops.decode_partial(Q, local_cache, local_block_table, local_seq_lens, cb_K=cb_K, cb_V=cb_V,
+                                block_size=block_size, scale=scale, max_seq_len=local_max_seq_len, workspace=workspace)
+    ops.merge_partials(gather_partials(packed, group), output)
