@@ -115,7 +115,9 @@ __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
 // The tensor-core operands are fp16, the codebook is fp32.  Rounding each level to fp16 puts the SAME relative error
 // (up to 2^-12) on every occurrence of that level, which does not average out -- with only four levels it shifts all
 // scores or all values together.  Instead the tables hold fp16(level / alpha) and the result is multiplied by alpha in
-// fp32 (folded into the softmax scale for K, into the final normalisation for V).  alpha is searched in
+// fp32 (folded into the softmax scale for K, into the final normalisation for V).  This is done for 4-level tables
+// only: with 16 levels the individual errors largely cancel and a common alpha cannot shrink all of them anyway, so
+// those tables use alpha = 1 and pay no set-up time.  alpha is searched in
 // [1, 1.0625) with step 2^-13 for the value whose worst-case |alpha * fp16(level / alpha) - level| is smallest; alpha = 1
 // is a candidate, so the result is never worse than plain rounding.
 constexpr int kScaleCandidates = 512;
@@ -127,6 +129,7 @@ __device__ __forceinline__ float table_value(float level, float inv_alpha) { ret
 template <int LA, int LB>
 __device__ __forceinline__ void find_table_scales(const float* __restrict__ cb_a, const float* __restrict__ cb_b, float* s_err, int* s_idx,
                                                   float& alpha_a, float& alpha_b) {
+  if (LA != 4 && LB != 4) { alpha_a = 1.0f; alpha_b = 1.0f; return; }
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
   float la[LA], lb[LB];
 #pragma unroll
@@ -138,10 +141,14 @@ __device__ __forceinline__ void find_table_scales(const float* __restrict__ cb_a
   for (int cand = tid; cand < kScaleCandidates; cand += blockDim.x) {
     const float alpha = 1.0f + cand * (1.0f / 8192.0f), inv = 1.0f / alpha;
     float ea = 0.f, eb = 0.f;
+    if (LA == 4) {
 #pragma unroll
-    for (int i = 0; i < LA; ++i) ea = fmaxf(ea, fabsf(fmaf(alpha, table_value(la[i], inv), -la[i])));
+      for (int i = 0; i < LA; ++i) ea = fmaxf(ea, fabsf(fmaf(alpha, table_value(la[i], inv), -la[i])));
+    }
+    if (LB == 4) {
 #pragma unroll
-    for (int i = 0; i < LB; ++i) eb = fmaxf(eb, fabsf(fmaf(alpha, table_value(lb[i], inv), -lb[i])));
+      for (int i = 0; i < LB; ++i) eb = fmaxf(eb, fabsf(fmaf(alpha, table_value(lb[i], inv), -lb[i])));
+    }
     if (ea < best[0]) { best[0] = ea; arg[0] = cand; }
     if (eb < best[1]) { best[1] = eb; arg[1] = cand; }
   }
@@ -167,8 +174,8 @@ __device__ __forceinline__ void find_table_scales(const float* __restrict__ cb_a
     win[t] = i;
   }
   __syncthreads();
-  alpha_a = 1.0f + win[0] * (1.0f / 8192.0f);
-  alpha_b = 1.0f + win[1] * (1.0f / 8192.0f);
+  alpha_a = LA == 4 ? 1.0f + win[0] * (1.0f / 8192.0f) : 1.0f;
+  alpha_b = LB == 4 ? 1.0f + win[1] * (1.0f / 8192.0f) : 1.0f;
 }
 
 // ---- codebook look-up tables in shared memory ----------------------------------------------------
