@@ -64,21 +64,16 @@ struct Geom {
   static constexpr int kSlotBytes = kChunks * 16;
   static constexpr int kGroupChunks = 16 * kChunks;
   static constexpr int kIssueIters = (kGroupChunks + 31) / 32;
-  static constexpr int kKRegion = 16 * kKBytes;
-  static constexpr int kVRegion = 16 * kVBytes;
-  static constexpr int kNOffset = kKRegion + kVRegion;
-  static constexpr int kStageBytes = kNOffset + 256;
+  // A ring stage keeps every slot whole in a 160-byte cell, cells in token order: a copy instruction then writes an
+  // almost contiguous run of shared memory (scattered 16-byte destinations cost one shared-memory cycle each).
+  // 160 = 32 (mod 128), and accumulator row r is fed by token perm(r) = 0,2,1,3,6,4,7,5: with that pairing the K
+  // reads of two rows and the V reads of four rows always fall into different banks.
+  static constexpr int kCell = 160;
+  static constexpr int kStageBytes = 16 * kCell;
+  static_assert(kSlotBytes <= kCell, "slot does not fit its cell");
 };
 
-// Shared-memory placement of 16-byte piece `k` of row `rho` inside the V region of a stage.
-template <int VB>
-__device__ __forceinline__ int v_piece_offset(int rho, int k) {
-  if (VB == 4) {   // 64-byte rows; rows {0,2,4,6} (and {1,3,5,7}) must land in four different 32-byte bank groups
-    return ((rho & 3) | ((rho >> 3) << 2)) * 128 + ((rho >> 2) & 1) * 64 + ((k ^ (((rho >> 1) & 1) << 1)) * 16);
-  } else {         // 32-byte rows
-    return ((rho & 1) | ((rho >> 3) << 1)) * 128 + ((rho >> 1) & 3) * 32 + k * 16;
-  }
-}
+__device__ __forceinline__ int stage_perm(int row) { return (0xBE6650u >> (3 * (row & 7))) & 7; }   // 0,2,1,3,6,4,7,5
 
 // ---- shared-memory access by 32-bit window address ---------------------------------------------------------------
 __device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {   // table reads: the table never changes after the barrier
@@ -199,11 +194,12 @@ struct WarpCtx {
   uint32_t dst_addr[Gm::kIssueIters];    // window address of this lane's pieces in stage 0
   int src_off[Gm::kIssueIters];
   bool last_valid;                        // whether the lane takes part in the last copy iteration
-  uint32_t k_addr, v_addr, n_addr;        // window addresses of this lane's fragment pieces in stage 0
+  uint32_t k_addr, v_addr, v_addr_b, n_addr;   // window addresses of this lane's fragment pieces in stage 0 (V: rows 2c, 2c+1)
   const uint8_t* cache_head;
   const int32_t* bt_row;
   int row_stride, block_size, num_blocks, gpb, gpb_shift;
   int g_begin_sub, R, ng, t_end, r;
+  int tok_r;                              // position inside the group of the token that feeds accumulator row r
   int blk_q;                              // block id of the next group to be issued
   float scale_log2;
   int* status;
@@ -235,30 +231,35 @@ struct WarpCtx {
 
   template <int S, bool MASKED>
   __device__ __forceinline__ void consume(int j) {
-    constexpr int O = S * Gm::kStageBytes;
+    constexpr int O = S * Gm::kStageBytes, H = 8 * Gm::kCell;   // rows rho + 8 sit 8 cells further
     GroupRegs<KB, VB> gr;
     if (KB == 4) {
-      const uint4 t0 = lds_stage16<O>(k_addr), t1 = lds_stage16<O + 8 * Gm::kKBytes>(k_addr);
+      const uint4 t0 = lds_stage16<O>(k_addr), t1 = lds_stage16<O + H>(k_addr);
       gr.k[0][0] = t0.x; gr.k[0][1] = t0.y; gr.k[0][KB - 2] = t0.z; gr.k[0][KB - 1] = t0.w;
       gr.k[1][0] = t1.x; gr.k[1][1] = t1.y; gr.k[1][KB - 2] = t1.z; gr.k[1][KB - 1] = t1.w;
     } else {
-      const uint2 t0 = lds_stage8<O>(k_addr), t1 = lds_stage8<O + 8 * Gm::kKBytes>(k_addr);
+      const uint2 t0 = lds_stage8<O>(k_addr), t1 = lds_stage8<O + H>(k_addr);
       gr.k[0][0] = t0.x; gr.k[0][1] = t0.y; gr.k[1][0] = t1.x; gr.k[1][1] = t1.y;
     }
-    const uint2 n0 = lds_stage8<O>(n_addr), n1 = lds_stage8<O + 128>(n_addr);
+    const uint2 n0 = lds_stage8<O>(n_addr), n1 = lds_stage8<O + H>(n_addr);
     gr.n[0] = make_float2(__uint_as_float(n0.x), __uint_as_float(n0.y));
     gr.n[1] = make_float2(__uint_as_float(n1.x), __uint_as_float(n1.y));
-    constexpr int kRow8 = VB == 4 ? 512 : 256;   // rows rho + 8 sit this many bytes further in the V region
     if (VB == 4) {
-      const uint2 a = lds_stage8<O>(v_addr), b = lds_stage8<O + 128>(v_addr);
-      const uint2 c2 = lds_stage8<O + kRow8>(v_addr), d = lds_stage8<O + kRow8 + 128>(v_addr);
+      const uint2 a = lds_stage8<O>(v_addr), b = lds_stage8<O>(v_addr_b);
+      const uint2 c2 = lds_stage8<O + H>(v_addr), d = lds_stage8<O + H>(v_addr_b);
       gr.v[0][0] = a.x; gr.v[0][VB / 2 - 1] = a.y; gr.v[1][0] = b.x; gr.v[1][VB / 2 - 1] = b.y;
       gr.v[2][0] = c2.x; gr.v[2][VB / 2 - 1] = c2.y; gr.v[3][0] = d.x; gr.v[3][VB / 2 - 1] = d.y;
     } else {
-      gr.v[0][0] = lds_stage4<O>(v_addr); gr.v[1][0] = lds_stage4<O + 128>(v_addr);
-      gr.v[2][0] = lds_stage4<O + kRow8>(v_addr); gr.v[3][0] = lds_stage4<O + kRow8 + 128>(v_addr);
+      gr.v[0][0] = lds_stage4<O>(v_addr); gr.v[1][0] = lds_stage4<O>(v_addr_b);
+      gr.v[2][0] = lds_stage4<O + H>(v_addr); gr.v[3][0] = lds_stage4<O + H>(v_addr_b);
     }
 
+    attend<MASKED>(gr, j);
+  }
+
+  // Scores, online softmax and P V for one 16-token group held in registers.
+  template <bool MASKED>
+  __device__ __forceinline__ void attend(const GroupRegs<KB, VB>& gr, int j) {
     float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
     {
       uint32_t ka[8][4];
@@ -275,7 +276,7 @@ struct WarpCtx {
     float nv0 = gr.n[0].y, nv1 = gr.n[1].y;
     if (MASKED) {   // ragged tail: rows past the end contribute nothing, whatever bytes they hold
       const int tok0 = (g_begin_sub + R * j) << 4;
-      const bool ok0 = tok0 + r < t_end, ok1 = tok0 + r + 8 < t_end;
+      const bool ok0 = tok0 + tok_r < t_end, ok1 = tok0 + tok_r + 8 < t_end;
       s0 = ok0 ? s0 : -INFINITY; s1 = ok0 ? s1 : -INFINITY; s2 = ok1 ? s2 : -INFINITY; s3 = ok1 ? s3 : -INFINITY;
       nv0 = ok0 ? nv0 : 0.f; nv1 = ok1 ? nv1 : 0.f;
     }
@@ -461,21 +462,19 @@ __global__ void __launch_bounds__(W * 32, 1) decode_split_kernel(const DecodePar
     if (ch >= Gm::kGroupChunks) ch = Gm::kGroupChunks - 1;
     const int rho = ch / Gm::kChunks, piece = ch - rho * Gm::kChunks;
     cx.src_off[it] = rho * cx.row_stride + piece * 16;
-    int d;
-    if (piece < KB) d = rho * Gm::kKBytes + piece * 16;
-    else if (piece < KB + VB) d = Gm::kKRegion + v_piece_offset<VB>(rho, piece - KB);
-    else d = Gm::kNOffset + rho * 16;
+    const int d = rho * Gm::kCell + piece * 16;
     cx.dst_addr[it] = ring + d;
   }
   cx.last_valid = (Gm::kIssueIters - 1) * 32 + lane < Gm::kGroupChunks;
-  cx.k_addr = ring + r * Gm::kKBytes + c * (4 * KB);
-  cx.v_addr = ring + Gm::kKRegion + (VB == 4 ? v_piece_offset<4>(2 * c, r >> 1) + 8 * (r & 1) : v_piece_offset<2>(2 * c, r >> 2) + 4 * (r & 3));
-  cx.n_addr = ring + Gm::kNOffset + r * 16;
+  cx.k_addr = ring + stage_perm(r) * Gm::kCell + c * (4 * KB);
+  cx.v_addr = ring + stage_perm(2 * c) * Gm::kCell + 16 * KB + r * (2 * VB);
+  cx.v_addr_b = ring + stage_perm(2 * c + 1) * Gm::kCell + 16 * KB + r * (2 * VB);
+  cx.n_addr = ring + stage_perm(r) * Gm::kCell + 16 * KB + 16 * VB;
   cx.cache_head = p.cache + static_cast<int64_t>(head) * Gm::kSlotBytes;
   cx.bt_row = p.block_table + static_cast<int64_t>(b) * p.bt_stride;
   cx.block_size = p.block_size; cx.num_blocks = p.num_blocks;
   cx.gpb = p.block_size >> 4; cx.gpb_shift = p.gpb_shift;
-  cx.g_begin_sub = (t_begin >> 4) + sub; cx.R = R; cx.ng = ng; cx.t_end = t_end; cx.r = r;
+  cx.g_begin_sub = (t_begin >> 4) + sub; cx.R = R; cx.ng = ng; cx.t_end = t_end; cx.r = r; cx.tok_r = stage_perm(r);
   cx.scale_log2 = p.scale_log2 * alpha_k; cx.status = p.status; cx.debug = p.debug;
   cx.m_run[0] = cx.m_run[1] = kMinusBig;
   cx.l_run[0] = cx.l_run[1] = 0.f;
@@ -509,6 +508,282 @@ __global__ void __launch_bounds__(W * 32, 1) decode_split_kernel(const DecodePar
     for (int t = 0; t < NT; ++t)
 #pragma unroll
       for (int i = 0; i < 4; ++i) cx.oacc[u][t][i] *= alpha_v;   // the V table holds level / alpha_v
+  if (G == 4) {
+    const int parity = c >> 1, q0 = 2 * (c & 1);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int d = 16 * r + 4 * u + parity;
+      if (q0 < g) { p.part_o[(prow0 + q0) * kHeadDim + d] = cx.oacc[u][0][0]; p.part_o[(prow0 + q0) * kHeadDim + d + 2] = cx.oacc[u][0][2]; }
+      if (q0 + 1 < g) { p.part_o[(prow0 + q0 + 1) * kHeadDim + d] = cx.oacc[u][0][1]; p.part_o[(prow0 + q0 + 1) * kHeadDim + d + 2] = cx.oacc[u][0][3]; }
+    }
+    if (r == 0 && c < 2) {
+      if (q0 < g) *reinterpret_cast<float2*>(p.part_ml + (prow0 + q0) * 2) = make_float2(m0, l0);
+      if (q0 + 1 < g) *reinterpret_cast<float2*>(p.part_ml + (prow0 + q0 + 1) * 2) = make_float2(m1, l1);
+    }
+  } else {
+    const int q0 = 2 * c;
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+#pragma unroll
+      for (int t = 0; t < NT; ++t) {
+        const int d = 16 * r + 4 * u + t;
+        if (q0 < g) { p.part_o[(prow0 + q0) * kHeadDim + d] = cx.oacc[u][t][0]; p.part_o[(prow0 + q0) * kHeadDim + d + 2] = cx.oacc[u][t][2]; }
+        if (q0 + 1 < g) { p.part_o[(prow0 + q0 + 1) * kHeadDim + d] = cx.oacc[u][t][1]; p.part_o[(prow0 + q0 + 1) * kHeadDim + d + 2] = cx.oacc[u][t][3]; }
+      }
+    if (r == 0) {
+      if (q0 < g) *reinterpret_cast<float2*>(p.part_ml + (prow0 + q0) * 2) = make_float2(m0, l0);
+      if (q0 + 1 < g) *reinterpret_cast<float2*>(p.part_ml + (prow0 + q0 + 1) * 2) = make_float2(m1, l1);
+    }
+  }
+}
+
+// ---- page-pipeline variant of the split kernel -----------------------------------------------------------------------
+// Same arithmetic (WarpCtx::attend), different data movement.  The HPC warps that share a key sub-range form a
+// pipeline: a stage holds one whole 16-token group of all their heads, brought in by 16 bulk copies (one per token:
+// HPC * slot bytes, contiguous in the cache) that complete on an mbarrier.  The copy engine does the address work, so
+// the warps spend no instructions and no load/store-unit time on it.  Token rows are spaced RS bytes apart in shared
+// memory with RS = 32 (mod 128), and accumulator row r is fed by token perm(r) = 0,2,1,3,6,4,7,5: with that pairing the
+// K reads of two rows and the V reads of four rows always fall into different banks.  The warp that finishes a stage
+// last (shared-memory counter) starts the copies of the group NS ahead into it; nobody ever waits for a consumer.
+template <int HPC, int SLOT>
+struct PageGeom {
+  static constexpr int kRowBytes = HPC * SLOT;                                  // bytes copied per token
+  static constexpr int kRS = (kRowBytes - 32 + 127) / 128 * 128 + 32;           // row stride in shared memory
+  static constexpr int kStage = 16 * kRS;
+};
+
+__device__ __forceinline__ int page_perm(int row) { return (0xBE6650u >> (3 * (row & 7))) & 7; }   // 0,2,1,3,6,4,7,5
+
+template <int G, int KB, int VB, int W, int NS, int HPC>
+__global__ void __launch_bounds__(W * 32, 1) decode_page_kernel(const DecodeParams p) {
+  using Gm = Geom<KB, VB>;
+  using Pg = PageGeom<HPC, Gm::kSlotBytes>;
+  constexpr int NT = G / 4;
+  constexpr int R = W / HPC;                    // pipelines (key sub-ranges) per CTA
+  constexpr int kRing = NS * Pg::kStage;        // bytes per pipeline
+  static_assert(kRing >= HPC * 8 * kHeadDim * 2, "pipeline ring too small to stage the query rows");
+  extern __shared__ __align__(128) uint8_t smem[];
+  __shared__ __align__(8) uint64_t s_full[R * NS];
+  __shared__ int s_cnt[R * NS];
+  __shared__ float s_err[64];
+  __shared__ int s_idx[64];
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int r = lane >> 2, c = lane & 3;
+  const int split = blockIdx.x, b = blockIdx.y, hg = blockIdx.z;
+  const int hic = warp % HPC;                   // head inside the CTA
+  const int head = hg * HPC + hic;
+  const int sub = warp / HPC;
+  const int g = p.group;
+
+  const int seq_len = p.seq_lens[b];
+  const int t_begin = split * p.tokens_per_split;
+  const int t_end = min(seq_len, t_begin + p.tokens_per_split);
+  const int cta_groups = t_end > t_begin ? (t_end - t_begin + 15) >> 4 : 0;
+  const int ng = cta_groups > sub ? (cta_groups - sub + R - 1) / R : 0;
+
+  const int part = split * R + sub;
+  const int64_t prow0 = (static_cast<int64_t>(part) * p.B + b) * p.H_q + head * g;
+
+  const uint32_t win0 = smem_addr(smem);
+  const uint32_t lut_win = (win0 + kLutWindow - 1) & ~static_cast<uint32_t>(kLutWindow - 1);
+  const int rings_before = static_cast<int>((lut_win - win0) / kRing);
+  const int rings_after = R > rings_before ? R - rings_before : 0;
+  const uint32_t win_end = lut_win + kLutWindow + rings_after * kRing;
+  const bool fits = win_end - win0 <= static_cast<uint32_t>(p.smem_bytes);
+  if (cta_groups == 0 || !fits) {
+    if (!fits && tid == 0) atomicOr(p.status, 2);
+    if (lane < g) *reinterpret_cast<float2*>(p.part_ml + (prow0 + lane) * 2) = make_float2(-INFINITY, 0.f);
+    return;
+  }
+  const uint32_t ring = sub < rings_before ? win0 + sub * kRing : lut_win + kLutWindow + (sub - rings_before) * kRing;
+  uint8_t* lut = smem + (lut_win - win0);
+
+  float alpha_k, alpha_v;
+  find_table_scales<(KB == 4 ? 16 : 4), (VB == 4 ? 16 : 4)>(p.cb_k, p.cb_v, s_err, s_idx, alpha_k, alpha_v);
+  {
+    constexpr int EK = KB == 4 ? 256 : 16, EV = VB == 4 ? 256 : 16, LK = KB == 4 ? 16 : 4, LV = VB == 4 ? 16 : 4;
+    const float inv_k = 1.0f / alpha_k, inv_v = 1.0f / alpha_v;
+    uint32_t* lw = reinterpret_cast<uint32_t*>(lut);
+    for (int e = warp; e < (EK > EV ? EK : EV); e += W) {
+      if (e < EK) {
+        const int first = KB == 4 ? (e >> 4) : (e >> 2), second = KB == 4 ? (e & 15) : (e & 3);
+        lw[e * 64 + lane] = pack_half2(__ldg(p.cb_k + (first & (LK - 1))) * inv_k, __ldg(p.cb_k + (second & (LK - 1))) * inv_k);
+      }
+      if (e < EV) {
+        const int first = VB == 4 ? (e >> 4) : (e >> 2), second = VB == 4 ? (e & 15) : (e & 3);
+        lw[e * 64 + 32 + lane] = pack_half2(__ldg(p.cb_v + (first & (LV - 1))) * inv_v, __ldg(p.cb_v + (second & (LV - 1))) * inv_v);
+      }
+    }
+  }
+
+  WarpCtx<G, KB, VB, NS> cx;
+  {
+    __half* q_rows = reinterpret_cast<__half*>(smem + (ring - win0)) + hic * 8 * kHeadDim;
+    for (int qi = 0; qi < 8; ++qi) {
+      float v[4] = {0.f, 0.f, 0.f, 0.f};
+      if (qi < g) {
+        load_half4(p.q + (static_cast<int64_t>(b) * p.H_q + head * g + qi) * kHeadDim + 4 * lane, v);
+        fht128_warp(v, lane);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v[i] *= kRsqrtD;
+      }
+      *reinterpret_cast<uint2*>(q_rows + qi * kHeadDim + 4 * lane) = pack_half4(v);
+    }
+    __syncwarp();
+    const int qrow = G == 4 ? (r & 3) : r;
+    const uint4* src = reinterpret_cast<const uint4*>(q_rows + qrow * kHeadDim + 32 * c);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint4 t = src[i];
+      cx.qf[4 * i] = t.x; cx.qf[4 * i + 1] = t.y; cx.qf[4 * i + 2] = t.z; cx.qf[4 * i + 3] = t.w;
+    }
+  }
+  const uint32_t bars = smem_addr(&s_full[sub * NS]);
+  if (hic == 0 && lane < NS) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bars + 8 * lane) : "memory");
+    s_cnt[sub * NS + lane] = 0;
+  }
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the query rows were ordinary stores; bulk copies reuse the space
+  __syncthreads();
+
+  cx.base_k = lut_win | (lane << 2);
+  cx.base_v = cx.base_k | 128u;
+  {
+    const bool odd = G == 4 && (r >> 2) != 0;
+    cx.sel_b0 = odd ? 0x1044u : 0x4410u;
+    cx.sel_b1 = odd ? 0x3244u : 0x4432u;
+  }
+  const int row_stride = p.H_kv * Gm::kSlotBytes;
+  const int gpb = p.block_size >> 4;
+  const int32_t* bt_row = p.block_table + static_cast<int64_t>(b) * p.bt_stride;
+  const int g_begin_sub = (t_begin >> 4) + sub;
+  cx.g_begin_sub = g_begin_sub; cx.R = R; cx.ng = ng; cx.t_end = t_end; cx.r = r; cx.tok_r = page_perm(r);
+  cx.scale_log2 = p.scale_log2 * alpha_k; cx.status = p.status; cx.debug = p.debug;
+  cx.m_run[0] = cx.m_run[1] = kMinusBig;
+  cx.l_run[0] = cx.l_run[1] = 0.f;
+#pragma unroll
+  for (int u = 0; u < 4; ++u)
+#pragma unroll
+    for (int t = 0; t < NT; ++t)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) cx.oacc[u][t][i] = 0.f;
+
+  // window addresses of this lane's pieces in stage 0 (rows +8 and later stages are compile-time offsets)
+  const uint32_t head_base = ring + hic * Gm::kSlotBytes;
+  const uint32_t k_addr = head_base + page_perm(r) * Pg::kRS + c * (4 * KB);
+  const uint32_t n_addr = head_base + page_perm(r) * Pg::kRS + 16 * KB + 16 * VB;
+  const uint32_t va_addr = head_base + page_perm(2 * c) * Pg::kRS + 16 * KB + r * (2 * VB);
+  const uint32_t vb_addr = head_base + page_perm(2 * c + 1) * Pg::kRS + 16 * KB + r * (2 * VB);
+  const uint8_t* cache_rows = p.cache + static_cast<int64_t>(hg) * HPC * Gm::kSlotBytes;   // first head of this CTA inside a slot row
+
+  auto block_of = [&](int j) -> int {      // block id of this pipeline's group j (clamped index; range-checked)
+    const int jj = j < ng ? j : ng - 1;
+    const int gidx = g_begin_sub + R * jj;
+    int blk = __ldg(bt_row + (p.gpb_shift >= 0 ? gidx >> p.gpb_shift : gidx / gpb));
+    if (static_cast<unsigned>(blk) >= static_cast<unsigned>(p.num_blocks)) { atomicOr(p.status, 1); blk = 0; }
+    return blk;
+  };
+  // Start the 16 row copies of group j into stage s (whole warp calls; lanes 0..15 copy).
+  auto refill = [&](int j, int s, int blk) {
+    const int gidx = g_begin_sub + R * j;
+    const int rem = p.gpb_shift >= 0 ? gidx & (gpb - 1) : gidx % gpb;
+    const int64_t slot0 = static_cast<int64_t>(blk) * p.block_size + (rem << 4);
+    const uint8_t* src = cache_rows + (slot0 + (lane & 15)) * row_stride;
+    const uint32_t bar = bars + 8 * s;
+    if (lane == 0) {
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "n"(16 * Pg::kRowBytes) : "memory");
+    }
+    __syncwarp();
+    if (lane < 16)
+      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                   ::"r"(ring + s * Pg::kStage + (lane & 15) * Pg::kRS), "l"(src), "n"(Pg::kRowBytes), "r"(bar) : "memory");
+  };
+
+  if (ng > 0) {
+    const bool tail_masked = ((t_end - t_begin) & 15) != 0 && (cta_groups - 1) % R == sub;
+    if (hic == 0) {
+#pragma unroll 1
+      for (int s = 0; s < NS; ++s)
+        if (s < ng) refill(s, s, block_of(s));
+    }
+    bool alive = true;
+#pragma unroll 1
+    for (int j0 = 0; j0 < ng && alive; j0 += NS) {
+      const uint32_t phase = (j0 / NS) & 1;
+#pragma unroll
+      for (int s = 0; s < NS; ++s) {
+        const int j = j0 + s;
+        if (j < ng && alive) {
+          const int blk_next = block_of(j + NS);      // needed only if this warp turns out to be the last one on the stage
+          {   // bounded poll of the stage barrier; a lost copy sets status bit 2 instead of hanging
+            uint32_t done = 0;
+            for (int spin = 0; spin < (1 << 24) && !done; ++spin)
+              asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                           : "=r"(done) : "r"(bars + 8 * s), "r"(phase) : "memory");
+            if (!done) { atomicOr(p.status, 4); alive = false; }
+          }
+          GroupRegs<KB, VB> gr;
+          {
+            const uint32_t so = s * Pg::kStage;       // s is a compile-time constant after unrolling
+            constexpr int H = 8 * Pg::kRS;
+            if (KB == 4) {
+              uint4 t0, t1;
+              asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(t0.x), "=r"(t0.y), "=r"(t0.z), "=r"(t0.w) : "r"(k_addr + so) : "memory");
+              asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(t1.x), "=r"(t1.y), "=r"(t1.z), "=r"(t1.w) : "r"(k_addr + so + H) : "memory");
+              gr.k[0][0] = t0.x; gr.k[0][1] = t0.y; gr.k[0][KB - 2] = t0.z; gr.k[0][KB - 1] = t0.w;
+              gr.k[1][0] = t1.x; gr.k[1][1] = t1.y; gr.k[1][KB - 2] = t1.z; gr.k[1][KB - 1] = t1.w;
+            } else {
+              const uint2 t0 = lds_stage8<0>(k_addr + so), t1 = lds_stage8<0>(k_addr + so + H);
+              gr.k[0][0] = t0.x; gr.k[0][1] = t0.y; gr.k[1][0] = t1.x; gr.k[1][1] = t1.y;
+            }
+            const uint2 n0 = lds_stage8<0>(n_addr + so), n1 = lds_stage8<0>(n_addr + so + H);
+            gr.n[0] = make_float2(__uint_as_float(n0.x), __uint_as_float(n0.y));
+            gr.n[1] = make_float2(__uint_as_float(n1.x), __uint_as_float(n1.y));
+            if (VB == 4) {
+              const uint2 a = lds_stage8<0>(va_addr + so), bb = lds_stage8<0>(vb_addr + so);
+              const uint2 c2 = lds_stage8<0>(va_addr + so + H), d = lds_stage8<0>(vb_addr + so + H);
+              gr.v[0][0] = a.x; gr.v[0][VB / 2 - 1] = a.y; gr.v[1][0] = bb.x; gr.v[1][VB / 2 - 1] = bb.y;
+              gr.v[2][0] = c2.x; gr.v[2][VB / 2 - 1] = c2.y; gr.v[3][0] = d.x; gr.v[3][VB / 2 - 1] = d.y;
+            } else {
+              gr.v[0][0] = lds_stage4<0>(va_addr + so); gr.v[1][0] = lds_stage4<0>(vb_addr + so);
+              gr.v[2][0] = lds_stage4<0>(va_addr + so + H); gr.v[3][0] = lds_stage4<0>(vb_addr + so + H);
+            }
+          }
+          if (p.debug & 8) cx.oacc[0][0][0] += __uint_as_float((gr.k[0][0] ^ gr.k[1][KB - 1] ^ gr.v[0][0] ^ gr.v[3][0] ^ __float_as_uint(gr.n[0].x)) & 0xff);
+          else if (tail_masked && j == ng - 1) cx.template attend<true>(gr, j);
+          else cx.template attend<false>(gr, j);
+          // hand the stage back: the last of the HPC warps starts the copies of group j + NS into it
+          __syncwarp();
+          int last = 0;
+          if (lane == 0) {
+            __threadfence_block();
+            last = atomicAdd(&s_cnt[sub * NS + s], 1) == HPC - 1;
+            if (last) s_cnt[sub * NS + s] = 0;
+          }
+          last = __shfl_sync(0xffffffffu, last, 0);
+          if (last && j + NS < ng) refill(j + NS, s, blk_next);
+        }
+      }
+    }
+  }
+
+  // ---- write this warp's partial -------------------------------------------------------------------------------------------
+  float l0 = cx.l_run[0], l1 = cx.l_run[1];
+#pragma unroll
+  for (int mask = 4; mask < 32; mask <<= 1) {
+    l0 += __shfl_xor_sync(0xffffffffu, l0, mask);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, mask);
+  }
+  const float m0 = l0 > 0.f ? cx.m_run[0] : -INFINITY, m1 = l1 > 0.f ? cx.m_run[1] : -INFINITY;
+#pragma unroll
+  for (int u = 0; u < 4; ++u)
+#pragma unroll
+    for (int t = 0; t < NT; ++t)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) cx.oacc[u][t][i] *= alpha_v;
   if (G == 4) {
     const int parity = c >> 1, q0 = 2 * (c & 1);
 #pragma unroll
@@ -773,8 +1048,41 @@ static int dispatch_shape(const DecodeParams& p, const Plan& pl, cudaStream_t st
   return pl.depth == 6 ? launch_split<G, KB, VB, 8, 6>(p, pl, st) : launch_split<G, KB, VB, 8, 4>(p, pl, st);
 }
 
+template <int G, int KB, int VB, int HPC>
+static int launch_page(const DecodeParams& p0, const Plan& pl, cudaStream_t st) {
+  constexpr int W = 16, NS = 3;
+  static bool configured[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    if (cudaFuncSetAttribute(decode_page_kernel<G, KB, VB, W, NS, HPC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             kMaxDynamicSmem) != cudaSuccess)
+      return check_launch("decode: shared memory opt-in");
+    if (dev >= 0 && dev < 64) configured[dev] = true;
+  }
+  DecodeParams p = p0;
+  p.smem_bytes = kMaxDynamicSmem;
+  static const int dbg = getenv("CDA_DECODE_DEBUG") ? atoi(getenv("CDA_DECODE_DEBUG")) : 0;
+  p.debug = dbg;
+  const dim3 grid(pl.splits, p.B, pl.head_groups);
+  decode_page_kernel<G, KB, VB, W, NS, HPC><<<grid, W * 32, kMaxDynamicSmem, st>>>(p);
+  return check_launch("decode page kernel");
+}
+
+template <int G, int KB, int VB>
+static int dispatch_page(const DecodeParams& p, const Plan& pl, cudaStream_t st) {
+  switch (pl.heads_per_cta) {
+    case 8: return launch_page<G, KB, VB, 8>(p, pl, st);
+    case 4: return launch_page<G, KB, VB, 4>(p, pl, st);
+    case 2: return launch_page<G, KB, VB, 2>(p, pl, st);
+    default: return launch_page<G, KB, VB, 1>(p, pl, st);
+  }
+}
+
 template <int G>
 static int dispatch_bits(const DecodeParams& p, const Plan& pl, int kb, int vb, cudaStream_t st) {
+  static const bool page = getenv("CDA_DECODE_PAGE") && atoi(getenv("CDA_DECODE_PAGE")) == 1;
+  if (page && pl.warps == 16 && kb == 4 && vb == 4) return dispatch_page<G, 4, 4>(p, pl, st);
   if (kb == 4 && vb == 4) return dispatch_shape<G, 4, 4>(p, pl, st);
   if (kb == 4 && vb == 2) return dispatch_shape<G, 4, 2>(p, pl, st);
   if (kb == 2 && vb == 2) return dispatch_shape<G, 2, 2>(p, pl, st);
