@@ -52,7 +52,6 @@ struct DecodeParams {
   int gpb_shift;          // log2(block_size / 16), or -1 when block_size / 16 is not a power of two
   int tokens_per_split;   // multiple of 16
   int smem_bytes;         // dynamic shared memory given to the kernel
-  int debug;              // timing experiments only (results become wrong): 1 no copies after the prologue, 2 no PV, 4 no QK
   float scale_log2;       // softmax scale * log2(e)
 };
 
@@ -198,12 +197,12 @@ struct WarpCtx {
   const uint8_t* cache_head;
   const int32_t* bt_row;
   int row_stride, block_size, num_blocks, gpb, gpb_shift;
+  uint32_t block_bytes, group_bytes;      // bytes of one cache block / of 16 consecutive slots (all heads)
   int g_begin_sub, R, ng, t_end, r;
   int tok_r;                              // position inside the group of the token that feeds accumulator row r
   int blk_q;                              // block id of the next group to be issued
+  bool bad_block;                         // a block id was out of range (block 0 was read instead)
   float scale_log2;
-  int* status;
-  int debug;
 
   __device__ __forceinline__ int block_index(int gidx) const { return gpb_shift >= 0 ? gidx >> gpb_shift : gidx / gpb; }
   __device__ __forceinline__ int block_rem(int gidx) const { return gpb_shift >= 0 ? gidx & (gpb - 1) : gidx % gpb; }
@@ -216,11 +215,12 @@ struct WarpCtx {
   template <int S>
   __device__ __forceinline__ void issue(int j) {
     if (j < ng) {
-      int blk = blk_q;
-      if (static_cast<unsigned>(blk) >= static_cast<unsigned>(num_blocks)) { atomicOr(status, 1); blk = 0; }
-      const int gidx = g_begin_sub + R * j;
-      const int64_t slot0 = static_cast<int64_t>(blk) * block_size + (block_rem(gidx) << 4);
-      const uint8_t* base = cache_head + slot0 * row_stride;
+      uint32_t blk = static_cast<uint32_t>(blk_q);
+      const bool bad = blk >= static_cast<uint32_t>(num_blocks);   // reported once, when the warp is done
+      bad_block |= bad;
+      blk = bad ? 0u : blk;
+      const uint8_t* base = cache_head + static_cast<uint64_t>(blk) * block_bytes;
+      if (gpb > 1) base += static_cast<uint32_t>(block_rem(g_begin_sub + R * j)) * group_bytes;
 #pragma unroll
       for (int it = 0; it < Gm::kIssueIters; ++it)
         if (it + 1 < Gm::kIssueIters || last_valid) cp_async16_imm<S * Gm::kStageBytes>(dst_addr[it], base + src_off[it]);
@@ -263,12 +263,10 @@ struct WarpCtx {
     float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
     {
       uint32_t ka[8][4];
-      if (!(debug & 4)) {
       QkGather<KB, 0>::run(ka, gr.k, base_k);
 #pragma unroll
       for (int s = 0; s < 8; ++s)   // even / odd k-steps: two independent accumulator chains
         mma_16816(sc[s & 1], ka[s][0], ka[s][1], ka[s][2], ka[s][3], qf[2 * s], qf[2 * s + 1]);
-      } else { sc[0][0] = __uint_as_float(gr.k[0][0] ^ gr.k[1][KB - 1]) * 1e-30f; sc[0][3] = __uint_as_float(gr.k[1][0] ^ gr.k[0][KB - 1]) * 1e-30f; }
     }
     const float f0 = gr.n[0].x * scale_log2, f1 = gr.n[1].x * scale_log2;
     float s0 = (sc[0][0] + sc[1][0]) * f0, s1 = (sc[0][1] + sc[1][1]) * f0;
@@ -306,7 +304,6 @@ struct WarpCtx {
     const uint32_t x1 = pack_half2(p2 * nv1, p3 * nv1);   // row r+8
     const uint32_t y[2] = {movmatrix_trans(x0), movmatrix_trans(x1)};   // (P[2c][r], P[2c+1][r]) of rows 0-7 / 8-15
     uint32_t pa[2][4][4];
-    if (debug & 2) { oacc[0][0][0] += __uint_as_float((gr.v[0][0] ^ gr.v[1][0] ^ gr.v[2][0] ^ gr.v[3][0] ^ y[0] ^ y[1]) & 0xff); return; }
     PvGather<VB, 0>::run(pa[0], gr.v[0], gr.v[1], base_v);
     PvGather<VB, 0>::run(pa[1], gr.v[2], gr.v[3], base_v);
 #pragma unroll
@@ -329,23 +326,25 @@ struct WarpCtx {
   }
 };
 
-template <int G, int KB, int VB, int NS, int S>
+// One turn of the ring: NS groups, stage S for group j0 + S.  STEADY turns are known to lie wholly inside the warp's
+// range and to hold no ragged group, so they carry no range or mask tests.
+template <int G, int KB, int VB, int NS, int S, bool STEADY>
 struct RingSteps {
   __device__ static __forceinline__ void run(WarpCtx<G, KB, VB, NS>& cx, int j0, bool tail_masked) {
     const int j = j0 + S;
-    if (j < cx.ng) {
-      if (!(cx.debug & 1)) cx.template issue<(S + NS - 1) % NS>(j + NS - 1); else cp_async_commit();
+    if (STEADY || j < cx.ng) {
+      cx.template issue<(S + NS - 1) % NS>(j + NS - 1);
       cp_async_wait<NS - 1>();
       __syncwarp();
-      if (tail_masked && j == cx.ng - 1) cx.template consume<S, true>(j);
+      if (!STEADY && tail_masked && j == cx.ng - 1) cx.template consume<S, true>(j);
       else cx.template consume<S, false>(j);
       __syncwarp();
     }
-    RingSteps<G, KB, VB, NS, S + 1>::run(cx, j0, tail_masked);
+    RingSteps<G, KB, VB, NS, S + 1, STEADY>::run(cx, j0, tail_masked);
   }
 };
-template <int G, int KB, int VB, int NS>
-struct RingSteps<G, KB, VB, NS, NS> {
+template <int G, int KB, int VB, int NS, bool STEADY>
+struct RingSteps<G, KB, VB, NS, NS, STEADY> {
   __device__ static __forceinline__ void run(WarpCtx<G, KB, VB, NS>&, int, bool) {}
 };
 
@@ -403,39 +402,71 @@ __global__ void __launch_bounds__(W * 32, 1) decode_split_kernel(const DecodePar
                                             : lut_win + kLutWindow + (warp - rings_before) * Cfg::kRingBytes;
   uint8_t* lut = smem + (lut_win - win0);
 
+  // ---- this warp's view of the cache; start the first copies so that their latency hides behind the set-up ------------
+  WarpCtx<G, KB, VB, NS> cx;
+  cx.row_stride = p.H_kv * Gm::kSlotBytes;
+#pragma unroll
+  for (int it = 0; it < Gm::kIssueIters; ++it) {
+    int ch = it * 32 + lane;
+    if (ch >= Gm::kGroupChunks) ch = Gm::kGroupChunks - 1;
+    const int rho = ch / Gm::kChunks, piece = ch - rho * Gm::kChunks;
+    cx.src_off[it] = rho * cx.row_stride + piece * 16;
+    cx.dst_addr[it] = ring + rho * Gm::kCell + piece * 16;
+  }
+  cx.last_valid = (Gm::kIssueIters - 1) * 32 + lane < Gm::kGroupChunks;
+  cx.k_addr = ring + stage_perm(r) * Gm::kCell + c * (4 * KB);
+  cx.v_addr = ring + stage_perm(2 * c) * Gm::kCell + 16 * KB + r * (2 * VB);
+  cx.v_addr_b = ring + stage_perm(2 * c + 1) * Gm::kCell + 16 * KB + r * (2 * VB);
+  cx.n_addr = ring + stage_perm(r) * Gm::kCell + 16 * KB + 16 * VB;
+  cx.cache_head = p.cache + static_cast<int64_t>(head) * Gm::kSlotBytes;
+  cx.bt_row = p.block_table + static_cast<int64_t>(b) * p.bt_stride;
+  cx.block_size = p.block_size; cx.num_blocks = p.num_blocks;
+  cx.gpb = p.block_size >> 4; cx.gpb_shift = p.gpb_shift;
+  cx.block_bytes = static_cast<uint32_t>(p.block_size) * cx.row_stride; cx.group_bytes = 16u * cx.row_stride;
+  cx.g_begin_sub = (t_begin >> 4) + sub; cx.R = R; cx.ng = ng; cx.t_end = t_end; cx.r = r; cx.tok_r = stage_perm(r);
+  cx.bad_block = false;
+  if (ng > 0) {
+    cx.load_block_id(0);
+    RingPrologue<G, KB, VB, NS, 0>::run(cx);   // stages 0 .. NS-2; stage NS-1 is free until the first turn of the ring
+  }
+
   __shared__ float s_err[64];
   __shared__ int s_idx[64];
   float alpha_k, alpha_v;
   find_table_scales<(KB == 4 ? 16 : 4), (VB == 4 ? 16 : 4)>(p.cb_k, p.cb_v, s_err, s_idx, alpha_k, alpha_v);
   {   // build both tables: code e, lane l -> K pair at e*256 + 4l, V pair at e*256 + 128 + 4l (levels divided by alpha)
     constexpr int EK = KB == 4 ? 256 : 16, EV = VB == 4 ? 256 : 16, LK = KB == 4 ? 16 : 4, LV = VB == 4 ? 16 : 4;
-    const float inv_k = 1.0f / alpha_k, inv_v = 1.0f / alpha_v;
+    // lane i keeps level i & (L - 1) of either codebook; entries are put together by shuffles
+    const float lev_k = __ldg(p.cb_k + (lane & (LK - 1))) * (1.0f / alpha_k);
+    const float lev_v = __ldg(p.cb_v + (lane & (LV - 1))) * (1.0f / alpha_v);
     uint32_t* lw = reinterpret_cast<uint32_t*>(lut);
+#pragma unroll 4
     for (int e = warp; e < (EK > EV ? EK : EV); e += W) {
-      if (e < EK) {
-        const int first = KB == 4 ? (e >> 4) : (e >> 2), second = KB == 4 ? (e & 15) : (e & 3);
-        lw[e * 64 + lane] = pack_half2(__ldg(p.cb_k + (first & (LK - 1))) * inv_k, __ldg(p.cb_k + (second & (LK - 1))) * inv_k);
-      }
-      if (e < EV) {
-        const int first = VB == 4 ? (e >> 4) : (e >> 2), second = VB == 4 ? (e & 15) : (e & 3);
-        lw[e * 64 + 32 + lane] = pack_half2(__ldg(p.cb_v + (first & (LV - 1))) * inv_v, __ldg(p.cb_v + (second & (LV - 1))) * inv_v);
-      }
+      const int fk = KB == 4 ? (e >> 4) & 15 : (e >> 2) & 3, sk = KB == 4 ? (e & 15) : (e & 3);
+      const int fv = VB == 4 ? (e >> 4) & 15 : (e >> 2) & 3, sv = VB == 4 ? (e & 15) : (e & 3);
+      const uint32_t wk = pack_half2(__shfl_sync(0xffffffffu, lev_k, fk), __shfl_sync(0xffffffffu, lev_k, sk));
+      const uint32_t wv = pack_half2(__shfl_sync(0xffffffffu, lev_v, fv), __shfl_sync(0xffffffffu, lev_v, sv));
+      if (e < EK) lw[e * 64 + lane] = wk;
+      if (e < EV) lw[e * 64 + 32 + lane] = wv;
     }
   }
 
-  WarpCtx<G, KB, VB, NS> cx;
-  // ---- rotate this head's queries, stage them as fp16 rows in this warp's own ring, pick up the B fragments ------------
+  // ---- rotate this head's queries, stage them as fp16 rows in the last stage of this warp's ring, pick up the B fragments --
   {
-    __half* q_rows = reinterpret_cast<__half*>(smem + (ring - win0));
-    for (int qi = 0; qi < 8; ++qi) {
-      float v[4] = {0.f, 0.f, 0.f, 0.f};
-      if (qi < g) {
-        load_half4(p.q + (static_cast<int64_t>(b) * p.H_q + head * g + qi) * kHeadDim + 4 * lane, v);
-        fht128_warp(v, lane);
+    __half* q_rows = reinterpret_cast<__half*>(smem + (ring - win0) + (NS - 1) * Gm::kStageBytes);
+    static_assert(8 * kHeadDim * 2 <= Gm::kStageBytes, "eight fp16 query rows must fit one ring stage");
+    float qv[G][4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) v[i] *= kRsqrtD;
-      }
-      *reinterpret_cast<uint2*>(q_rows + qi * kHeadDim + 4 * lane) = pack_half4(v);
+    for (int qi = 0; qi < G; ++qi) {
+      qv[qi][0] = qv[qi][1] = qv[qi][2] = qv[qi][3] = 0.f;
+      if (qi < g) load_half4(p.q + (static_cast<int64_t>(b) * p.H_q + head * g + qi) * kHeadDim + 4 * lane, qv[qi]);
+    }
+#pragma unroll
+    for (int qi = 0; qi < G; ++qi) {
+      fht128_warp(qv[qi], lane);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) qv[qi][i] *= kRsqrtD;
+      *reinterpret_cast<uint2*>(q_rows + qi * kHeadDim + 4 * lane) = pack_half4(qv[qi]);
     }
     __syncwarp();
     const int qrow = G == 4 ? (r & 3) : r;   // column r: query r, or r & 3 when the group is padded to 4
@@ -455,27 +486,7 @@ __global__ void __launch_bounds__(W * 32, 1) decode_split_kernel(const DecodePar
     cx.sel_b0 = odd ? 0x1044u : 0x4410u;
     cx.sel_b1 = odd ? 0x3244u : 0x4432u;
   }
-  cx.row_stride = p.H_kv * Gm::kSlotBytes;
-#pragma unroll
-  for (int it = 0; it < Gm::kIssueIters; ++it) {
-    int ch = it * 32 + lane;
-    if (ch >= Gm::kGroupChunks) ch = Gm::kGroupChunks - 1;
-    const int rho = ch / Gm::kChunks, piece = ch - rho * Gm::kChunks;
-    cx.src_off[it] = rho * cx.row_stride + piece * 16;
-    const int d = rho * Gm::kCell + piece * 16;
-    cx.dst_addr[it] = ring + d;
-  }
-  cx.last_valid = (Gm::kIssueIters - 1) * 32 + lane < Gm::kGroupChunks;
-  cx.k_addr = ring + stage_perm(r) * Gm::kCell + c * (4 * KB);
-  cx.v_addr = ring + stage_perm(2 * c) * Gm::kCell + 16 * KB + r * (2 * VB);
-  cx.v_addr_b = ring + stage_perm(2 * c + 1) * Gm::kCell + 16 * KB + r * (2 * VB);
-  cx.n_addr = ring + stage_perm(r) * Gm::kCell + 16 * KB + 16 * VB;
-  cx.cache_head = p.cache + static_cast<int64_t>(head) * Gm::kSlotBytes;
-  cx.bt_row = p.block_table + static_cast<int64_t>(b) * p.bt_stride;
-  cx.block_size = p.block_size; cx.num_blocks = p.num_blocks;
-  cx.gpb = p.block_size >> 4; cx.gpb_shift = p.gpb_shift;
-  cx.g_begin_sub = (t_begin >> 4) + sub; cx.R = R; cx.ng = ng; cx.t_end = t_end; cx.r = r; cx.tok_r = stage_perm(r);
-  cx.scale_log2 = p.scale_log2 * alpha_k; cx.status = p.status; cx.debug = p.debug;
+  cx.scale_log2 = p.scale_log2 * alpha_k;
   cx.m_run[0] = cx.m_run[1] = kMinusBig;
   cx.l_run[0] = cx.l_run[1] = 0.f;
 #pragma unroll
@@ -487,11 +498,14 @@ __global__ void __launch_bounds__(W * 32, 1) decode_split_kernel(const DecodePar
 
   if (ng > 0) {
     const bool tail_masked = ((t_end - t_begin) & 15) != 0 && (cta_groups - 1) % R == sub;
-    cx.load_block_id(0);
-    RingPrologue<G, KB, VB, NS, 0>::run(cx);
+    int j0 = 0;
+    const int steady_end = ng - (tail_masked ? 1 : 0);
 #pragma unroll 1
-    for (int j0 = 0; j0 < ng; j0 += NS) RingSteps<G, KB, VB, NS, 0>::run(cx, j0, tail_masked);
+    for (; j0 + NS <= steady_end; j0 += NS) RingSteps<G, KB, VB, NS, 0, true>::run(cx, j0, false);
+#pragma unroll 1
+    for (; j0 < ng; j0 += NS) RingSteps<G, KB, VB, NS, 0, false>::run(cx, j0, tail_masked);
     cp_async_wait<0>();
+    if (cx.bad_block) atomicOr(p.status, 1);
   }
 
   // ---- write this warp's partial -------------------------------------------------------------------------------------------
@@ -537,325 +551,66 @@ __global__ void __launch_bounds__(W * 32, 1) decode_split_kernel(const DecodePar
   }
 }
 
-// ---- page-pipeline variant of the split kernel -----------------------------------------------------------------------
-// Same arithmetic (WarpCtx::attend), different data movement.  The HPC warps that share a key sub-range form a
-// pipeline: a stage holds one whole 16-token group of all their heads, brought in by 16 bulk copies (one per token:
-// HPC * slot bytes, contiguous in the cache) that complete on an mbarrier.  The copy engine does the address work, so
-// the warps spend no instructions and no load/store-unit time on it.  Token rows are spaced RS bytes apart in shared
-// memory with RS = 32 (mod 128), and accumulator row r is fed by token perm(r) = 0,2,1,3,6,4,7,5: with that pairing the
-// K reads of two rows and the V reads of four rows always fall into different banks.  The warp that finishes a stage
-// last (shared-memory counter) starts the copies of the group NS ahead into it; nobody ever waits for a consumer.
-template <int HPC, int SLOT>
-struct PageGeom {
-  static constexpr int kRowBytes = HPC * SLOT;                                  // bytes copied per token
-  static constexpr int kRS = (kRowBytes - 32 + 127) / 128 * 128 + 32;           // row stride in shared memory
-  static constexpr int kStage = 16 * kRS;
-};
-
-__device__ __forceinline__ int page_perm(int row) { return (0xBE6650u >> (3 * (row & 7))) & 7; }   // 0,2,1,3,6,4,7,5
-
-template <int G, int KB, int VB, int W, int NS, int HPC>
-__global__ void __launch_bounds__(W * 32, 1) decode_page_kernel(const DecodeParams p) {
-  using Gm = Geom<KB, VB>;
-  using Pg = PageGeom<HPC, Gm::kSlotBytes>;
-  constexpr int NT = G / 4;
-  constexpr int R = W / HPC;                    // pipelines (key sub-ranges) per CTA
-  constexpr int kRing = NS * Pg::kStage;        // bytes per pipeline
-  static_assert(kRing >= HPC * 8 * kHeadDim * 2, "pipeline ring too small to stage the query rows");
-  extern __shared__ __align__(128) uint8_t smem[];
-  __shared__ __align__(8) uint64_t s_full[R * NS];
-  __shared__ int s_cnt[R * NS];
-  __shared__ float s_err[64];
-  __shared__ int s_idx[64];
-
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int r = lane >> 2, c = lane & 3;
-  const int split = blockIdx.x, b = blockIdx.y, hg = blockIdx.z;
-  const int hic = warp % HPC;                   // head inside the CTA
-  const int head = hg * HPC + hic;
-  const int sub = warp / HPC;
-  const int g = p.group;
-
-  const int seq_len = p.seq_lens[b];
-  const int t_begin = split * p.tokens_per_split;
-  const int t_end = min(seq_len, t_begin + p.tokens_per_split);
-  const int cta_groups = t_end > t_begin ? (t_end - t_begin + 15) >> 4 : 0;
-  const int ng = cta_groups > sub ? (cta_groups - sub + R - 1) / R : 0;
-
-  const int part = split * R + sub;
-  const int64_t prow0 = (static_cast<int64_t>(part) * p.B + b) * p.H_q + head * g;
-
-  const uint32_t win0 = smem_addr(smem);
-  const uint32_t lut_win = (win0 + kLutWindow - 1) & ~static_cast<uint32_t>(kLutWindow - 1);
-  const int rings_before = static_cast<int>((lut_win - win0) / kRing);
-  const int rings_after = R > rings_before ? R - rings_before : 0;
-  const uint32_t win_end = lut_win + kLutWindow + rings_after * kRing;
-  const bool fits = win_end - win0 <= static_cast<uint32_t>(p.smem_bytes);
-  if (cta_groups == 0 || !fits) {
-    if (!fits && tid == 0) atomicOr(p.status, 2);
-    if (lane < g) *reinterpret_cast<float2*>(p.part_ml + (prow0 + lane) * 2) = make_float2(-INFINITY, 0.f);
-    return;
-  }
-  const uint32_t ring = sub < rings_before ? win0 + sub * kRing : lut_win + kLutWindow + (sub - rings_before) * kRing;
-  uint8_t* lut = smem + (lut_win - win0);
-
-  float alpha_k, alpha_v;
-  find_table_scales<(KB == 4 ? 16 : 4), (VB == 4 ? 16 : 4)>(p.cb_k, p.cb_v, s_err, s_idx, alpha_k, alpha_v);
-  {
-    constexpr int EK = KB == 4 ? 256 : 16, EV = VB == 4 ? 256 : 16, LK = KB == 4 ? 16 : 4, LV = VB == 4 ? 16 : 4;
-    const float inv_k = 1.0f / alpha_k, inv_v = 1.0f / alpha_v;
-    uint32_t* lw = reinterpret_cast<uint32_t*>(lut);
-    for (int e = warp; e < (EK > EV ? EK : EV); e += W) {
-      if (e < EK) {
-        const int first = KB == 4 ? (e >> 4) : (e >> 2), second = KB == 4 ? (e & 15) : (e & 3);
-        lw[e * 64 + lane] = pack_half2(__ldg(p.cb_k + (first & (LK - 1))) * inv_k, __ldg(p.cb_k + (second & (LK - 1))) * inv_k);
-      }
-      if (e < EV) {
-        const int first = VB == 4 ? (e >> 4) : (e >> 2), second = VB == 4 ? (e & 15) : (e & 3);
-        lw[e * 64 + 32 + lane] = pack_half2(__ldg(p.cb_v + (first & (LV - 1))) * inv_v, __ldg(p.cb_v + (second & (LV - 1))) * inv_v);
-      }
-    }
-  }
-
-  WarpCtx<G, KB, VB, NS> cx;
-  {
-    __half* q_rows = reinterpret_cast<__half*>(smem + (ring - win0)) + hic * 8 * kHeadDim;
-    for (int qi = 0; qi < 8; ++qi) {
-      float v[4] = {0.f, 0.f, 0.f, 0.f};
-      if (qi < g) {
-        load_half4(p.q + (static_cast<int64_t>(b) * p.H_q + head * g + qi) * kHeadDim + 4 * lane, v);
-        fht128_warp(v, lane);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) v[i] *= kRsqrtD;
-      }
-      *reinterpret_cast<uint2*>(q_rows + qi * kHeadDim + 4 * lane) = pack_half4(v);
-    }
-    __syncwarp();
-    const int qrow = G == 4 ? (r & 3) : r;
-    const uint4* src = reinterpret_cast<const uint4*>(q_rows + qrow * kHeadDim + 32 * c);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const uint4 t = src[i];
-      cx.qf[4 * i] = t.x; cx.qf[4 * i + 1] = t.y; cx.qf[4 * i + 2] = t.z; cx.qf[4 * i + 3] = t.w;
-    }
-  }
-  const uint32_t bars = smem_addr(&s_full[sub * NS]);
-  if (hic == 0 && lane < NS) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bars + 8 * lane) : "memory");
-    s_cnt[sub * NS + lane] = 0;
-  }
-  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the query rows were ordinary stores; bulk copies reuse the space
-  __syncthreads();
-
-  cx.base_k = lut_win | (lane << 2);
-  cx.base_v = cx.base_k | 128u;
-  {
-    const bool odd = G == 4 && (r >> 2) != 0;
-    cx.sel_b0 = odd ? 0x1044u : 0x4410u;
-    cx.sel_b1 = odd ? 0x3244u : 0x4432u;
-  }
-  const int row_stride = p.H_kv * Gm::kSlotBytes;
-  const int gpb = p.block_size >> 4;
-  const int32_t* bt_row = p.block_table + static_cast<int64_t>(b) * p.bt_stride;
-  const int g_begin_sub = (t_begin >> 4) + sub;
-  cx.g_begin_sub = g_begin_sub; cx.R = R; cx.ng = ng; cx.t_end = t_end; cx.r = r; cx.tok_r = page_perm(r);
-  cx.scale_log2 = p.scale_log2 * alpha_k; cx.status = p.status; cx.debug = p.debug;
-  cx.m_run[0] = cx.m_run[1] = kMinusBig;
-  cx.l_run[0] = cx.l_run[1] = 0.f;
-#pragma unroll
-  for (int u = 0; u < 4; ++u)
-#pragma unroll
-    for (int t = 0; t < NT; ++t)
-#pragma unroll
-      for (int i = 0; i < 4; ++i) cx.oacc[u][t][i] = 0.f;
-
-  // window addresses of this lane's pieces in stage 0 (rows +8 and later stages are compile-time offsets)
-  const uint32_t head_base = ring + hic * Gm::kSlotBytes;
-  const uint32_t k_addr = head_base + page_perm(r) * Pg::kRS + c * (4 * KB);
-  const uint32_t n_addr = head_base + page_perm(r) * Pg::kRS + 16 * KB + 16 * VB;
-  const uint32_t va_addr = head_base + page_perm(2 * c) * Pg::kRS + 16 * KB + r * (2 * VB);
-  const uint32_t vb_addr = head_base + page_perm(2 * c + 1) * Pg::kRS + 16 * KB + r * (2 * VB);
-  const uint8_t* cache_rows = p.cache + static_cast<int64_t>(hg) * HPC * Gm::kSlotBytes;   // first head of this CTA inside a slot row
-
-  auto block_of = [&](int j) -> int {      // block id of this pipeline's group j (clamped index; range-checked)
-    const int jj = j < ng ? j : ng - 1;
-    const int gidx = g_begin_sub + R * jj;
-    int blk = __ldg(bt_row + (p.gpb_shift >= 0 ? gidx >> p.gpb_shift : gidx / gpb));
-    if (static_cast<unsigned>(blk) >= static_cast<unsigned>(p.num_blocks)) { atomicOr(p.status, 1); blk = 0; }
-    return blk;
-  };
-  // Start the 16 row copies of group j into stage s (whole warp calls; lanes 0..15 copy).
-  auto refill = [&](int j, int s, int blk) {
-    const int gidx = g_begin_sub + R * j;
-    const int rem = p.gpb_shift >= 0 ? gidx & (gpb - 1) : gidx % gpb;
-    const int64_t slot0 = static_cast<int64_t>(blk) * p.block_size + (rem << 4);
-    const uint8_t* src = cache_rows + (slot0 + (lane & 15)) * row_stride;
-    const uint32_t bar = bars + 8 * s;
-    if (lane == 0) {
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "n"(16 * Pg::kRowBytes) : "memory");
-    }
-    __syncwarp();
-    if (lane < 16)
-      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                   ::"r"(ring + s * Pg::kStage + (lane & 15) * Pg::kRS), "l"(src), "n"(Pg::kRowBytes), "r"(bar) : "memory");
-  };
-
-  if (ng > 0) {
-    const bool tail_masked = ((t_end - t_begin) & 15) != 0 && (cta_groups - 1) % R == sub;
-    if (hic == 0) {
-#pragma unroll 1
-      for (int s = 0; s < NS; ++s)
-        if (s < ng) refill(s, s, block_of(s));
-    }
-    bool alive = true;
-#pragma unroll 1
-    for (int j0 = 0; j0 < ng && alive; j0 += NS) {
-      const uint32_t phase = (j0 / NS) & 1;
-#pragma unroll
-      for (int s = 0; s < NS; ++s) {
-        const int j = j0 + s;
-        if (j < ng && alive) {
-          const int blk_next = block_of(j + NS);      // needed only if this warp turns out to be the last one on the stage
-          {   // bounded poll of the stage barrier; a lost copy sets status bit 2 instead of hanging
-            uint32_t done = 0;
-            for (int spin = 0; spin < (1 << 24) && !done; ++spin)
-              asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
-                           : "=r"(done) : "r"(bars + 8 * s), "r"(phase) : "memory");
-            if (!done) { atomicOr(p.status, 4); alive = false; }
-          }
-          GroupRegs<KB, VB> gr;
-          {
-            const uint32_t so = s * Pg::kStage;       // s is a compile-time constant after unrolling
-            constexpr int H = 8 * Pg::kRS;
-            if (KB == 4) {
-              uint4 t0, t1;
-              asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(t0.x), "=r"(t0.y), "=r"(t0.z), "=r"(t0.w) : "r"(k_addr + so) : "memory");
-              asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(t1.x), "=r"(t1.y), "=r"(t1.z), "=r"(t1.w) : "r"(k_addr + so + H) : "memory");
-              gr.k[0][0] = t0.x; gr.k[0][1] = t0.y; gr.k[0][KB - 2] = t0.z; gr.k[0][KB - 1] = t0.w;
-              gr.k[1][0] = t1.x; gr.k[1][1] = t1.y; gr.k[1][KB - 2] = t1.z; gr.k[1][KB - 1] = t1.w;
-            } else {
-              const uint2 t0 = lds_stage8<0>(k_addr + so), t1 = lds_stage8<0>(k_addr + so + H);
-              gr.k[0][0] = t0.x; gr.k[0][1] = t0.y; gr.k[1][0] = t1.x; gr.k[1][1] = t1.y;
-            }
-            const uint2 n0 = lds_stage8<0>(n_addr + so), n1 = lds_stage8<0>(n_addr + so + H);
-            gr.n[0] = make_float2(__uint_as_float(n0.x), __uint_as_float(n0.y));
-            gr.n[1] = make_float2(__uint_as_float(n1.x), __uint_as_float(n1.y));
-            if (VB == 4) {
-              const uint2 a = lds_stage8<0>(va_addr + so), bb = lds_stage8<0>(vb_addr + so);
-              const uint2 c2 = lds_stage8<0>(va_addr + so + H), d = lds_stage8<0>(vb_addr + so + H);
-              gr.v[0][0] = a.x; gr.v[0][VB / 2 - 1] = a.y; gr.v[1][0] = bb.x; gr.v[1][VB / 2 - 1] = bb.y;
-              gr.v[2][0] = c2.x; gr.v[2][VB / 2 - 1] = c2.y; gr.v[3][0] = d.x; gr.v[3][VB / 2 - 1] = d.y;
-            } else {
-              gr.v[0][0] = lds_stage4<0>(va_addr + so); gr.v[1][0] = lds_stage4<0>(vb_addr + so);
-              gr.v[2][0] = lds_stage4<0>(va_addr + so + H); gr.v[3][0] = lds_stage4<0>(vb_addr + so + H);
-            }
-          }
-          if (p.debug & 8) cx.oacc[0][0][0] += __uint_as_float((gr.k[0][0] ^ gr.k[1][KB - 1] ^ gr.v[0][0] ^ gr.v[3][0] ^ __float_as_uint(gr.n[0].x)) & 0xff);
-          else if (tail_masked && j == ng - 1) cx.template attend<true>(gr, j);
-          else cx.template attend<false>(gr, j);
-          // hand the stage back: the last of the HPC warps starts the copies of group j + NS into it
-          __syncwarp();
-          int last = 0;
-          if (lane == 0) {
-            __threadfence_block();
-            last = atomicAdd(&s_cnt[sub * NS + s], 1) == HPC - 1;
-            if (last) s_cnt[sub * NS + s] = 0;
-          }
-          last = __shfl_sync(0xffffffffu, last, 0);
-          if (last && j + NS < ng) refill(j + NS, s, blk_next);
-        }
-      }
-    }
-  }
-
-  // ---- write this warp's partial -------------------------------------------------------------------------------------------
-  float l0 = cx.l_run[0], l1 = cx.l_run[1];
-#pragma unroll
-  for (int mask = 4; mask < 32; mask <<= 1) {
-    l0 += __shfl_xor_sync(0xffffffffu, l0, mask);
-    l1 += __shfl_xor_sync(0xffffffffu, l1, mask);
-  }
-  const float m0 = l0 > 0.f ? cx.m_run[0] : -INFINITY, m1 = l1 > 0.f ? cx.m_run[1] : -INFINITY;
-#pragma unroll
-  for (int u = 0; u < 4; ++u)
-#pragma unroll
-    for (int t = 0; t < NT; ++t)
-#pragma unroll
-      for (int i = 0; i < 4; ++i) cx.oacc[u][t][i] *= alpha_v;
-  if (G == 4) {
-    const int parity = c >> 1, q0 = 2 * (c & 1);
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int d = 16 * r + 4 * u + parity;
-      if (q0 < g) { p.part_o[(prow0 + q0) * kHeadDim + d] = cx.oacc[u][0][0]; p.part_o[(prow0 + q0) * kHeadDim + d + 2] = cx.oacc[u][0][2]; }
-      if (q0 + 1 < g) { p.part_o[(prow0 + q0 + 1) * kHeadDim + d] = cx.oacc[u][0][1]; p.part_o[(prow0 + q0 + 1) * kHeadDim + d + 2] = cx.oacc[u][0][3]; }
-    }
-    if (r == 0 && c < 2) {
-      if (q0 < g) *reinterpret_cast<float2*>(p.part_ml + (prow0 + q0) * 2) = make_float2(m0, l0);
-      if (q0 + 1 < g) *reinterpret_cast<float2*>(p.part_ml + (prow0 + q0 + 1) * 2) = make_float2(m1, l1);
-    }
-  } else {
-    const int q0 = 2 * c;
-#pragma unroll
-    for (int u = 0; u < 4; ++u)
-#pragma unroll
-      for (int t = 0; t < NT; ++t) {
-        const int d = 16 * r + 4 * u + t;
-        if (q0 < g) { p.part_o[(prow0 + q0) * kHeadDim + d] = cx.oacc[u][t][0]; p.part_o[(prow0 + q0) * kHeadDim + d + 2] = cx.oacc[u][t][2]; }
-        if (q0 + 1 < g) { p.part_o[(prow0 + q0 + 1) * kHeadDim + d] = cx.oacc[u][t][1]; p.part_o[(prow0 + q0 + 1) * kHeadDim + d + 2] = cx.oacc[u][t][3]; }
-      }
-    if (r == 0) {
-      if (q0 < g) *reinterpret_cast<float2*>(p.part_ml + (prow0 + q0) * 2) = make_float2(m0, l0);
-      if (q0 + 1 < g) *reinterpret_cast<float2*>(p.part_ml + (prow0 + q0 + 1) * 2) = make_float2(m1, l1);
-    }
-  }
-}
-
 // ---- merge --------------------------------------------------------------------------------------------------
-// One CTA (8 warps) per output row.  Warp w folds partials w, w+8, ... with a running maximum; the eight
-// warp results are combined through shared memory.  m values are multiplied by `m_to_log2` on load (1 for the
-// split kernel's own partials, log2(e) for natural-log partials supplied through the C ABI).
+// One CTA (16 warps) per output row.  A first pass over the (m) column finds the row's maximum; then warp w sums
+// partials w, w+16, ... weighted by exp2(m_p - max), four at a time so that their loads are in flight together,
+// and the sixteen warp sums are added through shared memory.  m values are multiplied by `m_to_log2` on load (1 for
+// the split kernel's own partials, log2(e) for natural-log partials supplied through the C ABI).
 // mode 0: normalise, round to fp16, optional inverse Hadamard, store fp16.
 // mode 1: store the merged un-normalised partial as fp32 (O, m in natural log, l).
-__global__ void __launch_bounds__(256) decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_m,
-                                                           const float* __restrict__ part_l, int ml_stride, int P,
-                                                           int64_t rows, float m_to_log2, int mode, int unrotate,
-                                                           __half* __restrict__ out, float* __restrict__ out_o,
-                                                           float* __restrict__ out_m, float* __restrict__ out_l) {
-  __shared__ float s_o[8][kHeadDim];
-  __shared__ float s_m[8], s_l[8];
+constexpr int kMergeWarps = 16, kMergeUnroll = 4;
+__global__ void __launch_bounds__(kMergeWarps * 32) decode_merge_kernel(
+    const float* __restrict__ part_o, const float* __restrict__ part_m, const float* __restrict__ part_l, int ml_stride, int P,
+    int64_t rows, float m_to_log2, int mode, int unrotate, __half* __restrict__ out, float* __restrict__ out_o,
+    float* __restrict__ out_m, float* __restrict__ out_l) {
+  __shared__ float s_o[kMergeWarps][kHeadDim];
+  __shared__ float s_l[kMergeWarps], s_max[kMergeWarps];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t row = blockIdx.x;
-  float m = -INFINITY, l = 0.f, o[4] = {0.f, 0.f, 0.f, 0.f};
-  for (int pi = warp; pi < P; pi += 8) {
-    const int64_t pr = static_cast<int64_t>(pi) * rows + row;
-    const float mp = part_m[pr * ml_stride] * m_to_log2;
-    if (mp == -INFINITY) continue;          // empty range: nothing was written to part_o
-    const float lp = part_l[pr * ml_stride];
-    const float4 op = *reinterpret_cast<const float4*>(part_o + pr * kHeadDim + 4 * lane);
-    const float mn = fmaxf(m, mp);
-    const float a = fast_exp2(m - mn), bw = fast_exp2(mp - mn);
-    l = l * a + lp * bw;
-    o[0] = o[0] * a + op.x * bw; o[1] = o[1] * a + op.y * bw; o[2] = o[2] * a + op.z * bw; o[3] = o[3] * a + op.w * bw;
-    m = mn;
-  }
-  s_o[warp][4 * lane] = o[0]; s_o[warp][4 * lane + 1] = o[1]; s_o[warp][4 * lane + 2] = o[2]; s_o[warp][4 * lane + 3] = o[3];
-  if (lane == 0) { s_m[warp] = m; s_l[warp] = l; }
+  float mx = -INFINITY;
+  for (int pi = threadIdx.x; pi < P; pi += kMergeWarps * 32)
+    mx = fmaxf(mx, part_m[(static_cast<int64_t>(pi) * rows + row) * ml_stride]);
+#pragma unroll
+  for (int mask = 16; mask > 0; mask >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, mask));
+  if (lane == 0) s_max[warp] = mx;
   __syncthreads();
-  if (warp != 0) return;
   float mt = -INFINITY;
 #pragma unroll
-  for (int w = 0; w < 8; ++w) mt = fmaxf(mt, s_m[w]);
+  for (int w = 0; w < kMergeWarps; ++w) mt = fmaxf(mt, s_max[w]);
+  mt *= m_to_log2;                                   // the factor is positive: the maximum stays the maximum
   const float ms = mt == -INFINITY ? 0.f : mt;
+
+  float l = 0.f, o[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int base = warp; base < P; base += kMergeWarps * kMergeUnroll) {
+    float mp[kMergeUnroll], lp[kMergeUnroll];
+    float4 op[kMergeUnroll];
+#pragma unroll
+    for (int u = 0; u < kMergeUnroll; ++u) {
+      const int pi = base + u * kMergeWarps;
+      const bool valid = pi < P;
+      const int64_t pr = static_cast<int64_t>(valid ? pi : base) * rows + row;
+      mp[u] = valid ? part_m[pr * ml_stride] : -INFINITY;
+      lp[u] = part_l[pr * ml_stride];
+      op[u] = *reinterpret_cast<const float4*>(part_o + pr * kHeadDim + 4 * lane);
+    }
+#pragma unroll
+    for (int u = 0; u < kMergeUnroll; ++u) {
+      if (mp[u] == -INFINITY) continue;              // empty range: its O row was never written, do not touch it
+      const float bw = fast_exp2(mp[u] * m_to_log2 - ms);
+      l += lp[u] * bw;
+      o[0] += op[u].x * bw; o[1] += op[u].y * bw; o[2] += op[u].z * bw; o[3] += op[u].w * bw;
+    }
+  }
+  *reinterpret_cast<float4*>(&s_o[warp][4 * lane]) = make_float4(o[0], o[1], o[2], o[3]);
+  if (lane == 0) s_l[warp] = l;
+  __syncthreads();
+  if (warp != 0) return;
   float lt = 0.f, ot[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-  for (int w = 0; w < 8; ++w) {
-    const float a = fast_exp2(s_m[w] - ms);   // exp2(-inf) = 0 for warps that saw nothing
-    lt += s_l[w] * a;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) ot[i] += s_o[w][4 * lane + i] * a;
+  for (int w = 0; w < kMergeWarps; ++w) {
+    lt += s_l[w];
+    const float4 t = *reinterpret_cast<const float4*>(&s_o[w][4 * lane]);
+    ot[0] += t.x; ot[1] += t.y; ot[2] += t.z; ot[3] += t.w;
   }
   if (mode == 1) {
     *reinterpret_cast<float4*>(out_o + row * kHeadDim + 4 * lane) = make_float4(ot[0], ot[1], ot[2], ot[3]);
@@ -937,20 +692,9 @@ struct Plan {
   int warps, depth, heads_per_cta, head_groups, warps_per_head, splits, tokens_per_split, parts;
 };
 
-// Warps per CTA and ring stages per warp of the split kernel.  Defaults can be overridden for tuning with the
-// environment variables CDA_DECODE_WARPS (8 or 16) and CDA_DECODE_STAGES, read once per process.
-static void tuning(int* warps, int* depth) {
-  static int w = 0, d = 0;
-  if (w == 0) {
-    const char* ew = getenv("CDA_DECODE_WARPS");
-    const char* ed = getenv("CDA_DECODE_STAGES");
-    w = ew && atoi(ew) == 8 ? 8 : 16;
-    d = ed ? atoi(ed) : 0;
-    if (w == 16) d = d == 4 ? 4 : 3;
-    else d = d == 6 ? 6 : 4;
-  }
-  *warps = w; *depth = d;
-}
+// Warps per CTA and ring stages per warp of the split kernel: 16 warps (four per scheduler, 128 registers each)
+// with three 2560-byte stages per warp leave room for the 64 KB table in the 227 KB of one SM.
+constexpr int kSplitWarps = 16, kSplitStages = 3;
 
 static int pick_heads_per_cta(int H_kv) {
   int h = 8;
@@ -958,29 +702,32 @@ static int pick_heads_per_cta(int H_kv) {
   return h;
 }
 
-// Choose the number of key-range splits.  One CTA occupies one SM, so the grid should be a whole number of
-// waves of the SM count: take the largest wave count (<= 8) whose splits still hold >= 256 tokens; if even one
-// wave would cut the range finer than that, fall back to 128-token splits (a latency-bound launch anyway).
+// Choose the number of key-range splits.  One CTA occupies one SM and CTAs of one launch all carry the same work, so
+// the launch runs in ceil(CTAs / SMs) rounds, each as long as one CTA: a fixed part (launch, table and query set-up,
+// first copies, partial write and its share of the merge; measured at about the streaming time of 360 tokens) plus
+// the CTA's tokens.  Take the split count with the smallest estimate; splits never go below 128 tokens.
 static Plan make_plan(int B, int H_kv, int max_seq_len, int num_splits, int sms) {
-  constexpr int kMinTokens = 256, kFloorTokens = 128, kMaxWaves = 8;
+  constexpr int kFloorTokens = 128, kFixedTokens = 360, kMaxSplits = 4096;
   Plan pl;
-  tuning(&pl.warps, &pl.depth);
+  pl.warps = kSplitWarps; pl.depth = kSplitStages;
   pl.heads_per_cta = pick_heads_per_cta(H_kv);
   pl.head_groups = H_kv / pl.heads_per_cta;
   pl.warps_per_head = pl.warps / pl.heads_per_cta;
   const int n = max_seq_len > 0 ? max_seq_len : 1;
   int S = num_splits;
   if (S <= 0) {
-    const int64_t other = static_cast<int64_t>(B) * pl.head_groups;
-    S = 0;
-    for (int w = kMaxWaves; w >= 1 && S == 0; --w) {
-      const int64_t s_w = static_cast<int64_t>(w) * sms / other;
-      if (s_w >= 1 && (n + s_w - 1) / s_w >= kMinTokens) S = static_cast<int>(s_w);
-    }
-    if (S == 0) {
-      const int64_t one_wave = sms / other > 1 ? sms / other : 1;
-      const int64_t by_work = (n + kFloorTokens - 1) / kFloorTokens;
-      S = static_cast<int>(one_wave < by_work ? one_wave : by_work);
+    const int64_t other = static_cast<int64_t>(B > 0 ? B : 1) * pl.head_groups;
+    int s_max = (n + kFloorTokens - 1) / kFloorTokens;
+    if (s_max > kMaxSplits) s_max = kMaxSplits;
+    int64_t best = -1;
+    S = 1;
+    for (int s = 1; s <= s_max; ++s) {
+      const int tps_s = ((n + s - 1) / s + 15) / 16 * 16;
+      const int64_t ctas = static_cast<int64_t>((n + tps_s - 1) / tps_s) * other;
+      const int64_t rounds = (ctas + sms - 1) / sms;
+      const int64_t est = rounds * (kFixedTokens + tps_s);
+      if (best < 0 || est < best) { best = est; S = s; }
+      if (rounds > 16 && est > 2 * best) break;   // finer splits only add rounds from here on
     }
   }
   int tps = ((n + S - 1) / S + 15) / 16 * 16;
@@ -1024,6 +771,10 @@ constexpr int kMaxDynamicSmem = 232448 - 1024;   // the opt-in shared memory of 
 
 template <int G, int KB, int VB, int W, int NS>
 static int launch_split(const DecodeParams& p0, const Plan& pl, cudaStream_t st) {
+  // Wherever the dynamic window starts relative to a 64 KB boundary, the rings packed around the aligned table need
+  // at most one ring of slack (or, with few warps, the gap before the table itself).
+  static_assert(kLutWindow + (W + 1) * DecCfg<W, NS, KB, VB>::kRingBytes <= kMaxDynamicSmem && 2 * kLutWindow <= kMaxDynamicSmem,
+                "warp rings and the lookup table do not fit the shared memory of one SM");
   static bool configured[64];
   int dev = 0;
   cudaGetDevice(&dev);
@@ -1035,8 +786,6 @@ static int launch_split(const DecodeParams& p0, const Plan& pl, cudaStream_t st)
   }
   DecodeParams p = p0;
   p.smem_bytes = kMaxDynamicSmem;
-  static const int dbg = getenv("CDA_DECODE_DEBUG") ? atoi(getenv("CDA_DECODE_DEBUG")) : 0;
-  p.debug = dbg;
   const dim3 grid(pl.splits, p.B, pl.head_groups);
   decode_split_kernel<G, KB, VB, W, NS><<<grid, W * 32, kMaxDynamicSmem, st>>>(p);
   return check_launch("decode split kernel");
@@ -1044,45 +793,11 @@ static int launch_split(const DecodeParams& p0, const Plan& pl, cudaStream_t st)
 
 template <int G, int KB, int VB>
 static int dispatch_shape(const DecodeParams& p, const Plan& pl, cudaStream_t st) {
-  if (pl.warps == 16) return pl.depth == 4 ? launch_split<G, KB, VB, 16, 4>(p, pl, st) : launch_split<G, KB, VB, 16, 3>(p, pl, st);
-  return pl.depth == 6 ? launch_split<G, KB, VB, 8, 6>(p, pl, st) : launch_split<G, KB, VB, 8, 4>(p, pl, st);
-}
-
-template <int G, int KB, int VB, int HPC>
-static int launch_page(const DecodeParams& p0, const Plan& pl, cudaStream_t st) {
-  constexpr int W = 16, NS = 3;
-  static bool configured[64];
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64 || !configured[dev]) {
-    if (cudaFuncSetAttribute(decode_page_kernel<G, KB, VB, W, NS, HPC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             kMaxDynamicSmem) != cudaSuccess)
-      return check_launch("decode: shared memory opt-in");
-    if (dev >= 0 && dev < 64) configured[dev] = true;
-  }
-  DecodeParams p = p0;
-  p.smem_bytes = kMaxDynamicSmem;
-  static const int dbg = getenv("CDA_DECODE_DEBUG") ? atoi(getenv("CDA_DECODE_DEBUG")) : 0;
-  p.debug = dbg;
-  const dim3 grid(pl.splits, p.B, pl.head_groups);
-  decode_page_kernel<G, KB, VB, W, NS, HPC><<<grid, W * 32, kMaxDynamicSmem, st>>>(p);
-  return check_launch("decode page kernel");
-}
-
-template <int G, int KB, int VB>
-static int dispatch_page(const DecodeParams& p, const Plan& pl, cudaStream_t st) {
-  switch (pl.heads_per_cta) {
-    case 8: return launch_page<G, KB, VB, 8>(p, pl, st);
-    case 4: return launch_page<G, KB, VB, 4>(p, pl, st);
-    case 2: return launch_page<G, KB, VB, 2>(p, pl, st);
-    default: return launch_page<G, KB, VB, 1>(p, pl, st);
-  }
+  return launch_split<G, KB, VB, kSplitWarps, kSplitStages>(p, pl, st);
 }
 
 template <int G>
 static int dispatch_bits(const DecodeParams& p, const Plan& pl, int kb, int vb, cudaStream_t st) {
-  static const bool page = getenv("CDA_DECODE_PAGE") && atoi(getenv("CDA_DECODE_PAGE")) == 1;
-  if (page && pl.warps == 16 && kb == 4 && vb == 4) return dispatch_page<G, 4, 4>(p, pl, st);
   if (kb == 4 && vb == 4) return dispatch_shape<G, 4, 4>(p, pl, st);
   if (kb == 4 && vb == 2) return dispatch_shape<G, 4, 2>(p, pl, st);
   if (kb == 2 && vb == 2) return dispatch_shape<G, 2, 2>(p, pl, st);
@@ -1175,7 +890,7 @@ extern "C" int cda_b200_decode(const void* Q, const void* kv_cache, const int32_
   if (rc != CDA_OK) return rc;
   const int64_t rows = static_cast<int64_t>(B) * H_q;
   if (rows > 0x7fffffffLL) return fail(CDA_ERR_N_TOO_LARGE, "decode: B*H_q too large");
-  decode_merge_kernel<<<static_cast<unsigned>(rows), 256, 0, st>>>(po, ml, ml + 1, 2, pl.parts, rows, 1.0f, 0, 1,
+  decode_merge_kernel<<<static_cast<unsigned>(rows), kMergeWarps * 32, 0, st>>>(po, ml, ml + 1, 2, pl.parts, rows, 1.0f, 0, 1,
                                                                   static_cast<__half*>(out), nullptr, nullptr, nullptr);
   return check_launch("decode merge kernel");
 }
@@ -1197,7 +912,7 @@ extern "C" int cda_b200_decode_partial(const void* Q, const void* kv_cache, cons
   if (rc != CDA_OK) return rc;
   const int64_t rows = static_cast<int64_t>(B) * H_q;
   if (rows > 0x7fffffffLL) return fail(CDA_ERR_N_TOO_LARGE, "decode_partial: B*H_q too large");
-  decode_merge_kernel<<<static_cast<unsigned>(rows), 256, 0, st>>>(po, ml, ml + 1, 2, pl.parts, rows, 1.0f, 1, 0, nullptr, O, m, l);
+  decode_merge_kernel<<<static_cast<unsigned>(rows), kMergeWarps * 32, 0, st>>>(po, ml, ml + 1, 2, pl.parts, rows, 1.0f, 1, 0, nullptr, O, m, l);
   return check_launch("decode partial merge kernel");
 }
 
@@ -1208,7 +923,7 @@ extern "C" int cda_b200_merge_partials(const float* O, const float* m, const flo
   if (!O || !m || !l || !out) return fail(CDA_ERR_BAD_ARG, "merge_partials: null pointer");
   if (!aligned16(O) || (reinterpret_cast<uintptr_t>(out) & 7u)) return fail(CDA_ERR_BAD_ALIGN, "merge_partials: misaligned buffer");
   if (R > 0x7fffffffLL) return fail(CDA_ERR_N_TOO_LARGE, "merge_partials: too many rows");
-  decode_merge_kernel<<<static_cast<unsigned>(R), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  decode_merge_kernel<<<static_cast<unsigned>(R), kMergeWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
       O, m, l, 1, S, R, kLog2e, 0, unrotate ? 1 : 0, static_cast<__half*>(out), nullptr, nullptr, nullptr);
   return check_launch("merge_partials");
 }
@@ -1271,7 +986,7 @@ extern "C" int cda_b200_decode_static(const void* Q, const void* kv_cache, const
   Plan pl; float* ml; float* po;
   rc = run_split("decode_static", a, scratch, kStaticScratchBytes, splits, st, &pl, &ml, &po);
   if (rc != CDA_OK) return rc;
-  decode_merge_kernel<<<static_cast<unsigned>(rows), 256, 0, st>>>(po, ml, ml + 1, 2, pl.parts, rows, 1.0f, 0, 1,
+  decode_merge_kernel<<<static_cast<unsigned>(rows), kMergeWarps * 32, 0, st>>>(po, ml, ml + 1, 2, pl.parts, rows, 1.0f, 0, 1,
                                                                   static_cast<__half*>(out), nullptr, nullptr, nullptr);
   return check_launch("decode_static merge kernel");
 }

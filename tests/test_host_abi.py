@@ -97,7 +97,10 @@ def test_split_planning_properties(lib):
         parts = s * (16 // heads_per_cta)
         assert ws == 256 + parts * B * Hkv * 4 * 130 * 4
         assert L.cda_b200_decode_workspace_bytes(B, Hkv * 4, Hkv, n, 3, -1) <= 256 + 3 * (16 // heads_per_cta) * B * Hkv * 4 * 520
-    assert L.cda_b200_decode_plan_splits(32, 8, 65536, -1) == 37      # 32 x 37 CTAs = 8 waves of 148 SMs
+    assert L.cda_b200_decode_plan_splits(32, 8, 65536, -1) == 9       # 288 CTAs: two rounds of 148 SMs, 97 % full
+    assert L.cda_b200_decode_plan_splits(4, 8, 65536, -1) == 37       # 148 CTAs: exactly one round
+    assert L.cda_b200_decode_plan_splits(32, 8, 4096, -1) == 4        # one round; a second would double the fixed cost
+    assert L.cda_b200_decode_plan_splits(1, 8, 4096, -1) == 32        # never below 128 tokens per split
     assert L.cda_b200_decode_plan_splits(0, 8, 16, -1) == lib.CDA_ERR_BAD_ARG
 
 
