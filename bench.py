@@ -2,6 +2,7 @@
 """Decode benchmark: one layer of single-query GQA attention over the paged k4v4 cache.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--batch B] [--ctx N]
+    python bench.py --workload encode|prefill [--steps K] [--warmup W]      (secondary kernels, one GPU)
 
 Workload (N=1): Mistral-7B head geometry (32 query heads, 8 KV heads, d=128, GQA 4), k4v4, B=32 sequences of
 N=65536 tokens, block size 16, 144-byte slots, seeded synthetic data (N(0,1) fp16 with x8 outlier channels in K),
@@ -331,6 +332,122 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+# ---- secondary workloads: paged encode and causal varlen prefill (full-prompt prefill of 8 ragged sequences) ------------------
+
+def prompt_lengths(n_seq=8, lo=512, hi=8192):
+    import random
+    rng = random.Random(0xCDA)
+    return [rng.randint(lo, hi) for _ in range(n_seq)]
+
+
+def measured_peak(key, fallback):
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            return float(json.loads(path.read_text())[key]), "measured"
+        except Exception:
+            pass
+    return fallback, "fallback"
+
+
+def run_prompt_workload(args):
+    """`--workload encode` / `--workload prefill`: one GPU, k4v4, 8 prompts with seeded lengths in [512, 8192].
+
+    encode : K, V (T, 8, 128) fp16 -> 144-byte slots scattered by a shuffled slot mapping; metric GB/s over the
+             algorithmic bytes T * 8 * (2 * 256 + 136) + 4 T.
+    prefill: Q (T, 32, 128) over the encoded cache, causal, bottom-right aligned; metric TFLOP/s over
+             sum_b 4 * H_q * 128 * L_b * (L_b + 1) / 2.
+    """
+    import torch
+    from sub0_b200 import codebook
+    from sub0_b200.kernels_cuda.fa2_cda import fa2_cda_prefill_varlen_v1
+    from sub0_b200.kernels_cuda.wrappers import paged_encode_fused_cuda
+    from sub0_b200 import ops
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    lens = prompt_lengths()
+    T, H_q = sum(lens), H_KV * GROUP
+    g = torch.Generator(device=dev).manual_seed(0xCDA + T)
+    K = torch.randn(T, H_KV, 128, generator=g, device=dev, dtype=torch.float32)
+    K[..., [3, 37, 64, 101]] *= 8.0
+    K = K.to(torch.float16)
+    V = torch.randn(T, H_KV, 128, generator=g, device=dev, dtype=torch.float32).to(torch.float16)
+    Q = torch.randn(T, H_q, 128, generator=g, device=dev, dtype=torch.float32).to(torch.float16)
+    blocks_per = [-(-L // BLOCK) for L in lens]
+    n_blocks = sum(blocks_per)
+    perm = torch.randperm(n_blocks, generator=torch.Generator().manual_seed(0xCDA)).to(torch.int32)
+    bt = torch.zeros(len(lens), max(blocks_per), dtype=torch.int32)
+    slot_parts, at = [], 0
+    for b, L in enumerate(lens):
+        ids = perm[at:at + blocks_per[b]]
+        at += blocks_per[b]
+        bt[b, :blocks_per[b]] = ids
+        pos = torch.arange(L)
+        slot_parts.append(ids[pos // BLOCK].long() * BLOCK + pos % BLOCK)
+    slots = torch.cat(slot_parts).to(torch.int32).to(dev)
+    bt = bt.to(dev)
+    seq_lens = torch.tensor(lens, dtype=torch.int32, device=dev)
+    cu = torch.zeros(len(lens) + 1, dtype=torch.int32)
+    cu[1:] = torch.tensor(lens).cumsum(0)
+    cu = cu.to(dev)
+    cb = codebook.default_codebook(16).to(dev)
+    cache = torch.zeros(n_blocks * BLOCK, H_KV, ops.slot_bytes(4, 4), dtype=torch.uint8, device=dev)
+    out = torch.empty_like(Q)
+    rot = torch.empty(128, 128, device=dev)            # accepted and shape-checked only
+
+    def encode():
+        paged_encode_fused_cuda(K, V, slots, cache, cb_K=cb, cb_V=cb)
+
+    def prefill():
+        fa2_cda_prefill_varlen_v1(Q, cache, bt, cu, seq_lens, out, cb_K=cb, cb_V=cb, rotation_fp32=rot, group_size=GROUP,
+                                  block_size=BLOCK, max_query_len=max(lens), max_seq_len=max(lens), causal=True,
+                                  fuse_fa2_epilogue=True)
+
+    encode()
+    call = encode if args.workload == "encode" else prefill
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)     # written between steps: larger than L2
+    for _ in range(max(args.warmup, 3)):
+        call()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(0)
+    sampler.start()
+    per = []
+    for _ in range(args.steps):
+        flush.fill_(1)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        call()
+        e1.record()
+        torch.cuda.synchronize()
+        per.append(e0.elapsed_time(e1))
+    if len(sampler.samples) < 5:
+        t_end = time.perf_counter() + 0.3
+        while time.perf_counter() < t_end:
+            call()
+            torch.cuda.synchronize()
+    sampler.stop()
+    ms = statistics.mean(per)
+    if args.workload == "encode":
+        units = T * H_KV * (2 * 256 + 136) + 4 * T
+        value, unit, metric = units / (ms * 1e-3) / 1e9, "GB/s", "cda_paged_encode_k4v4_hbm_gbs"
+        peak, src = measured_peak("hbm_gbs", 6650.0)
+        roof = {"bound": "hbm", "achieved": value, "peak": peak, "unit": unit, "frac": value / peak, "peak_source": src,
+                "traffic": None}
+    else:
+        units = sum(4 * H_q * 128 * L * (L + 1) // 2 for L in lens)
+        value, unit, metric = units / (ms * 1e-3) / 1e12, "TFLOP/s", "cda_prefill_k4v4_tflops"
+        peak, src = measured_peak("bf16_tflops", 1590.0)
+        roof = {"bound": "tensor", "achieved": value, "peak": peak, "unit": unit, "frac": value / peak, "peak_source": src,
+                "traffic": None}
+    print(json.dumps({"metric": metric, "value": value, "unit": unit, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+                      "ms_per_step": ms, "ms_min": min(per), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                      "dtype": "f16", "data": "synthetic",
+                      "config": {"workload": f"{args.workload} k4v4, 8 prompts of {lens} tokens (T={T}), H_q={H_q} H_kv={H_KV} d=128 block={BLOCK}",
+                                 "timing": "one call per step, CUDA events", "l2": "256 MiB buffer written between steps"},
+                      "roofline": roof, "gpu_launches": args.steps, "clocks": sampler.summary()}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -340,8 +457,14 @@ def main():
     ap.add_argument("--batch", type=int, default=32)
     ap.add_argument("--ctx", type=int, default=65536)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="decode", choices=["decode", "encode", "prefill"],
+                    help="decode is the headline; encode / prefill time the other two kernels of the path on 8 ragged prompts")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.workload != "decode":
+        if args.impl != "ours" or args.gpus != 1:
+            raise SystemExit("--workload encode/prefill: one GPU, --impl ours only")
+        run_prompt_workload(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
