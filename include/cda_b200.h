@@ -182,6 +182,12 @@ int cda_b200_varlen_fwd_hadamard(const void* Q, const void* k_rot, const void* v
                                  const int32_t* seqused_k, int64_t T, int B, int H_q, int H_kv,
                                  int max_query_len, int max_seq_len, float scale, void* stream);
 
+/* The paged prefill kernel hands tiles between its warps through mbarriers with bounded waits.  A wait that gives up
+ * ends its CTA, leaves that CTA's output rows unwritten and sets a per-device flag that makes later prefill CTAs and
+ * launches return at once.  Returns 1 if the flag is set on the current device, 0 if not, a negative status on a CUDA
+ * error.  Synchronises the device.  (No counterpart in the reference: its kernels report nothing.) */
+int cda_b200_prefill_fault(void);
+
 #ifdef __cplusplus
 }
 #endif

@@ -16,7 +16,7 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libcda_b200.so"
-SOURCES = ["status.cu", "encode.cu", "decode.cu", "prefill.cu"]
+SOURCES = ["status.cu", "encode.cu", "decode.cu", "prefill.cu", "prefill_umma.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC",

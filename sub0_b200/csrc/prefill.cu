@@ -14,6 +14,7 @@
 #include <cmath>
 
 #include "common.cuh"
+#include "prefill_umma.cuh"
 
 namespace cda {
 
@@ -472,17 +473,14 @@ extern "C" int cda_b200_prefill_varlen(const void* Q, const void* kv_cache, cons
   if (static_cast<int64_t>(block_table_stride) * block_size < max_seq_len) return fail(CDA_ERR_BAD_SHAPE, "prefill_varlen: block table row shorter than max_seq_len");
   if (!kv_cache || !block_table || !seq_lens || !cb_K || !cb_V) return fail(CDA_ERR_BAD_ARG, "prefill_varlen: null pointer");
   if (!aligned16(kv_cache)) return fail(CDA_ERR_BAD_ALIGN, "prefill_varlen: cache must be 16-byte aligned");
-  PrefillParams p{};
+  if (H_q / H_kv > 8) return fail(CDA_ERR_UNSUPPORTED, "prefill_varlen: GQA group %d > 8", H_q / H_kv);
+  PrefillUmmaParams p{};
   p.q = static_cast<const __half*>(Q); p.out = static_cast<__half*>(out); p.cu_q = cu_seqlens_q;
   p.cache = static_cast<const uint8_t*>(kv_cache); p.block_table = block_table; p.seq_lens = seq_lens;
-  p.cb_k = cb_K; p.cb_v = cb_V; p.block_size = block_size; p.bt_stride = block_table_stride;
+  p.cb_k = cb_K; p.cb_v = cb_V; p.status = nullptr; p.block_size = block_size; p.bt_stride = block_table_stride;
   p.num_blocks = static_cast<int>(num_slots / block_size);
   p.H_q = H_q; p.H_kv = H_kv; p.group = H_q / H_kv; p.scale_log2 = scale * kLog2e;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (k_bits == 4 && v_bits == 4) return launch_prefill<4, 4, true>(p, max_query_len, B, st);
-  if (k_bits == 4 && v_bits == 2) return launch_prefill<4, 2, true>(p, max_query_len, B, st);
-  if (k_bits == 2 && v_bits == 2) return launch_prefill<2, 2, true>(p, max_query_len, B, st);
-  return launch_prefill<2, 4, true>(p, max_query_len, B, st);
+  return dispatch_prefill_umma(p, k_bits, v_bits, max_query_len, B, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int cda_b200_varlen_fwd_hadamard(const void* Q, const void* k_rot, const void* v_rot, void* out, const int32_t* cu_seqlens_q,

@@ -1,0 +1,27 @@
+// Interface between the C-ABI entry point (prefill.cu) and the tcgen05 prefill kernel (prefill_umma.cu).
+#pragma once
+#include <cstdint>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+namespace cda {
+
+struct PrefillUmmaParams {
+  const __half* q;
+  __half* out;
+  const int32_t* cu_q;
+  const uint8_t* cache;
+  const int32_t* block_table;
+  const int32_t* seq_lens;
+  const float* cb_k;
+  const float* cb_v;
+  int* status;          // device status word or null (bit 0: bad block id, bit 2: a bounded wait gave up)
+  int block_size, bt_stride, num_blocks;
+  int H_q, H_kv, group;
+  float scale_log2;
+};
+
+// Launch the causal varlen prefill over the paged cache.  Grid: (query tiles of 128 / G positions, KV heads, sequences).
+int dispatch_prefill_umma(const PrefillUmmaParams& p, int k_bits, int v_bits, int max_query_len, int B, cudaStream_t st);
+
+}  // namespace cda
