@@ -478,6 +478,8 @@ extern "C" int cda_b200_prefill_varlen(const void* Q, const void* kv_cache, cons
   p.q = static_cast<const __half*>(Q); p.out = static_cast<__half*>(out); p.cu_q = cu_seqlens_q;
   p.cache = static_cast<const uint8_t*>(kv_cache); p.block_table = block_table; p.seq_lens = seq_lens;
   p.cb_k = cb_K; p.cb_v = cb_V; p.status = nullptr; p.block_size = block_size; p.bt_stride = block_table_stride;
+  p.bs_shift = -1;
+  for (int sft = 4; sft < 31; ++sft) if ((1 << sft) == block_size) p.bs_shift = sft;
   p.num_blocks = static_cast<int>(num_slots / block_size);
   p.H_q = H_q; p.H_kv = H_kv; p.group = H_q / H_kv; p.scale_log2 = scale * kLog2e;
   return dispatch_prefill_umma(p, k_bits, v_bits, max_query_len, B, static_cast<cudaStream_t>(stream));

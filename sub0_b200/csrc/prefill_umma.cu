@@ -7,15 +7,21 @@
 // One CTA = 128 rows = (128 / G) consecutive query positions x the G query heads of one KV head, so that a
 // dequantised key/value tile serves the whole GQA group.  Keys are processed 64 at a time:
 //
-//   producer warps (4)   cache slots -> unit-level fp16 tiles in shared memory (128-byte swizzled rows, the layout
-//                        tcgen05.mma reads), norms to side arrays
-//   MMA warp (1 thread)  S = Q K^T (128x64x128) into TMEM, O += P V (128x128x64) into TMEM
-//   softmax warps (4)    thread t owns row t: TMEM -> registers, scale by the key norm, mask, online maximum with lazy
-//                        rescaling of O, exp2, fold the value norm, fp16 P -> shared memory
+//   producer warps (4)   cache slots -> registers (two tiles ahead) -> unit-level fp16 tiles in shared memory (128-byte
+//                        swizzled rows, the layout tcgen05.mma reads), norms to side arrays
+//   MMA warp (1 thread)  S = Q K^T (128x64x128) and O += P V (128x128x64); Q and P are read from tensor memory, only
+//                        the K and V tiles from shared memory
+//   softmax warps (8)    two threads per row (32 keys each): TMEM -> registers, scale by the key norm, mask, online
+//                        maximum with lazy rescaling of O, exp2, fold the value norm, fp16 P -> TMEM over the scores
 //
-// The roles hand tiles over through mbarriers; every wait is bounded (umma.cuh) and a wait that gives up sets bit 2 of
-// the status word and ends the CTA cleanly (TMEM is released).  Two CTAs fit one SM (108 KB shared memory, 256 TMEM
-// columns each), so one CTA's softmax overlaps the other's matrix products.
+// Tensor memory (256 columns): Q [0,64) as fp16 pairs, S [64,128) (P reuses its first 32 columns), O [128,256).
+// Shared memory is the scarce resource (its pipe was 84 % busy when Q and P were shared-memory operands and the
+// code tables had four copies): the tables own 32 KB -- one table with a copy per lane when both codebooks are the
+// same, else two with half the copies -- and gathers are then conflict-free.
+//
+// The roles hand tiles over through mbarriers; every wait is bounded (umma.cuh) and a wait that gives up sets a fault
+// flag and ends the CTA cleanly (TMEM is released).  Two CTAs fit one SM (86 KB shared memory, 256 TMEM columns each),
+// so one CTA's softmax overlaps the other's matrix products.
 #include "common.cuh"
 #include "umma.cuh"
 #include "prefill_umma.cuh"
@@ -30,35 +36,41 @@ namespace pfu {
 
 constexpr int kRows = 128;            // rows of a CTA tile
 constexpr int kKeys = 64;             // keys per tile
-constexpr int kSoftmaxWarps = 4, kProducerWarps = 4;
-constexpr int kThreads = (kSoftmaxWarps + kProducerWarps + 1) * 32;
-constexpr int kTmemCols = 256;        // S0 [0,64)  S1 [64,128)  O [128,256)
+constexpr int kSoftmaxWarps = 8, kProducerWarps = 4, kMmaWarp = kSoftmaxWarps + kProducerWarps;
+constexpr int kThreads = (kMmaWarp + 1) * 32;
+constexpr int kTmemCols = 256;
+constexpr int kColQ = 0, kColS = 64, kColO = 128;
 constexpr float kLazy = 4.0f;         // O is rescaled only when the row maximum grew by more than 2^4
 
 // shared memory map (bytes from the 1024-aligned base)
-constexpr int kOffQ = 0;                       // 2 column blocks x 128 rows x 128 B
-constexpr int kOffK = 32768;                   // 2 stages x (2 column blocks x 64 rows x 128 B)
-constexpr int kOffV = 65536;                   // 2 column blocks x 64 rows x 128 B
-constexpr int kOffP = 81920;                   // 128 rows x 128 B
-constexpr int kOffKn = 98304;                  // 4 x 64 floats: key norm * softmax scale * log2(e) * alpha_k
+constexpr int kOffK = 0;                       // 2 stages x (2 column blocks x 64 rows x 128 B); also stages Q and O rows
+constexpr int kOffV = 32768;                   // 2 column blocks x 64 rows x 128 B
+constexpr int kOffLut = 49152;                 // 32 KB of code tables
+constexpr int kLutBytes = 32768;
+constexpr int kOffKn = kOffLut + kLutBytes;    // 4 x 64 floats: key norm * softmax scale * log2(e) * alpha_k
 constexpr int kOffVn = kOffKn + 1024;          // 4 x 64 floats: value norm
-constexpr int kOffLutK = kOffVn + 1024;        // 4 KB
-constexpr int kOffLutV = kOffLutK + 4096;      // 4 KB
-constexpr int kOffBar = kOffLutV + 4096;       // mbarriers, TMEM address, flags
+constexpr int kOffXch = kOffVn + 1024;         // 2 x 2 x 128 floats: row maxima / sums exchanged between the two threads of a row
+constexpr int kOffBar = kOffXch + 2048;        // mbarriers, TMEM address, flags
 constexpr int kSmemBytes = kOffBar + 256 + 1024;   // + slack for the 1024-byte alignment
 
 // barrier slots (8 bytes each) inside kOffBar
-constexpr int kBarKFull = 0, kBarSFull = 2, kBarVFull = 4, kBarPFull = 5, kBarPvDone = 6, kBarNorms = 7;   // 11 barriers
-constexpr int kOffTmemAddr = 96, kOffAbort = 100;
+constexpr int kBarKFull = 0, kBarKEmpty = 2, kBarSFull = 4, kBarVFull = 5, kBarPFull = 6, kBarPvDone = 7, kBarNorms = 8,
+              kBarXch = 12;   // 14 barriers
+constexpr int kOffTmemAddr = 120, kOffAbort = 124;
 
 __device__ __forceinline__ uint32_t lds32(uint32_t a) {
   uint32_t v;
-  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(a));
+  asm("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(a));
   return v;
 }
 __device__ __forceinline__ uint2 lds64(uint32_t a) {
   uint2 v;
-  asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+  asm("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
   return v;
 }
 __device__ __forceinline__ void sts64(uint32_t a, uint32_t x, uint32_t y) {
@@ -82,36 +94,41 @@ __device__ __forceinline__ uint32_t sw128(uint32_t row, uint32_t chunk) {   // b
   return (row >> 3) * 1024u + (row & 7u) * 128u + ((chunk ^ (row & 7u)) << 4);
 }
 
-// Table entry for one code byte.  4-bit codes: 2 levels (4 bytes), four copies per entry (16-byte stride).  2-bit codes:
-// 4 levels (8 bytes), two copies.
+// Code tables.  One entry per code byte: 4-bit codes -> 2 levels (4 bytes), 2-bit codes -> 4 levels (8 bytes).  An entry
+// is stored `stride / entry bytes` times in a row of `stride` bytes (128 when the table owns the whole 32 KB, else 64),
+// and lane l reads copy l mod copies: with a copy per lane no two lanes ever meet in a bank.
 template <int BITS>
-__device__ __forceinline__ void fill_code_table(uint8_t* lut, const float* __restrict__ cb, float inv_alpha, int tid, int nthreads) {
-  for (int e = tid; e < 256; e += nthreads) {
+__device__ __forceinline__ void fill_code_table(uint8_t* lut, int stride, const float* __restrict__ cb, float inv_alpha, int tid,
+                                                int nthreads) {
+  const int words = stride / 4;                    // 32-bit words per entry row
+  for (int i = tid; i < 256 * words; i += nthreads) {
+    const int e = i / words, w = i - e * words;
+    uint32_t val;
     if (BITS == 4) {
-      const uint32_t w = pack_half2(__ldg(cb + (e >> 4)) * inv_alpha, __ldg(cb + (e & 15)) * inv_alpha);
-      *reinterpret_cast<uint4*>(lut + e * 16) = make_uint4(w, w, w, w);
+      val = pack_half2(__ldg(cb + (e >> 4)) * inv_alpha, __ldg(cb + (e & 15)) * inv_alpha);
     } else {
-      const uint32_t w0 = pack_half2(__ldg(cb + ((e >> 6) & 3)) * inv_alpha, __ldg(cb + ((e >> 4) & 3)) * inv_alpha);
-      const uint32_t w1 = pack_half2(__ldg(cb + ((e >> 2) & 3)) * inv_alpha, __ldg(cb + (e & 3)) * inv_alpha);
-      *reinterpret_cast<uint4*>(lut + e * 16) = make_uint4(w0, w1, w0, w1);
+      val = (w & 1) ? pack_half2(__ldg(cb + ((e >> 2) & 3)) * inv_alpha, __ldg(cb + (e & 3)) * inv_alpha)
+                    : pack_half2(__ldg(cb + ((e >> 6) & 3)) * inv_alpha, __ldg(cb + ((e >> 4) & 3)) * inv_alpha);
     }
+    reinterpret_cast<uint32_t*>(lut)[i] = val;
   }
 }
 
 // Expand 16 bytes of codes (one quad of a slot) of token row `nl` into fp16 chunks of a 64-row tile.
 // tile: shared address of column block 0 (block 1 is 8192 bytes further).  quad: index of the 16 bytes in the row's codes.
+// lut_lane: table address + this lane's copy; stride: bytes per entry row.
 template <int BITS>
-__device__ __forceinline__ void expand_quad(uint32_t tile, uint32_t lut_lane, const uint4& w, int nl, int quad) {
+__device__ __forceinline__ void expand_quad(uint32_t tile, uint32_t lut_lane, uint32_t stride, const uint4& w, int nl, int quad) {
   const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
   if (BITS == 4) {
 #pragma unroll
     for (int wi = 0; wi < 4; ++wi) {
       const uint32_t x = ws[wi];
       uint32_t v[4];
-      v[0] = lds32(lut_lane + ((x << 4) & 0xff0u));
-      v[1] = lds32(lut_lane + ((x >> 4) & 0xff0u));
-      v[2] = lds32(lut_lane + ((x >> 12) & 0xff0u));
-      v[3] = lds32(lut_lane + ((x >> 20) & 0xff0u));
+      v[0] = lds32(lut_lane + (x & 0xffu) * stride);
+      v[1] = lds32(lut_lane + ((x >> 8) & 0xffu) * stride);
+      v[2] = lds32(lut_lane + ((x >> 16) & 0xffu) * stride);
+      v[3] = lds32(lut_lane + (x >> 24) * stride);
       const int c16 = quad * 4 + wi;                       // 16-byte chunk of the row: 8 coordinates
       sts128(tile + (c16 >> 3) * 8192u + sw128(nl, c16 & 7), v[0], v[1], v[2], v[3]);
     }
@@ -122,7 +139,7 @@ __device__ __forceinline__ void expand_quad(uint32_t tile, uint32_t lut_lane, co
 #pragma unroll
       for (int hb = 0; hb < 2; ++hb) {                     // two code bytes = 8 coordinates = one chunk
         const uint32_t b0 = (x >> (16 * hb)) & 0xffu, b1 = (x >> (16 * hb + 8)) & 0xffu;
-        const uint2 lo = lds64(lut_lane + (b0 << 4)), hi = lds64(lut_lane + (b1 << 4));
+        const uint2 lo = lds64(lut_lane + b0 * stride), hi = lds64(lut_lane + b1 * stride);
         const int c16 = quad * 8 + wi * 2 + hb;
         sts128(tile + (c16 >> 3) * 8192u + sw128(nl, c16 & 7), lo.x, lo.y, hi.x, hi.y);
       }
@@ -138,7 +155,8 @@ __global__ void __launch_bounds__(pfu::kThreads, 2) prefill_umma_kernel(const Pr
   using namespace umma;
   constexpr int kPosPerTile = kRows / G;
   constexpr int kSlotBytes = 16 * KB + 16 * VB + 16;
-  constexpr int kQuadsK = KB, kQuadsV = VB;                // 16-byte pieces of a row's codes (64 or 32 bytes)
+  constexpr int kItK = kKeys * KB / 128, kItV = kKeys * VB / 128;   // 16-byte code pieces per producer thread and tile
+  constexpr int kLevK = KB == 4 ? 16 : 4, kLevV = VB == 4 ? 16 : 4;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_addr(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;
@@ -165,26 +183,37 @@ __global__ void __launch_bounds__(pfu::kThreads, 2) prefill_umma_kernel(const Pr
   __shared__ float s_err[64];
   __shared__ int s_idx[64];
   float alpha_k, alpha_v;
-  find_table_scales<(KB == 4 ? 16 : 4), (VB == 4 ? 16 : 4)>(p.cb_k, p.cb_v, s_err, s_idx, alpha_k, alpha_v);
+  find_table_scales<kLevK, kLevV>(p.cb_k, p.cb_v, s_err, s_idx, alpha_k, alpha_v);
+  // One table serves both sides when the codebooks are the same (then their scales are the same too).
+  bool same_cb = KB == VB;
+  if (KB == VB) {
+#pragma unroll
+    for (int i = 0; i < kLevK; ++i) same_cb = same_cb && __ldg(p.cb_k + i) == __ldg(p.cb_v + i);
+  }
+  const uint32_t lut_stride = same_cb ? 128u : 64u;
+  const uint32_t lutv_off = same_cb ? 0u : static_cast<uint32_t>(kLutBytes / 2);
 
   // ---- set-up: barriers, TMEM, tables, rotated queries -----------------------------------------------------------------
   if (tid == 0) {
     mbar_init(bar(kBarKFull), kProducerWarps); mbar_init(bar(kBarKFull + 1), kProducerWarps);
-    mbar_init(bar(kBarSFull), 1); mbar_init(bar(kBarSFull + 1), 1);
+    mbar_init(bar(kBarKEmpty), 1); mbar_init(bar(kBarKEmpty + 1), 1);
+    mbar_init(bar(kBarSFull), 1);
     mbar_init(bar(kBarVFull), kProducerWarps);
     mbar_init(bar(kBarPFull), kSoftmaxWarps);
     mbar_init(bar(kBarPvDone), 1);
     for (int i = 0; i < 4; ++i) mbar_init(bar(kBarNorms + i), kProducerWarps);
+    mbar_init(bar(kBarXch), kSoftmaxWarps); mbar_init(bar(kBarXch + 1), kSoftmaxWarps);
     *abort_flag = 0;
     mbar_init_fence();
   }
-  if (warp == kSoftmaxWarps + kProducerWarps) {
+  if (warp == kMmaWarp) {
     tmem_alloc(base + kOffBar + kOffTmemAddr, kTmemCols);
     tmem_relinquish();
   }
-  fill_code_table<KB>(sm + kOffLutK, p.cb_k, 1.0f / alpha_k, tid, kThreads);
-  fill_code_table<VB>(sm + kOffLutV, p.cb_v, 1.0f / alpha_v, tid, kThreads);
-  for (int t = warp; t < kRows; t += kThreads / 32) {   // one warp per row: load, rotate, store as the A operand of Q K^T
+  fill_code_table<KB>(sm + kOffLut, lut_stride, p.cb_k, 1.0f / alpha_k, tid, kThreads);
+  if (!same_cb) fill_code_table<VB>(sm + kOffLut + lutv_off, lut_stride, p.cb_v, 1.0f / alpha_v, tid, kThreads);
+  // Q: one warp per row loads, rotates and parks the fp16 row in the staging area (256-byte rows, chunk XOR (row & 15))
+  for (int t = warp; t < kRows; t += kThreads / 32) {
     const int pos = p0 + t / G, hl = t % G;
     float v[4] = {0.f, 0.f, 0.f, 0.f};
     if (pos < q_len && hl < g) {
@@ -193,54 +222,85 @@ __global__ void __launch_bounds__(pfu::kThreads, 2) prefill_umma_kernel(const Pr
 #pragma unroll
       for (int i = 0; i < 4; ++i) v[i] *= kRsqrtD;
     }
-    const uint32_t dst = base + kOffQ + (lane >> 4) * 16384u + sw128(t, (lane & 15) >> 1) + (lane & 1) * 8u;
     const uint2 h = pack_half4(v);
-    sts64(dst, h.x, h.y);
+    sts64(base + kOffK + t * 256u + ((static_cast<uint32_t>(lane >> 1) ^ (t & 15u)) << 4) + (lane & 1) * 8u, h.x, h.y);
   }
-  fence_async_smem();
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(sm + kOffBar + kOffTmemAddr);
+  if (warp < kSoftmaxWarps) {   // ... and from there into tensor memory: row t in lane t, coordinates 2c, 2c+1 in column c
+    const int quarter = warp & 3, half = warp >> 2, t = quarter * 32 + lane;
+    uint32_t qv[32];
+#pragma unroll
+    for (int ch = 0; ch < 8; ++ch) {
+      const uint32_t chunk = static_cast<uint32_t>(8 * half + ch);
+      const uint4 x = lds128(base + kOffK + t * 256u + ((chunk ^ (t & 15u)) << 4));
+      qv[4 * ch] = x.x; qv[4 * ch + 1] = x.y; qv[4 * ch + 2] = x.z; qv[4 * ch + 3] = x.w;
+    }
+    tmem_st32(tmem + (static_cast<uint32_t>(quarter * 32) << 16) + kColQ + 32 * half, qv);
+    tmem_wait_st();
+  }
+  tc_fence_before_sync();
+  __syncthreads();            // the staging area becomes the K stages; Q is in place for the first Q K^T
+  tc_fence_after_sync();
 
   if (warp < kSoftmaxWarps) {
-    // ================= softmax: thread t owns row t =====================================================================
-    const int t = tid;
+    // ================= softmax: two threads per row, 32 of the tile's 64 keys each ================================================
+    const int quarter = warp & 3, half = warp >> 2;          // TMEM lane quarter of this warp; which 32 keys / 64 O columns
+    const int t = quarter * 32 + lane;                       // row
     const int q_pos = q_offset + p0 + t / G;                 // key index of the diagonal for this row
-    const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+    const uint32_t lane_base = tmem + (static_cast<uint32_t>(quarter * 32) << 16);
+    float* xch = reinterpret_cast<float*>(sm + kOffXch);     // [2 parities][2 halves][128 rows]
     float m_used = -INFINITY, l_run = 0.f;
     bool alive = true;
-    for (int j = 0; j < n_tiles && alive; ++j) {
-      const uint32_t s_tmem = lane_base + (j & 1) * kKeys;
-      const float* kn = reinterpret_cast<const float*>(sm + kOffKn) + (j & 3) * kKeys;
-      const float* vn = reinterpret_cast<const float*>(sm + kOffVn) + (j & 3) * kKeys;
-      // the norms come straight from the producers (slot j & 3 is rewritten only for tile j + 4), the scores from the MMA
-      alive = warp_wait(bar(kBarNorms + (j & 3)), (j >> 2) & 1, abort_flag) &&
-              warp_wait(bar(kBarSFull + (j & 1)), (j >> 1) & 1, abort_flag);
+    for (int j = 0; j < n_tiles; ++j) {
+      const float4* kn4 = reinterpret_cast<const float4*>(sm + kOffKn + ((j & 3) * kKeys + 32 * half) * 4);
+      const float4* vn4 = reinterpret_cast<const float4*>(sm + kOffVn + ((j & 3) * kKeys + 32 * half) * 4);
+      // the norms come straight from the producers (slot j & 3 is rewritten only for tile j + 4), the scores from the MMA;
+      // Q K^T of tile j was issued behind P V of tile j - 1, so O is at rest as well
+      alive = warp_wait(bar(kBarNorms + (j & 3)), (j >> 2) & 1, abort_flag) && warp_wait(bar(kBarSFull), j & 1, abort_flag);
       if (!alive) break;
       tc_fence_after_sync();
-      const int key0 = j * kKeys;
-      const bool diag = key0 + kKeys - 1 > q_offset + p0;    // some row of the tile masks some key of this tile
-
-      // pass 1: row maximum over the 64 scores (two 32-column reads; the second half stays in registers)
-      uint32_t sa[32], sb[32];
-      float mx = -INFINITY;
-      tmem_ld32(s_tmem, sa);
-      tmem_ld32(s_tmem + 32, sb);
+      const int key0 = j * kKeys + 32 * half;
+      uint32_t s[32];
+      tmem_ld32(lane_base + kColS + 32 * half, s);
       tmem_wait_ld();
+      float mx = -INFINITY;
+      if (key0 + 31 > q_offset + p0) {                       // some row of the tile masks some of these keys
 #pragma unroll
-      for (int c = 0; c < 32; ++c) {
-        float x = __uint_as_float(sa[c]) * kn[c];
-        if (diag && key0 + c > q_pos) x = -INFINITY;
-        mx = fmaxf(mx, x);
-      }
+        for (int c4 = 0; c4 < 8; ++c4) {
+          const float4 n4 = kn4[c4];
+          const float nn[4] = {n4.x, n4.y, n4.z, n4.w};
 #pragma unroll
-      for (int c = 0; c < 32; ++c) {
-        float x = __uint_as_float(sb[c]) * kn[32 + c];
-        if (diag && key0 + 32 + c > q_pos) x = -INFINITY;
-        sb[c] = __float_as_uint(x);
-        mx = fmaxf(mx, x);
+          for (int i = 0; i < 4; ++i) {
+            float x = __uint_as_float(s[4 * c4 + i]) * nn[i];
+            x = key0 + 4 * c4 + i > q_pos ? -INFINITY : x;
+            s[4 * c4 + i] = __float_as_uint(x);
+            mx = fmaxf(mx, x);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int c4 = 0; c4 < 8; ++c4) {
+          const float4 n4 = kn4[c4];
+          const float nn[4] = {n4.x, n4.y, n4.z, n4.w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float x = __uint_as_float(s[4 * c4 + i]) * nn[i];
+            s[4 * c4 + i] = __float_as_uint(x);
+            mx = fmaxf(mx, x);
+          }
+        }
       }
+      // the row maximum needs the other half's keys; past this barrier both threads hold their scores in registers,
+      // so P may overwrite the score columns
+      xch[((j & 1) * 2 + half) * kRows + t] = mx;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(kBarXch + (j & 1)));
+      alive = warp_wait(bar(kBarXch + (j & 1)), (j >> 1) & 1, abort_flag);
+      if (!alive) break;
+      mx = fmaxf(mx, xch[((j & 1) * 2 + (half ^ 1)) * kRows + t]);
       float factor = 1.0f;
       if (mx > m_used + kLazy || m_used == -INFINITY) {      // tile 0 always lands here (key 0 is never masked)
         const float m_new = fmaxf(m_used, mx);
@@ -250,58 +310,50 @@ __global__ void __launch_bounds__(pfu::kThreads, 2) prefill_umma_kernel(const Pr
       }
       const bool rescale = j > 0 && __any_sync(0xffffffffu, factor != 1.0f);
 
-      // second half -> probabilities (registers), then the first half again from TMEM
-      uint32_t pk[32];
+      uint32_t pk[16];
 #pragma unroll
-      for (int c = 0; c < 32; c += 2) {
-        const float e0 = fast_exp2(__uint_as_float(sb[c]) - m_used), e1 = fast_exp2(__uint_as_float(sb[c + 1]) - m_used);
-        l_run += e0 + e1;
-        pk[16 + c / 2] = pack_half2(e0 * vn[32 + c], e1 * vn[32 + c + 1]);
-      }
-#pragma unroll
-      for (int c = 0; c < 32; c += 2) {
-        float x0 = __uint_as_float(sa[c]) * kn[c], x1 = __uint_as_float(sa[c + 1]) * kn[c + 1];
-        if (diag && key0 + c > q_pos) x0 = -INFINITY;
-        if (diag && key0 + c + 1 > q_pos) x1 = -INFINITY;
-        const float e0 = fast_exp2(x0 - m_used), e1 = fast_exp2(x1 - m_used);
-        l_run += e0 + e1;
-        pk[c / 2] = pack_half2(e0 * vn[c], e1 * vn[c + 1]);
-      }
-
-      if (j > 0) {   // P and O belong to the previous P V product until it has completed
-        alive = warp_wait(bar(kBarPvDone), (j - 1) & 1, abort_flag);
-        if (!alive) break;
-        tc_fence_after_sync();
+      for (int c4 = 0; c4 < 8; ++c4) {
+        const float4 n4 = vn4[c4];
+        const float e0 = fast_exp2(__uint_as_float(s[4 * c4]) - m_used), e1 = fast_exp2(__uint_as_float(s[4 * c4 + 1]) - m_used);
+        const float e2 = fast_exp2(__uint_as_float(s[4 * c4 + 2]) - m_used), e3 = fast_exp2(__uint_as_float(s[4 * c4 + 3]) - m_used);
+        l_run += (e0 + e1) + (e2 + e3);
+        pk[2 * c4] = pack_half2(e0 * n4.x, e1 * n4.y);
+        pk[2 * c4 + 1] = pack_half2(e2 * n4.z, e3 * n4.w);
       }
       if (rescale) {
 #pragma unroll 1
-        for (int ch = 0; ch < 4; ++ch) {
+        for (int ch = 0; ch < 2; ++ch) {
           uint32_t o[32];
-          tmem_ld32(lane_base + 128 + 32 * ch, o);
+          tmem_ld32(lane_base + kColO + 64 * half + 32 * ch, o);
           tmem_wait_ld();
 #pragma unroll
           for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * factor);
-          tmem_st32(lane_base + 128 + 32 * ch, o);
+          tmem_st32(lane_base + kColO + 64 * half + 32 * ch, o);
         }
-        tmem_wait_st();
       }
-      const uint32_t prow = base + kOffP;
-#pragma unroll
-      for (int ch = 0; ch < 8; ++ch) sts128(prow + sw128(t, ch), pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
-      fence_async_smem();
+      tmem_st16(lane_base + kColS + 16 * half, pk);          // keys 2c, 2c+1 of the tile in column c
+      tmem_wait_st();
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(kBarPFull));
     }
-    // ---- epilogue part 1: normalised fp16 row of O into the (now unused) Q area, 256-byte rows, chunk XOR (t & 15) ------
+    // ---- epilogue part 1: normalised fp16 row of O into the staging area, 256-byte rows, chunk XOR (t & 15) --------------
+    if (alive) {   // the row sum needs the other half's keys (slot and phase follow on from the loop's use of the barrier)
+      const int j = n_tiles;
+      xch[((j & 1) * 2 + half) * kRows + t] = l_run;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(kBarXch + (j & 1)));
+      alive = warp_wait(bar(kBarXch + (j & 1)), (j >> 1) & 1, abort_flag);
+      if (alive) l_run += xch[((j & 1) * 2 + (half ^ 1)) * kRows + t];
+    }
     if (alive) alive = warp_wait(bar(kBarPvDone), (n_tiles - 1) & 1, abort_flag);
     if (alive) {
       tc_fence_after_sync();
       const float inv = alpha_v / fmaxf(l_run, 1e-30f);
 #pragma unroll 1
-      for (int ch = 0; ch < 4; ++ch) {
+      for (int ch = 0; ch < 2; ++ch) {
         uint32_t o[32];
-        tmem_ld32(lane_base + 128 + 32 * ch, o);
+        tmem_ld32(lane_base + kColO + 64 * half + 32 * ch, o);
         tmem_wait_ld();
 #pragma unroll
         for (int c8 = 0; c8 < 4; ++c8) {
@@ -309,8 +361,8 @@ __global__ void __launch_bounds__(pfu::kThreads, 2) prefill_umma_kernel(const Pr
 #pragma unroll
           for (int i = 0; i < 4; ++i)
             h[i] = pack_half2(__uint_as_float(o[8 * c8 + 2 * i]) * inv, __uint_as_float(o[8 * c8 + 2 * i + 1]) * inv);
-          const uint32_t chunk = static_cast<uint32_t>(ch * 4 + c8);
-          sts128(base + kOffQ + t * 256u + ((chunk ^ (t & 15u)) << 4), h[0], h[1], h[2], h[3]);
+          const uint32_t chunk = static_cast<uint32_t>(8 * half + ch * 4 + c8);
+          sts128(base + kOffK + t * 256u + ((chunk ^ (t & 15u)) << 4), h[0], h[1], h[2], h[3]);
         }
       }
     }
@@ -318,8 +370,9 @@ __global__ void __launch_bounds__(pfu::kThreads, 2) prefill_umma_kernel(const Pr
   } else if (warp < kSoftmaxWarps + kProducerWarps) {
     // ================= producers: slots -> unit-level fp16 tiles ============================================================
     const int pt = tid - kSoftmaxWarps * 32;                 // 0..127
-    const uint32_t lutk_lane = base + kOffLutK + (KB == 4 ? (lane & 3) * 4u : (lane & 1) * 8u);
-    const uint32_t lutv_lane = base + kOffLutV + (VB == 4 ? (lane & 3) * 4u : (lane & 1) * 8u);
+    const uint32_t k_copies = lut_stride / (KB == 4 ? 4u : 8u), v_copies = lut_stride / (VB == 4 ? 4u : 8u);
+    const uint32_t lutk_lane = base + kOffLut + (lane & (k_copies - 1)) * (KB == 4 ? 4u : 8u);
+    const uint32_t lutv_lane = base + kOffLut + lutv_off + (lane & (v_copies - 1)) * (VB == 4 ? 4u : 8u);
     const int32_t* bt_row = p.block_table + static_cast<int64_t>(b) * p.bt_stride;
     const int64_t row_stride = static_cast<int64_t>(p.H_kv) * kSlotBytes;
     const float kscale = p.scale_log2 * alpha_k;
@@ -327,56 +380,79 @@ __global__ void __launch_bounds__(pfu::kThreads, 2) prefill_umma_kernel(const Pr
 
     auto slot_ptr = [&](int nl, int key0) -> const uint8_t* {
       const int n = min(key0 + nl, seq_len - 1);             // keys past the end are masked later; read a valid slot
-      int blk = __ldg(bt_row + n / p.block_size);
+      const int bi = p.bs_shift >= 0 ? n >> p.bs_shift : n / p.block_size;
+      const int in_block = n - bi * p.block_size;
+      int blk = __ldg(bt_row + bi);
       if (static_cast<unsigned>(blk) >= static_cast<unsigned>(p.num_blocks)) { bad_block = true; blk = 0; }
-      return p.cache + (static_cast<int64_t>(blk) * p.block_size + n % p.block_size) * row_stride + kvh * kSlotBytes;
+      return p.cache + (static_cast<int64_t>(blk) * p.block_size + in_block) * row_stride + kvh * kSlotBytes;
     };
-    auto produce_k = [&](int j) {
+    // Slot words travel through registers and are fetched two tiles before they are expanded (two register sets, used
+    // alternately), so that the global-memory latency lies behind a whole tile of work.
+    struct KRegs { uint4 w[kItK]; float2 n[kItK]; };
+    struct VRegs { uint4 w[kItV]; };
+    auto load_k = [&](int j, KRegs& r) {
+      if (j >= n_tiles) return;
+#pragma unroll
+      for (int it = 0; it < kItK; ++it) {
+        const int x = pt + 128 * it, nl = x / KB, quad = x % KB;
+        const uint8_t* src = slot_ptr(nl, j * kKeys);
+        r.w[it] = __ldg(reinterpret_cast<const uint4*>(src + 16 * quad));
+        if (quad == 0) r.n[it] = __ldg(reinterpret_cast<const float2*>(src + 16 * KB + 16 * VB));
+      }
+    };
+    auto load_v = [&](int j, VRegs& r) {
+      if (j >= n_tiles) return;
+#pragma unroll
+      for (int it = 0; it < kItV; ++it) {
+        const int x = pt + 128 * it, nl = x / VB, quad = x % VB;
+        r.w[it] = __ldg(reinterpret_cast<const uint4*>(slot_ptr(nl, j * kKeys) + 16 * KB + 16 * quad));
+      }
+    };
+    auto expand_k = [&](int j, const KRegs& r) {
       const uint32_t tile = base + kOffK + (j & 1) * 16384u;
       float* kn = reinterpret_cast<float*>(sm + kOffKn) + (j & 3) * kKeys;
       float* vn = reinterpret_cast<float*>(sm + kOffVn) + (j & 3) * kKeys;
 #pragma unroll
-      for (int it = 0; it < kKeys * kQuadsK / 128; ++it) {
-        const int x = pt + 128 * it, nl = x / kQuadsK, quad = x % kQuadsK;
-        const uint8_t* src = slot_ptr(nl, j * kKeys);
-        const uint4 w = __ldg(reinterpret_cast<const uint4*>(src + 16 * quad));
-        if (quad == 0) {
-          const float2 nrm = __ldg(reinterpret_cast<const float2*>(src + 16 * KB + 16 * VB));
-          kn[nl] = nrm.x * kscale;
-          vn[nl] = nrm.y;
-        }
-        expand_quad<KB>(tile, lutk_lane, w, nl, quad);
+      for (int it = 0; it < kItK; ++it) {
+        const int x = pt + 128 * it, nl = x / KB, quad = x % KB;
+        if (quad == 0) { kn[nl] = r.n[it].x * kscale; vn[nl] = r.n[it].y; }
+        expand_quad<KB>(tile, lutk_lane, lut_stride, r.w[it], nl, quad);
       }
       fence_async_smem();
       __syncwarp();
       if (lane == 0) { mbar_arrive(bar(kBarNorms + (j & 3))); mbar_arrive(bar(kBarKFull + (j & 1))); }
     };
-    auto produce_v = [&](int j) {
-      const uint32_t tile = base + kOffV;
+    auto expand_v = [&](int j, const VRegs& r) {
 #pragma unroll
-      for (int it = 0; it < kKeys * kQuadsV / 128; ++it) {
-        const int x = pt + 128 * it, nl = x / kQuadsV, quad = x % kQuadsV;
-        const uint8_t* src = slot_ptr(nl, j * kKeys);
-        const uint4 w = __ldg(reinterpret_cast<const uint4*>(src + 16 * KB + 16 * quad));
-        expand_quad<VB>(tile, lutv_lane, w, nl, quad);
+      for (int it = 0; it < kItV; ++it) {
+        const int x = pt + 128 * it, nl = x / VB, quad = x % VB;
+        expand_quad<VB>(base + kOffV, lutv_lane, lut_stride, r.w[it], nl, quad);
       }
       fence_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(kBarVFull));
     };
-
-    produce_k(0);
-    if (n_tiles > 1) produce_k(1);
-    produce_v(0);
-    for (int j = 1; j < n_tiles && alive; ++j) {
-      if (j + 1 < n_tiles) {                                 // stage (j+1)&1 is free once Q K^T of tile j-1 has completed
-        alive = warp_wait(bar(kBarSFull + ((j + 1) & 1)), ((j - 1) >> 1) & 1, abort_flag);
-        if (!alive) break;
-        produce_k(j + 1);
+    // step j: fetch K of tile j+2 and V of tile j+1, then expand K of tile j+1 and V of tile j
+    auto step = [&](int j, KRegs& k_fetch, VRegs& v_fetch, const KRegs& k_exp, const VRegs& v_exp) -> bool {
+      load_k(j + 2, k_fetch);
+      load_v(j + 1, v_fetch);
+      if (j + 1 < n_tiles) {
+        if (j >= 1 && !warp_wait(bar(kBarKEmpty + ((j + 1) & 1)), ((j - 1) >> 1) & 1, abort_flag)) return false;   // Q K^T of tile j-1 done
+        expand_k(j + 1, k_exp);
       }
-      alive = warp_wait(bar(kBarPvDone), (j - 1) & 1, abort_flag);   // the V tile is free once P V of tile j-1 has completed
-      if (!alive) break;
-      produce_v(j);
+      if (j >= 1 && !warp_wait(bar(kBarPvDone), (j - 1) & 1, abort_flag)) return false;   // P V of tile j-1 done: V tile free
+      expand_v(j, v_exp);
+      return true;
+    };
+    KRegs ka, kb;
+    VRegs va, vb;
+    load_k(0, ka);
+    load_v(0, va);
+    load_k(1, kb);
+    expand_k(0, ka);
+    for (int j = 0; j < n_tiles && alive; j += 2) {
+      alive = step(j, ka, vb, kb, va);
+      if (alive && j + 1 < n_tiles) alive = step(j + 1, kb, va, ka, vb);
     }
     if (bad_block && p.status) atomicOr(p.status, 1);
   } else {
@@ -384,17 +460,16 @@ __global__ void __launch_bounds__(pfu::kThreads, 2) prefill_umma_kernel(const Pr
     if (lane == 0) {
       constexpr uint32_t idesc_qk = instr_desc_f16(kRows, kKeys, false, false);
       constexpr uint32_t idesc_pv = instr_desc_f16(kRows, kHeadDim, false, true);
-      const uint32_t o_tmem = tmem + 128;
       bool alive = true;
       auto issue_qk = [&](int j) {
         const uint32_t ktile = base + kOffK + (j & 1) * 16384u;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
-          const uint64_t a = smem_desc_sw128(base + kOffQ + (ks >> 2) * 16384u + (ks & 3) * 32u, 16, 1024);
           const uint64_t bd = smem_desc_sw128(ktile + (ks >> 2) * 8192u + (ks & 3) * 32u, 16, 1024);
-          mma_ss(tmem + (j & 1) * kKeys, a, bd, idesc_qk, ks > 0 ? 1u : 0u);
+          mma_ts(tmem + kColS, tmem + kColQ + 8 * ks, bd, idesc_qk, ks > 0 ? 1u : 0u);
         }
-        mma_commit(bar(kBarSFull + (j & 1)));
+        mma_commit(bar(kBarSFull));
+        mma_commit(bar(kBarKEmpty + (j & 1)));
       };
       alive = mbar_wait(bar(kBarKFull), 0, abort_flag);
       if (alive) {
@@ -402,22 +477,21 @@ __global__ void __launch_bounds__(pfu::kThreads, 2) prefill_umma_kernel(const Pr
         issue_qk(0);
       }
       for (int j = 0; j < n_tiles && alive; ++j) {
-        if (j + 1 < n_tiles) {
-          alive = mbar_wait(bar(kBarKFull + ((j + 1) & 1)), ((j + 1) >> 1) & 1, abort_flag);
-          if (!alive) break;
-          tc_fence_after_sync();
-          issue_qk(j + 1);
-        }
         alive = mbar_wait(bar(kBarVFull), j & 1, abort_flag) && mbar_wait(bar(kBarPFull), j & 1, abort_flag);
         if (!alive) break;
         tc_fence_after_sync();
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) {
-          const uint64_t a = smem_desc_sw128(base + kOffP + ks * 32u, 16, 1024);
           const uint64_t bd = smem_desc_sw128(base + kOffV + ks * 2048u, 8192, 1024);
-          mma_ss(o_tmem, a, bd, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+          mma_ts(tmem + kColO, tmem + kColS + 8 * ks, bd, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
         }
         mma_commit(bar(kBarPvDone));
+        if (j + 1 < n_tiles) {   // the scores of the next tile overwrite P: issued behind P V, executed behind it
+          alive = mbar_wait(bar(kBarKFull + ((j + 1) & 1)), ((j + 1) >> 1) & 1, abort_flag);
+          if (!alive) break;
+          tc_fence_after_sync();
+          issue_qk(j + 1);
+        }
       }
       if (alive) mbar_wait(bar(kBarPvDone), (n_tiles - 1) & 1, abort_flag);   // nothing in flight when TMEM is released
     }
@@ -432,8 +506,9 @@ __global__ void __launch_bounds__(pfu::kThreads, 2) prefill_umma_kernel(const Pr
     for (int t = warp; t < kRows; t += kThreads / 32) {
       const int pos = p0 + t / G, hl = t % G;
       if (pos >= q_len || hl >= g) continue;
-      const uint32_t src = base + kOffQ + t * 256u + ((static_cast<uint32_t>(lane >> 1) ^ (t & 15u)) << 4) + (lane & 1) * 8u;
-      const uint2 raw = lds64(src);
+      const uint32_t src = base + kOffK + t * 256u + ((static_cast<uint32_t>(lane >> 1) ^ (t & 15u)) << 4) + (lane & 1) * 8u;
+      const uint4 raw4 = lds128(src & ~15u);   // (volatile read: the row was written by another warp)
+      const uint2 raw = (lane & 1) ? make_uint2(raw4.z, raw4.w) : make_uint2(raw4.x, raw4.y);
       float v[4];
       unpack_half4(raw, v);
       fht128_warp(v, lane);
@@ -446,7 +521,7 @@ __global__ void __launch_bounds__(pfu::kThreads, 2) prefill_umma_kernel(const Pr
     if (p.status) atomicOr(p.status, 4);
   }
   __syncthreads();
-  if (warp == kSoftmaxWarps + kProducerWarps) {
+  if (warp == kMmaWarp) {
     tc_fence_after_sync();
     tmem_dealloc(tmem, kTmemCols);
   }

@@ -16,7 +16,7 @@ struct PrefillUmmaParams {
   const float* cb_k;
   const float* cb_v;
   int* status;          // device status word or null (bit 0: bad block id, bit 2: a bounded wait gave up)
-  int block_size, bt_stride, num_blocks;
+  int block_size, bs_shift, bt_stride, num_blocks;   // bs_shift: log2(block_size), or -1 if it is not a power of two
   int H_q, H_kv, group;
   float scale_log2;
 };
