@@ -20,7 +20,7 @@
 // same, else two with half the copies -- and gathers are then conflict-free.
 //
 // The roles hand tiles over through mbarriers; every wait is bounded (umma.cuh) and a wait that gives up sets a fault
-// flag and ends the CTA cleanly (TMEM is released).  Two CTAs fit one SM (86 KB shared memory, 256 TMEM columns each),
+// flag and ends the CTA cleanly (TMEM is released).  Two CTAs fit one SM (102 KB shared memory, 256 TMEM columns each),
 // so one CTA's softmax overlaps the other's matrix products.
 #include "common.cuh"
 #include "umma.cuh"
@@ -44,8 +44,8 @@ constexpr float kLazy = 4.0f;         // O is rescaled only when the row maximum
 
 // shared memory map (bytes from the 1024-aligned base)
 constexpr int kOffK = 0;                       // 2 stages x (2 column blocks x 64 rows x 128 B); also stages Q and O rows
-constexpr int kOffV = 32768;                   // 2 column blocks x 64 rows x 128 B
-constexpr int kOffLut = 49152;                 // 32 KB of code tables
+constexpr int kOffV = 32768;                   // 2 stages x (2 column blocks x 64 rows x 128 B)
+constexpr int kOffLut = 65536;                 // 32 KB of code tables
 constexpr int kLutBytes = 32768;
 constexpr int kOffKn = kOffLut + kLutBytes;    // 4 x 64 floats: key norm * softmax scale * log2(e) * alpha_k
 constexpr int kOffVn = kOffKn + 1024;          // 4 x 64 floats: value norm
@@ -54,9 +54,9 @@ constexpr int kOffBar = kOffXch + 2048;        // mbarriers, TMEM address, flags
 constexpr int kSmemBytes = kOffBar + 256 + 1024;   // + slack for the 1024-byte alignment
 
 // barrier slots (8 bytes each) inside kOffBar
-constexpr int kBarKFull = 0, kBarKEmpty = 2, kBarSFull = 4, kBarVFull = 5, kBarPFull = 6, kBarPvDone = 7, kBarNorms = 8,
-              kBarXch = 12;   // 14 barriers
-constexpr int kOffTmemAddr = 120, kOffAbort = 124;
+constexpr int kBarKFull = 0, kBarKEmpty = 2, kBarSFull = 4, kBarVFull = 5, kBarPFull = 7, kBarPvDone = 8, kBarNorms = 9,
+              kBarVEmpty = 13;   // 15 barriers
+constexpr int kOffTmemAddr = 120, kOffAbort = 124, kOffVerdict = 128;   // verdict words: 2 per waiting group
 
 __device__ __forceinline__ uint32_t lds32(uint32_t a) {
   uint32_t v;
@@ -84,11 +84,28 @@ __device__ __forceinline__ void unpack_half4(const uint2& raw, float (&v)[4]) {
   const float2 fa = __half22float2(a), fb = __half22float2(b);
   v[0] = fa.x; v[1] = fa.y; v[2] = fb.x; v[3] = fb.y;
 }
-// mbar_wait with a warp-uniform result (the callers go on to warp-synchronous instructions)
-__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  const bool ok = umma::mbar_wait(bar, parity, abort_flag);
-  return __all_sync(0xffffffffu, ok);
+// A group of warps waits for an mbarrier phase: only lane 0 of the group's first warp polls, the others are parked on
+// a named hardware barrier (a parked warp takes no issue slots from the warps that are working).  The poller always
+// arrives at the named barrier -- its own wait is bounded -- and publishes its verdict in one of two words used
+// alternately (it can be at most one call ahead of the slowest reader), so the result is the same for every thread
+// of the group and nobody is left behind at a later barrier.
+__device__ __forceinline__ void named_barrier(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
+struct GroupWaiter {
+  volatile int* verdict;     // two words in shared memory
+  volatile int* abort_flag;
+  int id, nthreads, turn;
+  bool leader;               // lane 0 of the group's first warp
+  __device__ __forceinline__ bool wait(uint32_t bar, uint32_t parity) {
+    if (leader) verdict[turn] = umma::mbar_wait(bar, parity, abort_flag) ? 1 : 0;
+    named_barrier(id, nthreads);
+    const bool ok = verdict[turn] != 0;
+    turn ^= 1;
+    return ok;
+  }
+};
+constexpr int kBarIdSoftmax = 1, kBarIdProducer = 2;
 
 __device__ __forceinline__ uint32_t sw128(uint32_t row, uint32_t chunk) {   // byte offset inside a block of 128-byte rows
   return (row >> 3) * 1024u + (row & 7u) * 128u + ((chunk ^ (row & 7u)) << 4);
@@ -198,11 +215,11 @@ __global__ void __launch_bounds__(pfu::kThreads, 2) prefill_umma_kernel(const Pr
     mbar_init(bar(kBarKFull), kProducerWarps); mbar_init(bar(kBarKFull + 1), kProducerWarps);
     mbar_init(bar(kBarKEmpty), 1); mbar_init(bar(kBarKEmpty + 1), 1);
     mbar_init(bar(kBarSFull), 1);
-    mbar_init(bar(kBarVFull), kProducerWarps);
+    mbar_init(bar(kBarVFull), kProducerWarps); mbar_init(bar(kBarVFull + 1), kProducerWarps);
+    mbar_init(bar(kBarVEmpty), 1); mbar_init(bar(kBarVEmpty + 1), 1);
     mbar_init(bar(kBarPFull), kSoftmaxWarps);
     mbar_init(bar(kBarPvDone), 1);
     for (int i = 0; i < 4; ++i) mbar_init(bar(kBarNorms + i), kProducerWarps);
-    mbar_init(bar(kBarXch), kSoftmaxWarps); mbar_init(bar(kBarXch + 1), kSoftmaxWarps);
     *abort_flag = 0;
     mbar_init_fence();
   }
@@ -254,12 +271,14 @@ __global__ void __launch_bounds__(pfu::kThreads, 2) prefill_umma_kernel(const Pr
     float* xch = reinterpret_cast<float*>(sm + kOffXch);     // [2 parities][2 halves][128 rows]
     float m_used = -INFINITY, l_run = 0.f;
     bool alive = true;
+    GroupWaiter gw{reinterpret_cast<volatile int*>(sm + kOffBar + kOffVerdict), abort_flag, kBarIdSoftmax, kSoftmaxWarps * 32, 0, tid == 0};
     for (int j = 0; j < n_tiles; ++j) {
       const float4* kn4 = reinterpret_cast<const float4*>(sm + kOffKn + ((j & 3) * kKeys + 32 * half) * 4);
       const float4* vn4 = reinterpret_cast<const float4*>(sm + kOffVn + ((j & 3) * kKeys + 32 * half) * 4);
       // the norms come straight from the producers (slot j & 3 is rewritten only for tile j + 4), the scores from the MMA;
       // Q K^T of tile j was issued behind P V of tile j - 1, so O is at rest as well
-      alive = warp_wait(bar(kBarNorms + (j & 3)), (j >> 2) & 1, abort_flag) && warp_wait(bar(kBarSFull), j & 1, abort_flag);
+      if (gw.leader && !umma::mbar_wait(bar(kBarNorms + (j & 3)), (j >> 2) & 1, abort_flag)) {}   // (a failure shows in the next verdict)
+      alive = gw.wait(bar(kBarSFull), j & 1);
       if (!alive) break;
       tc_fence_after_sync();
       const int key0 = j * kKeys + 32 * half;
@@ -296,10 +315,7 @@ __global__ void __launch_bounds__(pfu::kThreads, 2) prefill_umma_kernel(const Pr
       // the row maximum needs the other half's keys; past this barrier both threads hold their scores in registers,
       // so P may overwrite the score columns
       xch[((j & 1) * 2 + half) * kRows + t] = mx;
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(kBarXch + (j & 1)));
-      alive = warp_wait(bar(kBarXch + (j & 1)), (j >> 1) & 1, abort_flag);
-      if (!alive) break;
+      named_barrier(kBarIdSoftmax, kSoftmaxWarps * 32);
       mx = fmaxf(mx, xch[((j & 1) * 2 + (half ^ 1)) * kRows + t]);
       float factor = 1.0f;
       if (mx > m_used + kLazy || m_used == -INFINITY) {      // tile 0 always lands here (key 0 is never masked)
@@ -341,12 +357,10 @@ __global__ void __launch_bounds__(pfu::kThreads, 2) prefill_umma_kernel(const Pr
     if (alive) {   // the row sum needs the other half's keys (slot and phase follow on from the loop's use of the barrier)
       const int j = n_tiles;
       xch[((j & 1) * 2 + half) * kRows + t] = l_run;
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(kBarXch + (j & 1)));
-      alive = warp_wait(bar(kBarXch + (j & 1)), (j >> 1) & 1, abort_flag);
-      if (alive) l_run += xch[((j & 1) * 2 + (half ^ 1)) * kRows + t];
+      named_barrier(kBarIdSoftmax, kSoftmaxWarps * 32);
+      l_run += xch[((j & 1) * 2 + (half ^ 1)) * kRows + t];
+      alive = gw.wait(bar(kBarPvDone), (n_tiles - 1) & 1);
     }
-    if (alive) alive = warp_wait(bar(kBarPvDone), (n_tiles - 1) & 1, abort_flag);
     if (alive) {
       tc_fence_after_sync();
       const float inv = alpha_v / fmaxf(l_run, 1e-30f);
@@ -376,28 +390,39 @@ __global__ void __launch_bounds__(pfu::kThreads, 2) prefill_umma_kernel(const Pr
     const int32_t* bt_row = p.block_table + static_cast<int64_t>(b) * p.bt_stride;
     const int64_t row_stride = static_cast<int64_t>(p.H_kv) * kSlotBytes;
     const float kscale = p.scale_log2 * alpha_k;
-    bool alive = true, bad_block = false;
+    bool bad_block = false;
+    GroupWaiter gw{reinterpret_cast<volatile int*>(sm + kOffBar + kOffVerdict + 8), abort_flag, kBarIdProducer, kProducerWarps * 32, 0,
+                   pt == 0};
 
-    auto slot_ptr = [&](int nl, int key0) -> const uint8_t* {
-      const int n = min(key0 + nl, seq_len - 1);             // keys past the end are masked later; read a valid slot
+    // Block ids are read one fetch ahead of the slots they address, slot words one tile ahead of their expansion:
+    // neither global-memory latency sits on the tile-to-tile chain.
+    auto block_id = [&](int nl, int tile) -> int {
+      const int n = min(tile * kKeys + nl, seq_len - 1);     // keys past the end are masked later; read a valid slot
       const int bi = p.bs_shift >= 0 ? n >> p.bs_shift : n / p.block_size;
-      const int in_block = n - bi * p.block_size;
-      int blk = __ldg(bt_row + bi);
+      return __ldg(bt_row + bi);
+    };
+    auto slot_ptr = [&](int blk, int nl, int tile) -> const uint8_t* {
+      const int n = min(tile * kKeys + nl, seq_len - 1);
+      const int in_block = p.bs_shift >= 0 ? n & (p.block_size - 1) : n % p.block_size;
       if (static_cast<unsigned>(blk) >= static_cast<unsigned>(p.num_blocks)) { bad_block = true; blk = 0; }
       return p.cache + (static_cast<int64_t>(blk) * p.block_size + in_block) * row_stride + kvh * kSlotBytes;
     };
-    // Slot words travel through registers and are fetched two tiles before they are expanded (two register sets, used
-    // alternately), so that the global-memory latency lies behind a whole tile of work.
     struct KRegs { uint4 w[kItK]; float2 n[kItK]; };
     struct VRegs { uint4 w[kItV]; };
+    int kblk[kItK], vblk[kItV];                               // block ids of the next tile to fetch
+#pragma unroll
+    for (int it = 0; it < kItK; ++it) kblk[it] = block_id((pt + 128 * it) / KB, 0);
+#pragma unroll
+    for (int it = 0; it < kItV; ++it) vblk[it] = block_id((pt + 128 * it) / VB, 0);
     auto load_k = [&](int j, KRegs& r) {
       if (j >= n_tiles) return;
 #pragma unroll
       for (int it = 0; it < kItK; ++it) {
         const int x = pt + 128 * it, nl = x / KB, quad = x % KB;
-        const uint8_t* src = slot_ptr(nl, j * kKeys);
+        const uint8_t* src = slot_ptr(kblk[it], nl, j);
         r.w[it] = __ldg(reinterpret_cast<const uint4*>(src + 16 * quad));
         if (quad == 0) r.n[it] = __ldg(reinterpret_cast<const float2*>(src + 16 * KB + 16 * VB));
+        kblk[it] = block_id(nl, j + 1);
       }
     };
     auto load_v = [&](int j, VRegs& r) {
@@ -405,7 +430,8 @@ __global__ void __launch_bounds__(pfu::kThreads, 2) prefill_umma_kernel(const Pr
 #pragma unroll
       for (int it = 0; it < kItV; ++it) {
         const int x = pt + 128 * it, nl = x / VB, quad = x % VB;
-        r.w[it] = __ldg(reinterpret_cast<const uint4*>(slot_ptr(nl, j * kKeys) + 16 * KB + 16 * quad));
+        r.w[it] = __ldg(reinterpret_cast<const uint4*>(slot_ptr(vblk[it], nl, j) + 16 * KB + 16 * quad));
+        vblk[it] = block_id(nl, j + 1);
       }
     };
     auto expand_k = [&](int j, const KRegs& r) {
@@ -426,33 +452,27 @@ __global__ void __launch_bounds__(pfu::kThreads, 2) prefill_umma_kernel(const Pr
 #pragma unroll
       for (int it = 0; it < kItV; ++it) {
         const int x = pt + 128 * it, nl = x / VB, quad = x % VB;
-        expand_quad<VB>(base + kOffV, lutv_lane, lut_stride, r.w[it], nl, quad);
+        expand_quad<VB>(base + kOffV + (j & 1) * 16384u, lutv_lane, lut_stride, r.w[it], nl, quad);
       }
       fence_async_smem();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(kBarVFull));
+      if (lane == 0) mbar_arrive(bar(kBarVFull + (j & 1)));
     };
-    // step j: fetch K of tile j+2 and V of tile j+1, then expand K of tile j+1 and V of tile j
-    auto step = [&](int j, KRegs& k_fetch, VRegs& v_fetch, const KRegs& k_exp, const VRegs& v_exp) -> bool {
-      load_k(j + 2, k_fetch);
-      load_v(j + 1, v_fetch);
-      if (j + 1 < n_tiles) {
-        if (j >= 1 && !warp_wait(bar(kBarKEmpty + ((j + 1) & 1)), ((j - 1) >> 1) & 1, abort_flag)) return false;   // Q K^T of tile j-1 done
-        expand_k(j + 1, k_exp);
-      }
-      if (j >= 1 && !warp_wait(bar(kBarPvDone), (j - 1) & 1, abort_flag)) return false;   // P V of tile j-1 done: V tile free
-      expand_v(j, v_exp);
-      return true;
-    };
-    KRegs ka, kb;
-    VRegs va, vb;
-    load_k(0, ka);
-    load_v(0, va);
-    load_k(1, kb);
-    expand_k(0, ka);
-    for (int j = 0; j < n_tiles && alive; j += 2) {
-      alive = step(j, ka, vb, kb, va);
-      if (alive && j + 1 < n_tiles) alive = step(j + 1, kb, va, ka, vb);
+    // Tile i is expanded from registers that were filled while tile i-1 was being expanded; its K stage is free once
+    // Q K^T of tile i-2 is done, its V stage once P V of tile i-2 is done.  (One copy of each piece of code: the kernel
+    // has to stay small enough for the instruction cache.)
+    KRegs kr;
+    VRegs vr;
+    load_k(0, kr);
+    load_v(0, vr);
+#pragma unroll 1
+    for (int i = 0; i < n_tiles; ++i) {
+      if (i >= 2 && !gw.wait(bar(kBarKEmpty + (i & 1)), ((i - 2) >> 1) & 1)) break;
+      expand_k(i, kr);
+      load_k(i + 1, kr);
+      if (i >= 2 && !gw.wait(bar(kBarVEmpty + (i & 1)), ((i - 2) >> 1) & 1)) break;
+      expand_v(i, vr);
+      load_v(i + 1, vr);
     }
     if (bad_block && p.status) atomicOr(p.status, 1);
   } else {
@@ -460,38 +480,58 @@ __global__ void __launch_bounds__(pfu::kThreads, 2) prefill_umma_kernel(const Pr
     if (lane == 0) {
       constexpr uint32_t idesc_qk = instr_desc_f16(kRows, kKeys, false, false);
       constexpr uint32_t idesc_pv = instr_desc_f16(kRows, kHeadDim, false, true);
-      bool alive = true;
-      auto issue_qk = [&](int j) {
-        const uint32_t ktile = base + kOffK + (j & 1) * 16384u;
+      // every operand descriptor is made once: the issue loop is then one instruction per matrix product
+      uint64_t kdesc[2][8], vdesc[2][4];
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          const uint64_t bd = smem_desc_sw128(ktile + (ks >> 2) * 8192u + (ks & 3) * 32u, 16, 1024);
-          mma_ts(tmem + kColS, tmem + kColQ + 8 * ks, bd, idesc_qk, ks > 0 ? 1u : 0u);
-        }
+      for (int st = 0; st < 2; ++st) {
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          kdesc[st][ks] = smem_desc_sw128(base + kOffK + st * 16384u + (ks >> 2) * 8192u + (ks & 3) * 32u, 16, 1024);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) vdesc[st][ks] = smem_desc_sw128(base + kOffV + st * 16384u + ks * 2048u, 8192, 1024);
+      }
+      const uint32_t tq = tmem + kColQ, ts = tmem + kColS, to = tmem + kColO;
+      bool alive = true;
+      auto issue_qk = [&](int st) {
+        mma_ts<false>(ts, tq, kdesc[st][0], idesc_qk);
+#pragma unroll
+        for (int ks = 1; ks < 8; ++ks) mma_ts<true>(ts, tq + 8 * ks, kdesc[st][ks], idesc_qk);
         mma_commit(bar(kBarSFull));
-        mma_commit(bar(kBarKEmpty + (j & 1)));
+        mma_commit(bar(kBarKEmpty + st));
+      };
+      auto issue_pv = [&](int st, bool first) {
+        if (first) mma_ts<false>(to, ts, vdesc[st][0], idesc_pv);
+        else mma_ts<true>(to, ts, vdesc[st][0], idesc_pv);
+#pragma unroll
+        for (int ks = 1; ks < 4; ++ks) mma_ts<true>(to, ts + 8 * ks, vdesc[st][ks], idesc_pv);
+        mma_commit(bar(kBarPvDone));
+        mma_commit(bar(kBarVEmpty + st));
       };
       alive = mbar_wait(bar(kBarKFull), 0, abort_flag);
       if (alive) {
         tc_fence_after_sync();
         issue_qk(0);
       }
-      for (int j = 0; j < n_tiles && alive; ++j) {
-        alive = mbar_wait(bar(kBarVFull), j & 1, abort_flag) && mbar_wait(bar(kBarPFull), j & 1, abort_flag);
+      for (int j = 0; j < n_tiles && alive; j += 2) {   // two tiles per turn: the stage index is a constant in each half
+        alive = mbar_wait(bar(kBarVFull), (j >> 1) & 1, abort_flag) && mbar_wait(bar(kBarPFull), j & 1, abort_flag);
         if (!alive) break;
         tc_fence_after_sync();
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-          const uint64_t bd = smem_desc_sw128(base + kOffV + ks * 2048u, 8192, 1024);
-          mma_ts(tmem + kColO, tmem + kColS + 8 * ks, bd, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
-        }
-        mma_commit(bar(kBarPvDone));
-        if (j + 1 < n_tiles) {   // the scores of the next tile overwrite P: issued behind P V, executed behind it
-          alive = mbar_wait(bar(kBarKFull + ((j + 1) & 1)), ((j + 1) >> 1) & 1, abort_flag);
-          if (!alive) break;
-          tc_fence_after_sync();
-          issue_qk(j + 1);
-        }
+        issue_pv(0, j == 0);
+        if (j + 1 >= n_tiles) break;
+        // the scores of the next tile overwrite P: issued behind P V, executed behind it
+        alive = mbar_wait(bar(kBarKFull + 1), (j >> 1) & 1, abort_flag);
+        if (!alive) break;
+        tc_fence_after_sync();
+        issue_qk(1);
+        alive = mbar_wait(bar(kBarVFull + 1), (j >> 1) & 1, abort_flag) && mbar_wait(bar(kBarPFull), (j + 1) & 1, abort_flag);
+        if (!alive) break;
+        tc_fence_after_sync();
+        issue_pv(1, false);
+        if (j + 2 >= n_tiles) break;
+        alive = mbar_wait(bar(kBarKFull), ((j + 2) >> 1) & 1, abort_flag);
+        if (!alive) break;
+        tc_fence_after_sync();
+        issue_qk(0);
       }
       if (alive) mbar_wait(bar(kBarPvDone), (n_tiles - 1) & 1, abort_flag);   // nothing in flight when TMEM is released
     }
