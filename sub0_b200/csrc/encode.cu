@@ -8,9 +8,10 @@
 
 namespace cda {
 
-// Nearest level of the ascending table `cb` (shared memory, L entries), following
-// Compressor.quantize_unit (cda/algorithm/compression.py:298-313) literally: upper = number of levels
-// strictly below x, clamped to L-1; lower = upper-1 clamped to 0; upper wins only if strictly closer.
+// Nearest level of the ascending table `cb` (L entries), following Compressor.quantize_unit
+// (cda/algorithm/compression.py:298-313) literally: upper = number of levels strictly below x, clamped to L-1;
+// lower = upper-1 clamped to 0; upper wins only if strictly closer.  Used to derive the thresholds below and by the
+// reference kernels of the tests.
 template <int L>
 __device__ __forceinline__ int nearest_level(float x, const float* cb) {
   int upper = 0;
@@ -23,10 +24,54 @@ __device__ __forceinline__ int nearest_level(float x, const float* cb) {
   return d_upper < d_lower ? upper : lower;
 }
 
+// The rule above is monotone in x, so it is the same as counting thresholds: index(x) = #{i : x > T[i]}, where T[i] is
+// the largest float in [cb[i], cb[i+1]] for which the rule still answers i.  T[i] is found by bisection over the
+// ordered integer image of the floats, evaluating the rule's own comparison fabsf(cb[i+1] - x) < fabsf(x - cb[i]) in
+// fp32 exactly as the rule does, so the result is bit-identical, ties and rounding included.
+__device__ __forceinline__ uint32_t float_key(float x) {
+  const uint32_t b = __float_as_uint(x);
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__device__ __forceinline__ float key_float(uint32_t k) {
+  return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
+// Threads 0 .. L-2 of the calling group each find one threshold; T gets 16 entries (unused ones = +inf).
+template <int L>
+__device__ __forceinline__ void build_thresholds(const float* cb, float* T, int t) {
+  if (t >= 0 && t < 16) {
+    float thr = INFINITY;
+    if (t < L - 1) {
+      const float lo = cb[t], hi = cb[t + 1];
+      uint32_t a = float_key(lo), b = float_key(hi);        // rule says t at a; says t+1 at b (if hi > lo)
+      thr = lo;
+      if (b > a) {
+        while (b - a > 1u) {
+          const uint32_t mid = a + ((b - a) >> 1);
+          const float x = key_float(mid);
+          if (fabsf(hi - x) < fabsf(x - lo)) b = mid; else a = mid;
+        }
+        thr = key_float(a);
+      }
+    }
+    T[t] = thr;
+  }
+}
+template <int L>
+__device__ __forceinline__ int count_thresholds(float x, const float* T) {
+  int lo = 0;
+  if (L == 16) {
+    lo = x > T[7] ? 8 : 0;
+    lo += x > T[lo + 3] ? 4 : 0;
+  }
+  lo += x > T[lo + 1] ? 2 : 0;
+  lo += x > T[lo] ? 1 : 0;
+  return lo;
+}
+
 // v: this lane's four rotated fp32 coordinates.  Writes the packed indices of the row to `idx_dst`
-// (16*BITS bytes per row) and returns the row norm (identical in every lane).
+// (16*BITS bytes per row) and returns the row norm (identical in every lane).  T: thresholds of the codebook.
 template <int BITS>
-__device__ __forceinline__ float quantize_row(const float (&v)[4], const float* cb, uint8_t* idx_dst, int lane) {
+__device__ __forceinline__ float quantize_row(const float (&v)[4], const float* T, uint8_t* idx_dst, int lane) {
   constexpr int L = BITS == 4 ? 16 : 4;
   float ss = v[0] * v[0];
   ss = fmaf(v[1], v[1], ss);
@@ -39,7 +84,7 @@ __device__ __forceinline__ float quantize_row(const float (&v)[4], const float* 
   for (int i = 0; i < 4; ++i) {
     float u = __fdiv_rn(v[i], norm);
     u = fminf(fmaxf(u, -1.0f), 1.0f);
-    idx[i] = nearest_level<L>(u, cb);
+    idx[i] = count_thresholds<L>(u, T);
   }
   if (BITS == 4) {
     const uint16_t two = static_cast<uint16_t>(((idx[0] << 4) | idx[1]) | (((idx[2] << 4) | idx[3]) << 8));
@@ -56,51 +101,57 @@ __global__ void __launch_bounds__(256) paged_encode_kernel(const __half* __restr
                                                            uint8_t* __restrict__ cache, const float* __restrict__ cb_K,
                                                            const float* __restrict__ cb_V, int64_t rows, int H_kv,
                                                            int64_t num_slots, int slot_bytes) {
-  __shared__ float s_cb[2][16];
+  __shared__ float s_cb[2][16], s_thr[2][16];
   if (threadIdx.x < 16) {
     s_cb[0][threadIdx.x] = threadIdx.x < (KB == 4 ? 16 : 4) ? cb_K[threadIdx.x] : 0.f;
     s_cb[1][threadIdx.x] = threadIdx.x < (VB == 4 ? 16 : 4) ? cb_V[threadIdx.x] : 0.f;
   }
   __syncthreads();
+  build_thresholds<(KB == 4 ? 16 : 4)>(s_cb[0], s_thr[0], threadIdx.x);
+  build_thresholds<(VB == 4 ? 16 : 4)>(s_cb[1], s_thr[1], static_cast<int>(threadIdx.x) - 32);
+  __syncthreads();
   const int lane = threadIdx.x & 31;
-  const int64_t row = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);   // = t * H_kv + h
-  if (row >= rows) return;
-  const int64_t t = row / H_kv;
-  const int h = static_cast<int>(row - t * H_kv);
-  const int64_t slot = slot_mapping[t];
-  if (slot < 0 || slot >= num_slots) return;
-  uint8_t* dst = cache + (slot * H_kv + h) * slot_bytes;
   constexpr int kKBytes = 16 * KB, kVBytes = 16 * VB;
+  // grid-stride over rows (row = t * H_kv + h): the threshold set-up is paid once per CTA
+  for (int64_t row = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5); row < rows; row += static_cast<int64_t>(gridDim.x) * 8) {
+    const int64_t t = row / H_kv;
+    const int h = static_cast<int>(row - t * H_kv);
+    const int64_t slot = slot_mapping[t];
+    if (slot < 0 || slot >= num_slots) continue;
+    uint8_t* dst = cache + (slot * H_kv + h) * slot_bytes;
 
-  float v[4];
-  load_half4(K + row * kHeadDim + 4 * lane, v);
-  fht128_warp(v, lane);
+    float v[4], w[4];
+    load_half4(K + row * kHeadDim + 4 * lane, v);
+    load_half4(V + row * kHeadDim + 4 * lane, w);
+    fht128_warp(v, lane);
+    fht128_warp(w, lane);
 #pragma unroll
-  for (int i = 0; i < 4; ++i) v[i] = round_to_half(v[i] * kRsqrtD);   // Compressor.rotate casts back to fp16
-  const float nk = quantize_row<KB>(v, s_cb[0], dst, lane);
-
-  load_half4(V + row * kHeadDim + 4 * lane, v);
-  fht128_warp(v, lane);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) v[i] = round_to_half(v[i] * kRsqrtD);
-  const float nv = quantize_row<VB>(v, s_cb[1], dst + kKBytes, lane);
-  if (lane == 0) *reinterpret_cast<float2*>(dst + kKBytes + kVBytes) = make_float2(nk, nv);
+    for (int i = 0; i < 4; ++i) {                       // Compressor.rotate casts back to fp16
+      v[i] = round_to_half(v[i] * kRsqrtD);
+      w[i] = round_to_half(w[i] * kRsqrtD);
+    }
+    const float nk = quantize_row<KB>(v, s_thr[0], dst, lane);
+    const float nv = quantize_row<VB>(w, s_thr[1], dst + kKBytes, lane);
+    if (lane == 0) *reinterpret_cast<float2*>(dst + kKBytes + kVBytes) = make_float2(nk, nv);
+  }
 }
 
 template <int BITS>
 __global__ void __launch_bounds__(256) quantize_rotated_kernel(const float* __restrict__ x, int64_t rows,
                                                                const float* __restrict__ cb, uint8_t* __restrict__ idx_out,
                                                                float* __restrict__ norm_out) {
-  __shared__ float s_cb[16];
+  __shared__ float s_cb[16], s_thr[16];
   if (threadIdx.x < 16) s_cb[threadIdx.x] = threadIdx.x < (BITS == 4 ? 16 : 4) ? cb[threadIdx.x] : 0.f;
   __syncthreads();
+  build_thresholds<(BITS == 4 ? 16 : 4)>(s_cb, s_thr, threadIdx.x);
+  __syncthreads();
   const int lane = threadIdx.x & 31;
-  const int64_t row = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
-  if (row >= rows) return;
-  const float4 raw = *reinterpret_cast<const float4*>(x + row * kHeadDim + 4 * lane);
-  const float v[4] = {raw.x, raw.y, raw.z, raw.w};
-  const float n = quantize_row<BITS>(v, s_cb, idx_out + row * (16 * BITS), lane);
-  if (lane == 0) norm_out[row] = n;
+  for (int64_t row = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5); row < rows; row += static_cast<int64_t>(gridDim.x) * 8) {
+    const float4 raw = *reinterpret_cast<const float4*>(x + row * kHeadDim + 4 * lane);
+    const float v[4] = {raw.x, raw.y, raw.z, raw.w};
+    const float n = quantize_row<BITS>(v, s_thr, idx_out + row * (16 * BITS), lane);
+    if (lane == 0) norm_out[row] = n;
+  }
 }
 
 __global__ void __launch_bounds__(256) hadamard128_kernel(const __half* __restrict__ x, __half* __restrict__ y,
@@ -117,6 +168,11 @@ __global__ void __launch_bounds__(256) hadamard128_kernel(const __half* __restri
 }
 
 static int64_t blocks_for_rows(int64_t rows) { return (rows + 7) / 8; }
+// Grid of the row kernels that loop over rows: enough CTAs to fill every SM (8 CTAs of 256 threads each), no more.
+static unsigned persistent_grid(int64_t rows) {
+  const int64_t want = blocks_for_rows(rows), cap = static_cast<int64_t>(device_sm_count(-1)) * 8;
+  return static_cast<unsigned>(want < cap ? want : cap);
+}
 
 }  // namespace cda
 
@@ -137,7 +193,7 @@ extern "C" int cda_b200_paged_encode(const void* K, const void* V, const int32_t
   const int64_t rows = T * H_kv;
   const int64_t blocks = blocks_for_rows(rows);
   if (blocks > 0x7fffffffLL) return fail(CDA_ERR_N_TOO_LARGE, "paged_encode: T*H_kv too large");
-  const dim3 grid(static_cast<unsigned>(blocks)), block(256);
+  const dim3 grid(persistent_grid(rows)), block(256);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const __half* k = static_cast<const __half*>(K);
   const __half* v = static_cast<const __half*>(V);
@@ -164,9 +220,9 @@ extern "C" int cda_b200_quantize_rotated(const float* x_rot, int64_t rows, const
   if (blocks > 0x7fffffffLL) return fail(CDA_ERR_N_TOO_LARGE, "quantize_rotated: too many rows");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (bits == 4)
-    quantize_rotated_kernel<4><<<static_cast<unsigned>(blocks), 256, 0, st>>>(x_rot, rows, cb, idx_out, norm_out);
+    quantize_rotated_kernel<4><<<persistent_grid(rows), 256, 0, st>>>(x_rot, rows, cb, idx_out, norm_out);
   else
-    quantize_rotated_kernel<2><<<static_cast<unsigned>(blocks), 256, 0, st>>>(x_rot, rows, cb, idx_out, norm_out);
+    quantize_rotated_kernel<2><<<persistent_grid(rows), 256, 0, st>>>(x_rot, rows, cb, idx_out, norm_out);
   return check_launch("quantize_rotated");
 }
 
