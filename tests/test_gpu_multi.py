@@ -61,7 +61,22 @@ def _rank_main(rank, world, port, q):
                                 local_max_seq_len=max(local_max, 1))
         torch.cuda.synchronize()
         ok, ratio, cos = Cs.close(out.cpu(), want)
-        q.put((rank, same, ok, ratio))
+        # --- the same shards through the vLLM backend's decode-context-parallel path (gathers over the default group)
+        from sub0_b200.vllm_integration.cda_attn_v2 import get_backend_classes
+        _, Impl, _, Metadata = get_backend_classes()
+        impl = Impl(16, 128, 128 ** -0.5, num_kv_heads=4)
+        slots, hkv, w = case["cache"].shape
+        kv = case["cache"].view(slots // 16, 16, hkv, w).contiguous().to(dev).view(torch.float16)
+        md = Metadata(num_actual_tokens=2, num_reqs=2, max_query_len=1, max_seq_len=max(local_max, 1),
+                      query_start_loc=torch.tensor([0, 1, 2], dtype=torch.int32, device=dev),
+                      seq_lens=torch.tensor(lens, dtype=torch.int32, device=dev), block_table=bt.to(dev),
+                      slot_mapping=torch.zeros(2, dtype=torch.int64, device=dev), dcp_world_size=world, dcp_rank=rank,
+                      num_decodes=2, num_decode_tokens=2)
+        out2 = torch.empty(2, 16 * 128, dtype=torch.float16, device=dev)
+        impl.forward(None, case["Q"].to(dev).view(2, -1), None, None, kv, md, output=out2)
+        torch.cuda.synchronize()
+        ok2, ratio2, _ = Cs.close(out2.view(2, 16, 128).cpu(), want)
+        q.put((rank, same, ok and ok2, max(ratio, ratio2)))
     except Exception as exc:
         q.put((rank, False, False, repr(exc)))
     finally:
