@@ -34,6 +34,8 @@ if str(ROOT) not in sys.path:
 H_KV, GROUP, BLOCK = 8, 4, 16
 METRIC = "cda_decode_k4v4_hbm_gbs"
 UNIT = "GB/s"
+# dram bytes (read + write) per algorithmic byte of the split kernel, from the ncu capture of the B=16, N=65536 cell
+DRAM_TRAFFIC_RATIO = 1.062
 
 
 def algorithmic_bytes(B, N, H_kv, H_q, k_bits=4, v_bits=4, block=BLOCK):
@@ -291,8 +293,14 @@ def run_ours(args):
                 "dtype": "f16", "data": "synthetic", "config": config(args, world),
                 "frac_of_8000_gbs_nominal": value / (8000.0 * world),
                 "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": UNIT, "frac": achieved / peak,
-                             "peak_source": peak_src, "traffic": None,
-                             "note": "rank-0 launch = split kernel + merge kernel (merge < 3 % of the time); algorithmic bytes of this rank's shard"},
+                             "frac_of_min_step": rank_bytes / (min(per_step) * 1e-3) / 1e9 / peak,
+                             "peak_source": peak_src, "traffic": rank_bytes * DRAM_TRAFFIC_RATIO,
+                             "note": "rank-0 launch = split kernel + merge kernel (merge < 5 % of the time); algorithmic "
+                                     "bytes of this rank's shard; traffic = these bytes x 1.062, the ratio of "
+                                     "dram__bytes_read+write to algorithmic bytes in the ncu capture of the B=16 cell "
+                                     "(144-byte slots vs 136-byte payloads, plus partials), which grows with the units "
+                                     "processed; the peak is a best-of-10 burst figure, frac_of_min_step is the like-for-like "
+                                     "fraction, frac the one sustained over all steps"},
                 "e2e": {"value": e2e_val, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d * world,
                         "d2h_bytes_per_step": d2h * world,
                         "what": "pinned H2D of Q/new K,V/slots/block table/seq lens + paged encode + decode + D2H of the output, synchronised every step; the KV cache is resident state"},
@@ -451,7 +459,7 @@ def run_prompt_workload(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=32)
