@@ -113,9 +113,15 @@ __global__ void __launch_bounds__(256) paged_encode_kernel(const __half* __restr
   const int lane = threadIdx.x & 31;
   constexpr int kKBytes = 16 * KB, kVBytes = 16 * VB;
   // grid-stride over rows (row = t * H_kv + h): the threshold set-up is paid once per CTA
-  for (int64_t row = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5); row < rows; row += static_cast<int64_t>(gridDim.x) * 8) {
-    const int64_t t = row / H_kv;
-    const int h = static_cast<int>(row - t * H_kv);
+  // (token, head) of the row advance with the row, so the 64-bit division happens once per warp
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * 8;
+  const int64_t t_step = stride / H_kv;
+  const int h_step = static_cast<int>(stride - t_step * H_kv);
+  int64_t row = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  int64_t t = row / H_kv;
+  int h = static_cast<int>(row - t * H_kv);
+  for (; row < rows; row += stride, t += t_step, h += h_step) {
+    if (h >= H_kv) { h -= H_kv; ++t; }
     const int64_t slot = slot_mapping[t];
     if (slot < 0 || slot >= num_slots) continue;
     uint8_t* dst = cache + (slot * H_kv + h) * slot_bytes;

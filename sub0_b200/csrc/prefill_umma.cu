@@ -4,24 +4,24 @@
 // rotate Q, attend to the dequantised keys and values in the rotated domain with bottom-right aligned causal masking,
 // round the normalised output to fp16, rotate back.
 //
-// One CTA = 128 rows = (128 / G) consecutive query positions x the G query heads of one KV head, so that a
-// dequantised key/value tile serves the whole GQA group.  Keys are processed 64 at a time:
+// One CTA per SM works on 256 rows = two blocks of 128 rows = (256 / G) consecutive query positions x the G query heads
+// of one KV head, so that a dequantised key/value tile serves the whole GQA group and both blocks.  Keys are processed
+// 128 at a time; the two blocks run half a step apart, so one block's softmax overlaps the other's matrix products:
 //
-//   producer warps (4)   cache slots -> registers (two tiles ahead) -> unit-level fp16 tiles in shared memory (128-byte
-//                        swizzled rows, the layout tcgen05.mma reads), norms to side arrays
-//   MMA warp (1 thread)  S = Q K^T (128x64x128) and O += P V (128x128x64); Q and P are read from tensor memory, only
-//                        the K and V tiles from shared memory
-//   softmax warps (8)    two threads per row (32 keys each): TMEM -> registers, scale by the key norm, mask, online
-//                        maximum with lazy rescaling of O, exp2, fold the value norm, fp16 P -> TMEM over the scores
+//   producer warps (8)    cache slots -> registers (one tile ahead) -> unit-level fp16 tiles in shared memory (128-byte
+//                         swizzled rows, the layout tcgen05.mma reads), norms to side arrays
+//   MMA warp (1 thread)   per block: S = Q K^T (128x128x128, Q and K from shared memory) and O += P V (128x128x128, P from
+//                         tensor memory, V from shared memory)
+//   softmax warps (2 x 8) two threads per row (64 keys each): TMEM -> registers, scale by the key norm, mask, online
+//                         maximum with lazy rescaling of O, exp2, fold the value norm, fp16 P -> TMEM over the thread's
+//                         own score columns
 //
-// Tensor memory (256 columns): Q [0,64) as fp16 pairs, S [64,128) (P reuses its first 32 columns), O [128,256).
-// Shared memory is the scarce resource (its pipe was 84 % busy when Q and P were shared-memory operands and the
-// code tables had four copies): the tables own 32 KB -- one table with a copy per lane when both codebooks are the
-// same, else two with half the copies -- and gathers are then conflict-free.
+// Tensor memory (512 columns): S of block b at [128 b, 128 b + 128), O of block b at [256 + 128 b, ...).  P of the keys
+// [64 h, 64 h + 64) lives in the first 32 columns of the same thread's scores, [128 b + 64 h, + 32).
+// Shared memory (217 KB): Q 64 KB, K 2 x 32 KB, V 2 x 32 KB, code tables 16 KB, norms, exchange words, barriers.
 //
 // The roles hand tiles over through mbarriers; every wait is bounded (umma.cuh) and a wait that gives up sets a fault
-// flag and ends the CTA cleanly (TMEM is released).  Two CTAs fit one SM (102 KB shared memory, 256 TMEM columns each),
-// so one CTA's softmax overlaps the other's matrix products.
+// flag and ends the CTA cleanly (TMEM is released).
 #include "common.cuh"
 #include "umma.cuh"
 #include "prefill_umma.cuh"
@@ -34,29 +34,33 @@ __device__ int g_prefill_fault = 0;
 
 namespace pfu {
 
-constexpr int kRows = 128;            // rows of a CTA tile
-constexpr int kKeys = 64;             // keys per tile
-constexpr int kSoftmaxWarps = 8, kProducerWarps = 4, kMmaWarp = kSoftmaxWarps + kProducerWarps;
+constexpr int kRows = 128;            // rows of one block (one tcgen05.mma M)
+constexpr int kBlocks = 2;            // row blocks per CTA
+constexpr int kKeys = 128;            // keys per tile
+constexpr int kSoftmaxWarpsPerBlock = 8, kSoftmaxWarps = kBlocks * kSoftmaxWarpsPerBlock, kProducerWarps = 8;
+constexpr int kMmaWarp = kSoftmaxWarps + kProducerWarps;
 constexpr int kThreads = (kMmaWarp + 1) * 32;
-constexpr int kTmemCols = 256;
-constexpr int kColQ = 0, kColS = 64, kColO = 128;
+constexpr int kTmemCols = 512;
+constexpr int kColS = 0, kColO = 256;    // + 128 * block
 constexpr float kLazy = 4.0f;         // O is rescaled only when the row maximum grew by more than 2^4
 
 // shared memory map (bytes from the 1024-aligned base)
-constexpr int kOffK = 0;                       // 2 stages x (2 column blocks x 64 rows x 128 B); also stages Q and O rows
-constexpr int kOffV = 32768;                   // 2 stages x (2 column blocks x 64 rows x 128 B)
-constexpr int kOffLut = 65536;                 // 32 KB of code tables
-constexpr int kLutBytes = 32768;
-constexpr int kOffKn = kOffLut + kLutBytes;    // 4 x 64 floats: key norm * softmax scale * log2(e) * alpha_k
-constexpr int kOffVn = kOffKn + 1024;          // 4 x 64 floats: value norm
-constexpr int kOffXch = kOffVn + 1024;         // 2 x 2 x 128 floats: row maxima / sums exchanged between the two threads of a row
-constexpr int kOffBar = kOffXch + 2048;        // mbarriers, TMEM address, flags
+constexpr int kOffQ = 0;                       // 2 blocks x (2 column blocks x 128 rows x 128 B)
+constexpr int kOffK = 65536;                   // 2 stages x (2 column blocks x 128 rows x 128 B); also stages the O rows
+constexpr int kOffV = 131072;                  // 2 stages x (2 column blocks x 128 rows x 128 B)
+constexpr int kTileBytes = 32768, kColBlockBytes = 16384;
+constexpr int kOffLut = 196608;                // 16 KB of code tables
+constexpr int kLutBytes = 16384;
+constexpr int kOffKn = kOffLut + kLutBytes;    // 4 x 128 floats: key norm * softmax scale * log2(e) * alpha_k
+constexpr int kOffVn = kOffKn + 2048;          // 4 x 128 floats: value norm
+constexpr int kOffXch = kOffVn + 2048;         // 2 blocks x 2 parities x 2 halves x 128 floats: row maxima / sums of the two threads of a row
+constexpr int kOffBar = kOffXch + 4096;        // mbarriers, TMEM address, flags
 constexpr int kSmemBytes = kOffBar + 256 + 1024;   // + slack for the 1024-byte alignment
 
 // barrier slots (8 bytes each) inside kOffBar
-constexpr int kBarKFull = 0, kBarKEmpty = 2, kBarSFull = 4, kBarVFull = 5, kBarPFull = 7, kBarPvDone = 8, kBarNorms = 9,
-              kBarVEmpty = 13;   // 15 barriers
-constexpr int kOffTmemAddr = 120, kOffAbort = 124, kOffVerdict = 128;   // verdict words: 2 per waiting group
+constexpr int kBarKFull = 0, kBarKEmpty = 2, kBarVFull = 4, kBarVEmpty = 6, kBarSFull = 8, kBarPFull = 10, kBarPvDone = 12,
+              kBarNorms = 14;   // 18 barriers
+constexpr int kOffTmemAddr = 160, kOffAbort = 164, kOffVerdict = 168;   // verdict words: 2 per waiting group (3 groups)
 
 __device__ __forceinline__ uint32_t lds32(uint32_t a) {
   uint32_t v;
@@ -105,15 +109,15 @@ struct GroupWaiter {
     return ok;
   }
 };
-constexpr int kBarIdSoftmax = 1, kBarIdProducer = 2;
+constexpr int kBarIdSoftmax = 1, kBarIdProducer = 3;   // named barriers 1 and 2: the softmax groups of blocks 0 and 1
 
 __device__ __forceinline__ uint32_t sw128(uint32_t row, uint32_t chunk) {   // byte offset inside a block of 128-byte rows
   return (row >> 3) * 1024u + (row & 7u) * 128u + ((chunk ^ (row & 7u)) << 4);
 }
 
 // Code tables.  One entry per code byte: 4-bit codes -> 2 levels (4 bytes), 2-bit codes -> 4 levels (8 bytes).  An entry
-// is stored `stride / entry bytes` times in a row of `stride` bytes (128 when the table owns the whole 32 KB, else 64),
-// and lane l reads copy l mod copies: with a copy per lane no two lanes ever meet in a bank.
+// is stored `stride / entry bytes` times in a row of `stride` bytes (64 when one table serves both sides and owns the
+// whole 16 KB, else 32), and lane l reads copy l mod copies, which spreads the lanes of a gather over the banks.
 template <int BITS>
 __device__ __forceinline__ void fill_code_table(uint8_t* lut, int stride, const float* __restrict__ cb, float inv_alpha, int tid,
                                                 int nthreads) {
@@ -131,8 +135,8 @@ __device__ __forceinline__ void fill_code_table(uint8_t* lut, int stride, const 
   }
 }
 
-// Expand 16 bytes of codes (one quad of a slot) of token row `nl` into fp16 chunks of a 64-row tile.
-// tile: shared address of column block 0 (block 1 is 8192 bytes further).  quad: index of the 16 bytes in the row's codes.
+// Expand 16 bytes of codes (one quad of a slot) of token row `nl` into fp16 chunks of a 128-row tile.
+// tile: shared address of column block 0 (block 1 is kColBlockBytes further).  quad: index of the 16 bytes in the row's codes.
 // lut_lane: table address + this lane's copy; stride: bytes per entry row.
 template <int BITS>
 __device__ __forceinline__ void expand_quad(uint32_t tile, uint32_t lut_lane, uint32_t stride, const uint4& w, int nl, int quad) {
@@ -147,7 +151,7 @@ __device__ __forceinline__ void expand_quad(uint32_t tile, uint32_t lut_lane, ui
       v[2] = lds32(lut_lane + ((x >> 16) & 0xffu) * stride);
       v[3] = lds32(lut_lane + (x >> 24) * stride);
       const int c16 = quad * 4 + wi;                       // 16-byte chunk of the row: 8 coordinates
-      sts128(tile + (c16 >> 3) * 8192u + sw128(nl, c16 & 7), v[0], v[1], v[2], v[3]);
+      sts128(tile + (c16 >> 3) * kColBlockBytes + sw128(nl, c16 & 7), v[0], v[1], v[2], v[3]);
     }
   } else {
 #pragma unroll
@@ -158,21 +162,68 @@ __device__ __forceinline__ void expand_quad(uint32_t tile, uint32_t lut_lane, ui
         const uint32_t b0 = (x >> (16 * hb)) & 0xffu, b1 = (x >> (16 * hb + 8)) & 0xffu;
         const uint2 lo = lds64(lut_lane + b0 * stride), hi = lds64(lut_lane + b1 * stride);
         const int c16 = quad * 8 + wi * 2 + hb;
-        sts128(tile + (c16 >> 3) * 8192u + sw128(nl, c16 & 7), lo.x, lo.y, hi.x, hi.y);
+        sts128(tile + (c16 >> 3) * kColBlockBytes + sw128(nl, c16 & 7), lo.x, lo.y, hi.x, hi.y);
       }
     }
   }
 }
 
+// One thread's 64 scores of a tile (columns s_col .. s_col + 63 of its TMEM lane), scaled by the key norms kn[0..63].
+// MASK: keys beyond q_pos (the row's diagonal) count as minus infinity.
+template <bool MASK>
+__device__ __forceinline__ float row_max(uint32_t s_col, const float* kn, int key0, int q_pos) {
+  float mx = -INFINITY;
+#pragma unroll
+  for (int ch = 0; ch < 4; ++ch) {
+    uint32_t s[16];
+    umma::tmem_ld16(s_col + 16 * ch, s);
+    umma::tmem_wait_ld();
+#pragma unroll
+    for (int c = 0; c < 16; ++c) {
+      float x = __uint_as_float(s[c]) * kn[16 * ch + c];
+      if (MASK) x = key0 + 16 * ch + c > q_pos ? -INFINITY : x;
+      mx = fmaxf(mx, x);
+    }
+  }
+  return mx;
+}
+// exp2(score * kn - m) for the same 64 scores; P = probability * vn as fp16 pairs into columns s_col .. s_col + 31.
+// Returns the sum of the probabilities.
+template <bool MASK>
+__device__ __forceinline__ float row_probabilities(uint32_t s_col, const float* kn, const float* vn, float m, int key0, int q_pos) {
+  float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+  for (int ch = 0; ch < 4; ++ch) {
+    uint32_t s[16], pk[8];
+    umma::tmem_ld16(s_col + 16 * ch, s);
+    umma::tmem_wait_ld();
+#pragma unroll
+    for (int c = 0; c < 16; c += 2) {
+      float a0 = fmaf(__uint_as_float(s[c]), kn[16 * ch + c], -m), a1 = fmaf(__uint_as_float(s[c + 1]), kn[16 * ch + c + 1], -m);
+      if (MASK) {
+        a0 = key0 + 16 * ch + c > q_pos ? -INFINITY : a0;
+        a1 = key0 + 16 * ch + c + 1 > q_pos ? -INFINITY : a1;
+      }
+      const float e0 = fast_exp2(a0), e1 = fast_exp2(a1);
+      sum0 += e0;
+      sum1 += e1;
+      pk[c / 2] = pack_half2(e0 * vn[16 * ch + c], e1 * vn[16 * ch + c + 1]);
+    }
+    umma::tmem_st8(s_col + 8 * ch, pk);
+  }
+  return sum0 + sum1;
+}
+
 }  // namespace pfu
 
 template <int G, int KB, int VB>
-__global__ void __launch_bounds__(pfu::kThreads, 2) prefill_umma_kernel(const PrefillUmmaParams p) {
+__global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const PrefillUmmaParams p) {
   using namespace pfu;
   using namespace umma;
-  constexpr int kPosPerTile = kRows / G;
+  constexpr int kPosPerTile = kBlocks * kRows / G;
   constexpr int kSlotBytes = 16 * KB + 16 * VB + 16;
-  constexpr int kItK = kKeys * KB / 128, kItV = kKeys * VB / 128;   // 16-byte code pieces per producer thread and tile
+  constexpr int kProducerThreads = kProducerWarps * 32;
+  constexpr int kItK = kKeys * KB / kProducerThreads, kItV = kKeys * VB / kProducerThreads;   // 16-byte code pieces per producer thread and tile
   constexpr int kLevK = KB == 4 ? 16 : 4, kLevV = VB == 4 ? 16 : 4;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_addr(smem_raw);
@@ -207,18 +258,16 @@ __global__ void __launch_bounds__(pfu::kThreads, 2) prefill_umma_kernel(const Pr
 #pragma unroll
     for (int i = 0; i < kLevK; ++i) same_cb = same_cb && __ldg(p.cb_k + i) == __ldg(p.cb_v + i);
   }
-  const uint32_t lut_stride = same_cb ? 128u : 64u;
+  const uint32_t lut_stride = same_cb ? 64u : 32u;
   const uint32_t lutv_off = same_cb ? 0u : static_cast<uint32_t>(kLutBytes / 2);
 
   // ---- set-up: barriers, TMEM, tables, rotated queries -----------------------------------------------------------------
   if (tid == 0) {
-    mbar_init(bar(kBarKFull), kProducerWarps); mbar_init(bar(kBarKFull + 1), kProducerWarps);
-    mbar_init(bar(kBarKEmpty), 1); mbar_init(bar(kBarKEmpty + 1), 1);
-    mbar_init(bar(kBarSFull), 1);
-    mbar_init(bar(kBarVFull), kProducerWarps); mbar_init(bar(kBarVFull + 1), kProducerWarps);
-    mbar_init(bar(kBarVEmpty), 1); mbar_init(bar(kBarVEmpty + 1), 1);
-    mbar_init(bar(kBarPFull), kSoftmaxWarps);
-    mbar_init(bar(kBarPvDone), 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar(kBarKFull + i), kProducerWarps); mbar_init(bar(kBarKEmpty + i), 1);
+      mbar_init(bar(kBarVFull + i), kProducerWarps); mbar_init(bar(kBarVEmpty + i), 1);
+      mbar_init(bar(kBarSFull + i), 1); mbar_init(bar(kBarPFull + i), kSoftmaxWarpsPerBlock); mbar_init(bar(kBarPvDone + i), 1);
+    }
     for (int i = 0; i < 4; ++i) mbar_init(bar(kBarNorms + i), kProducerWarps);
     *abort_flag = 0;
     mbar_init_fence();
@@ -229,9 +278,9 @@ __global__ void __launch_bounds__(pfu::kThreads, 2) prefill_umma_kernel(const Pr
   }
   fill_code_table<KB>(sm + kOffLut, lut_stride, p.cb_k, 1.0f / alpha_k, tid, kThreads);
   if (!same_cb) fill_code_table<VB>(sm + kOffLut + lutv_off, lut_stride, p.cb_v, 1.0f / alpha_v, tid, kThreads);
-  // Q: one warp per row loads, rotates and parks the fp16 row in the staging area (256-byte rows, chunk XOR (row & 15))
-  for (int t = warp; t < kRows; t += kThreads / 32) {
-    const int pos = p0 + t / G, hl = t % G;
+  // Q: one warp per row loads, rotates and stores the fp16 row as the A operand of Q K^T (K-major, 128-byte swizzle)
+  for (int r = warp; r < kBlocks * kRows; r += kThreads / 32) {
+    const int pos = p0 + r / G, hl = r % G;
     float v[4] = {0.f, 0.f, 0.f, 0.f};
     if (pos < q_len && hl < g) {
       load_half4(p.q + (static_cast<int64_t>(q_begin + pos) * p.H_q + kvh * g + hl) * kHeadDim + 4 * lane, v);
@@ -240,82 +289,48 @@ __global__ void __launch_bounds__(pfu::kThreads, 2) prefill_umma_kernel(const Pr
       for (int i = 0; i < 4; ++i) v[i] *= kRsqrtD;
     }
     const uint2 h = pack_half4(v);
-    sts64(base + kOffK + t * 256u + ((static_cast<uint32_t>(lane >> 1) ^ (t & 15u)) << 4) + (lane & 1) * 8u, h.x, h.y);
+    const uint32_t t = static_cast<uint32_t>(r & (kRows - 1));
+    sts64(base + kOffQ + (r / kRows) * kTileBytes + (lane >> 4) * kColBlockBytes + sw128(t, (lane & 15) >> 1) + (lane & 1) * 8u, h.x, h.y);
   }
+  fence_async_smem();
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(sm + kOffBar + kOffTmemAddr);
-  if (warp < kSoftmaxWarps) {   // ... and from there into tensor memory: row t in lane t, coordinates 2c, 2c+1 in column c
-    const int quarter = warp & 3, half = warp >> 2, t = quarter * 32 + lane;
-    uint32_t qv[32];
-#pragma unroll
-    for (int ch = 0; ch < 8; ++ch) {
-      const uint32_t chunk = static_cast<uint32_t>(8 * half + ch);
-      const uint4 x = lds128(base + kOffK + t * 256u + ((chunk ^ (t & 15u)) << 4));
-      qv[4 * ch] = x.x; qv[4 * ch + 1] = x.y; qv[4 * ch + 2] = x.z; qv[4 * ch + 3] = x.w;
-    }
-    tmem_st32(tmem + (static_cast<uint32_t>(quarter * 32) << 16) + kColQ + 32 * half, qv);
-    tmem_wait_st();
-  }
-  tc_fence_before_sync();
-  __syncthreads();            // the staging area becomes the K stages; Q is in place for the first Q K^T
-  tc_fence_after_sync();
 
   if (warp < kSoftmaxWarps) {
-    // ================= softmax: two threads per row, 32 of the tile's 64 keys each ================================================
-    const int quarter = warp & 3, half = warp >> 2;          // TMEM lane quarter of this warp; which 32 keys / 64 O columns
-    const int t = quarter * 32 + lane;                       // row
-    const int q_pos = q_offset + p0 + t / G;                 // key index of the diagonal for this row
+    // ================= softmax: per block, two threads per row, 64 of the tile's 128 keys each ================================
+    const int blk = warp / kSoftmaxWarpsPerBlock, w = warp % kSoftmaxWarpsPerBlock;
+    const int quarter = w & 3, half = w >> 2;                // TMEM lane quarter of this warp; which 64 keys / 64 O columns
+    const int t = quarter * 32 + lane;                       // row inside the block
+    const int q_pos = q_offset + p0 + (blk * kRows + t) / G; // key index of the diagonal for this row
     const uint32_t lane_base = tmem + (static_cast<uint32_t>(quarter * 32) << 16);
-    float* xch = reinterpret_cast<float*>(sm + kOffXch);     // [2 parities][2 halves][128 rows]
+    const uint32_t s_col = lane_base + kColS + 128 * blk + 64 * half;     // this thread's scores; P goes over the first 32 columns
+    const uint32_t o_col = lane_base + kColO + 128 * blk + 64 * half;     // this thread's half of the O row
+    float* xch = reinterpret_cast<float*>(sm + kOffXch) + blk * 4 * kRows;   // [2 parities][2 halves][128 rows]
+    const int bar_id = kBarIdSoftmax + blk, group_threads = kSoftmaxWarpsPerBlock * 32;
     float m_used = -INFINITY, l_run = 0.f;
     bool alive = true;
-    GroupWaiter gw{reinterpret_cast<volatile int*>(sm + kOffBar + kOffVerdict), abort_flag, kBarIdSoftmax, kSoftmaxWarps * 32, 0, tid == 0};
+    GroupWaiter gw{reinterpret_cast<volatile int*>(sm + kOffBar + kOffVerdict + 8 * blk), abort_flag, bar_id, group_threads, 0, w == 0 && lane == 0};
+#pragma unroll 1
     for (int j = 0; j < n_tiles; ++j) {
-      const float4* kn4 = reinterpret_cast<const float4*>(sm + kOffKn + ((j & 3) * kKeys + 32 * half) * 4);
-      const float4* vn4 = reinterpret_cast<const float4*>(sm + kOffVn + ((j & 3) * kKeys + 32 * half) * 4);
+      const float* kn = reinterpret_cast<const float*>(sm + kOffKn) + (j & 3) * kKeys + 64 * half;
+      const float* vn = reinterpret_cast<const float*>(sm + kOffVn) + (j & 3) * kKeys + 64 * half;
       // the norms come straight from the producers (slot j & 3 is rewritten only for tile j + 4), the scores from the MMA;
-      // Q K^T of tile j was issued behind P V of tile j - 1, so O is at rest as well
+      // Q K^T of tile j was issued behind P V of tile j - 1 of this block, so its O is at rest as well
       if (gw.leader && !umma::mbar_wait(bar(kBarNorms + (j & 3)), (j >> 2) & 1, abort_flag)) {}   // (a failure shows in the next verdict)
-      alive = gw.wait(bar(kBarSFull), j & 1);
+      alive = gw.wait(bar(kBarSFull + blk), j & 1);
       if (!alive) break;
       tc_fence_after_sync();
-      const int key0 = j * kKeys + 32 * half;
-      uint32_t s[32];
-      tmem_ld32(lane_base + kColS + 32 * half, s);
-      tmem_wait_ld();
-      float mx = -INFINITY;
-      if (key0 + 31 > q_offset + p0) {                       // some row of the tile masks some of these keys
-#pragma unroll
-        for (int c4 = 0; c4 < 8; ++c4) {
-          const float4 n4 = kn4[c4];
-          const float nn[4] = {n4.x, n4.y, n4.z, n4.w};
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            float x = __uint_as_float(s[4 * c4 + i]) * nn[i];
-            x = key0 + 4 * c4 + i > q_pos ? -INFINITY : x;
-            s[4 * c4 + i] = __float_as_uint(x);
-            mx = fmaxf(mx, x);
-          }
-        }
-      } else {
-#pragma unroll
-        for (int c4 = 0; c4 < 8; ++c4) {
-          const float4 n4 = kn4[c4];
-          const float nn[4] = {n4.x, n4.y, n4.z, n4.w};
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const float x = __uint_as_float(s[4 * c4 + i]) * nn[i];
-            s[4 * c4 + i] = __float_as_uint(x);
-            mx = fmaxf(mx, x);
-          }
-        }
-      }
-      // the row maximum needs the other half's keys; past this barrier both threads hold their scores in registers,
-      // so P may overwrite the score columns
+      const int key0 = j * kKeys + 64 * half;
+      const bool diag = key0 + 63 > q_offset + p0;           // some row of the CTA masks some of these keys
+
+      // pass 1: maximum of this thread's 64 scaled scores (diagonal tiles take the masking variant)
+      const float mx_own = diag ? row_max<true>(s_col, kn, key0, q_pos) : row_max<false>(s_col, kn, key0, q_pos);
+      float mx = mx_own;
+      // the row maximum needs the other half's keys
       xch[((j & 1) * 2 + half) * kRows + t] = mx;
-      named_barrier(kBarIdSoftmax, kSoftmaxWarps * 32);
+      named_barrier(bar_id, group_threads);
       mx = fmaxf(mx, xch[((j & 1) * 2 + (half ^ 1)) * kRows + t]);
       float factor = 1.0f;
       if (mx > m_used + kLazy || m_used == -INFINITY) {      // tile 0 always lands here (key 0 is never masked)
@@ -325,49 +340,41 @@ __global__ void __launch_bounds__(pfu::kThreads, 2) prefill_umma_kernel(const Pr
         l_run *= factor;
       }
       const bool rescale = j > 0 && __any_sync(0xffffffffu, factor != 1.0f);
-
-      uint32_t pk[16];
-#pragma unroll
-      for (int c4 = 0; c4 < 8; ++c4) {
-        const float4 n4 = vn4[c4];
-        const float e0 = fast_exp2(__uint_as_float(s[4 * c4]) - m_used), e1 = fast_exp2(__uint_as_float(s[4 * c4 + 1]) - m_used);
-        const float e2 = fast_exp2(__uint_as_float(s[4 * c4 + 2]) - m_used), e3 = fast_exp2(__uint_as_float(s[4 * c4 + 3]) - m_used);
-        l_run += (e0 + e1) + (e2 + e3);
-        pk[2 * c4] = pack_half2(e0 * n4.x, e1 * n4.y);
-        pk[2 * c4 + 1] = pack_half2(e2 * n4.z, e3 * n4.w);
-      }
       if (rescale) {
 #pragma unroll 1
         for (int ch = 0; ch < 2; ++ch) {
           uint32_t o[32];
-          tmem_ld32(lane_base + kColO + 64 * half + 32 * ch, o);
+          tmem_ld32(o_col + 32 * ch, o);
           tmem_wait_ld();
 #pragma unroll
           for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * factor);
-          tmem_st32(lane_base + kColO + 64 * half + 32 * ch, o);
+          tmem_st32(o_col + 32 * ch, o);
         }
       }
-      tmem_st16(lane_base + kColS + 16 * half, pk);          // keys 2c, 2c+1 of the tile in column c
+      // pass 2: probabilities.  The scores are read again from TMEM, 16 columns at a time; the fp16 P of a chunk
+      // (keys 2c, 2c+1 in column c) goes straight over score columns this thread has already consumed.
+      l_run += diag ? row_probabilities<true>(s_col, kn, vn, m_used, key0, q_pos) : row_probabilities<false>(s_col, kn, vn, m_used, key0, q_pos);
       tmem_wait_st();
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(kBarPFull));
+      if (lane == 0) mbar_arrive(bar(kBarPFull + blk));
     }
-    // ---- epilogue part 1: normalised fp16 row of O into the staging area, 256-byte rows, chunk XOR (t & 15) --------------
-    if (alive) {   // the row sum needs the other half's keys (slot and phase follow on from the loop's use of the barrier)
+    // ---- epilogue part 1: normalised fp16 row of O into the staging area (the K stages), 256-byte rows, chunk XOR (row & 15)
+    if (alive) {   // the row sum needs the other half's keys
       const int j = n_tiles;
       xch[((j & 1) * 2 + half) * kRows + t] = l_run;
-      named_barrier(kBarIdSoftmax, kSoftmaxWarps * 32);
+      named_barrier(bar_id, group_threads);
       l_run += xch[((j & 1) * 2 + (half ^ 1)) * kRows + t];
-      alive = gw.wait(bar(kBarPvDone), (n_tiles - 1) & 1);
+      alive = gw.wait(bar(kBarPvDone + blk), (n_tiles - 1) & 1);
     }
     if (alive) {
       tc_fence_after_sync();
       const float inv = alpha_v / fmaxf(l_run, 1e-30f);
+      const uint32_t row = static_cast<uint32_t>(blk * kRows + t);
 #pragma unroll 1
       for (int ch = 0; ch < 2; ++ch) {
         uint32_t o[32];
-        tmem_ld32(lane_base + kColO + 64 * half + 32 * ch, o);
+        tmem_ld32(o_col + 32 * ch, o);
         tmem_wait_ld();
 #pragma unroll
         for (int c8 = 0; c8 < 4; ++c8) {
@@ -376,14 +383,14 @@ __global__ void __launch_bounds__(pfu::kThreads, 2) prefill_umma_kernel(const Pr
           for (int i = 0; i < 4; ++i)
             h[i] = pack_half2(__uint_as_float(o[8 * c8 + 2 * i]) * inv, __uint_as_float(o[8 * c8 + 2 * i + 1]) * inv);
           const uint32_t chunk = static_cast<uint32_t>(8 * half + ch * 4 + c8);
-          sts128(base + kOffK + t * 256u + ((chunk ^ (t & 15u)) << 4), h[0], h[1], h[2], h[3]);
+          sts128(base + kOffK + row * 256u + ((chunk ^ (row & 15u)) << 4), h[0], h[1], h[2], h[3]);
         }
       }
     }
     tc_fence_before_sync();
   } else if (warp < kSoftmaxWarps + kProducerWarps) {
     // ================= producers: slots -> unit-level fp16 tiles ============================================================
-    const int pt = tid - kSoftmaxWarps * 32;                 // 0..127
+    const int pt = tid - kSoftmaxWarps * 32;                 // 0..255
     const uint32_t k_copies = lut_stride / (KB == 4 ? 4u : 8u), v_copies = lut_stride / (VB == 4 ? 4u : 8u);
     const uint32_t lutk_lane = base + kOffLut + (lane & (k_copies - 1)) * (KB == 4 ? 4u : 8u);
     const uint32_t lutv_lane = base + kOffLut + lutv_off + (lane & (v_copies - 1)) * (VB == 4 ? 4u : 8u);
@@ -391,8 +398,7 @@ __global__ void __launch_bounds__(pfu::kThreads, 2) prefill_umma_kernel(const Pr
     const int64_t row_stride = static_cast<int64_t>(p.H_kv) * kSlotBytes;
     const float kscale = p.scale_log2 * alpha_k;
     bool bad_block = false;
-    GroupWaiter gw{reinterpret_cast<volatile int*>(sm + kOffBar + kOffVerdict + 8), abort_flag, kBarIdProducer, kProducerWarps * 32, 0,
-                   pt == 0};
+    GroupWaiter gw{reinterpret_cast<volatile int*>(sm + kOffBar + kOffVerdict + 16), abort_flag, kBarIdProducer, kProducerThreads, 0, pt == 0};
 
     // Block ids are read one fetch ahead of the slots they address, slot words one tile ahead of their expansion:
     // neither global-memory latency sits on the tile-to-tile chain.
@@ -411,14 +417,14 @@ __global__ void __launch_bounds__(pfu::kThreads, 2) prefill_umma_kernel(const Pr
     struct VRegs { uint4 w[kItV]; };
     int kblk[kItK], vblk[kItV];                               // block ids of the next tile to fetch
 #pragma unroll
-    for (int it = 0; it < kItK; ++it) kblk[it] = block_id((pt + 128 * it) / KB, 0);
+    for (int it = 0; it < kItK; ++it) kblk[it] = block_id((pt + kProducerThreads * it) / KB, 0);
 #pragma unroll
-    for (int it = 0; it < kItV; ++it) vblk[it] = block_id((pt + 128 * it) / VB, 0);
+    for (int it = 0; it < kItV; ++it) vblk[it] = block_id((pt + kProducerThreads * it) / VB, 0);
     auto load_k = [&](int j, KRegs& r) {
       if (j >= n_tiles) return;
 #pragma unroll
       for (int it = 0; it < kItK; ++it) {
-        const int x = pt + 128 * it, nl = x / KB, quad = x % KB;
+        const int x = pt + kProducerThreads * it, nl = x / KB, quad = x % KB;
         const uint8_t* src = slot_ptr(kblk[it], nl, j);
         r.w[it] = __ldg(reinterpret_cast<const uint4*>(src + 16 * quad));
         if (quad == 0) r.n[it] = __ldg(reinterpret_cast<const float2*>(src + 16 * KB + 16 * VB));
@@ -429,18 +435,18 @@ __global__ void __launch_bounds__(pfu::kThreads, 2) prefill_umma_kernel(const Pr
       if (j >= n_tiles) return;
 #pragma unroll
       for (int it = 0; it < kItV; ++it) {
-        const int x = pt + 128 * it, nl = x / VB, quad = x % VB;
+        const int x = pt + kProducerThreads * it, nl = x / VB, quad = x % VB;
         r.w[it] = __ldg(reinterpret_cast<const uint4*>(slot_ptr(vblk[it], nl, j) + 16 * KB + 16 * quad));
         vblk[it] = block_id(nl, j + 1);
       }
     };
     auto expand_k = [&](int j, const KRegs& r) {
-      const uint32_t tile = base + kOffK + (j & 1) * 16384u;
+      const uint32_t tile = base + kOffK + (j & 1) * kTileBytes;
       float* kn = reinterpret_cast<float*>(sm + kOffKn) + (j & 3) * kKeys;
       float* vn = reinterpret_cast<float*>(sm + kOffVn) + (j & 3) * kKeys;
 #pragma unroll
       for (int it = 0; it < kItK; ++it) {
-        const int x = pt + 128 * it, nl = x / KB, quad = x % KB;
+        const int x = pt + kProducerThreads * it, nl = x / KB, quad = x % KB;
         if (quad == 0) { kn[nl] = r.n[it].x * kscale; vn[nl] = r.n[it].y; }
         expand_quad<KB>(tile, lutk_lane, lut_stride, r.w[it], nl, quad);
       }
@@ -451,16 +457,15 @@ __global__ void __launch_bounds__(pfu::kThreads, 2) prefill_umma_kernel(const Pr
     auto expand_v = [&](int j, const VRegs& r) {
 #pragma unroll
       for (int it = 0; it < kItV; ++it) {
-        const int x = pt + 128 * it, nl = x / VB, quad = x % VB;
-        expand_quad<VB>(base + kOffV + (j & 1) * 16384u, lutv_lane, lut_stride, r.w[it], nl, quad);
+        const int x = pt + kProducerThreads * it, nl = x / VB, quad = x % VB;
+        expand_quad<VB>(base + kOffV + (j & 1) * kTileBytes, lutv_lane, lut_stride, r.w[it], nl, quad);
       }
       fence_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(kBarVFull + (j & 1)));
     };
     // Tile i is expanded from registers that were filled while tile i-1 was being expanded; its K stage is free once
-    // Q K^T of tile i-2 is done, its V stage once P V of tile i-2 is done.  (One copy of each piece of code: the kernel
-    // has to stay small enough for the instruction cache.)
+    // Q K^T of tile i-2 is done for both blocks, its V stage once P V of tile i-2 is done for both blocks.
     KRegs kr;
     VRegs vr;
     load_k(0, kr);
@@ -478,62 +483,58 @@ __global__ void __launch_bounds__(pfu::kThreads, 2) prefill_umma_kernel(const Pr
   } else {
     // ================= MMA issuer ==================================================================================================
     if (lane == 0) {
-      constexpr uint32_t idesc_qk = instr_desc_f16(kRows, kKeys, false, false);
-      constexpr uint32_t idesc_pv = instr_desc_f16(kRows, kHeadDim, false, true);
-      // every operand descriptor is made once: the issue loop is then one instruction per matrix product
-      uint64_t kdesc[2][8], vdesc[2][4];
-#pragma unroll
-      for (int st = 0; st < 2; ++st) {
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-          kdesc[st][ks] = smem_desc_sw128(base + kOffK + st * 16384u + (ks >> 2) * 8192u + (ks & 3) * 32u, 16, 1024);
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks) vdesc[st][ks] = smem_desc_sw128(base + kOffV + st * 16384u + ks * 2048u, 8192, 1024);
-      }
-      const uint32_t tq = tmem + kColQ, ts = tmem + kColS, to = tmem + kColO;
+      constexpr uint32_t idesc = instr_desc_f16(kRows, 128, false, false);          // S = Q K^T: both operands K-major
+      constexpr uint32_t idesc_pv = instr_desc_f16(kRows, kHeadDim, false, true);    // O += P V: V is MN-major
       bool alive = true;
-      auto issue_qk = [&](int st) {
-        mma_ts<false>(ts, tq, kdesc[st][0], idesc_qk);
+      // P of keys [64 h, 64 h + 64) sits in columns [64 h, 64 h + 32) of the block's scores: contraction step ks (16 keys) reads
+      // columns 64 (ks / 4) + 8 (ks % 4).
+      auto issue_qk = [&](int blk, int j) {
+        const uint32_t q = base + kOffQ + blk * kTileBytes, k = base + kOffK + (j & 1) * kTileBytes, s = tmem + kColS + 128 * blk;
 #pragma unroll
-        for (int ks = 1; ks < 8; ++ks) mma_ts<true>(ts, tq + 8 * ks, kdesc[st][ks], idesc_qk);
-        mma_commit(bar(kBarSFull));
-        mma_commit(bar(kBarKEmpty + st));
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint32_t off = (ks >> 2) * kColBlockBytes + (ks & 3) * 32u;
+          mma_ss(s, smem_desc_sw128(q + off, 16, 1024), smem_desc_sw128(k + off, 16, 1024), idesc, ks > 0 ? 1u : 0u);
+        }
+        mma_commit(bar(kBarSFull + blk));
+        if (blk == kBlocks - 1) mma_commit(bar(kBarKEmpty + (j & 1)));
       };
-      auto issue_pv = [&](int st, bool first) {
-        if (first) mma_ts<false>(to, ts, vdesc[st][0], idesc_pv);
-        else mma_ts<true>(to, ts, vdesc[st][0], idesc_pv);
+      auto issue_pv = [&](int blk, int j) {
+        const uint32_t v = base + kOffV + (j & 1) * kTileBytes, s = tmem + kColS + 128 * blk, o = tmem + kColO + 128 * blk;
 #pragma unroll
-        for (int ks = 1; ks < 4; ++ks) mma_ts<true>(to, ts + 8 * ks, vdesc[st][ks], idesc_pv);
-        mma_commit(bar(kBarPvDone));
-        mma_commit(bar(kBarVEmpty + st));
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint64_t bd = smem_desc_sw128(v + ks * 2048u, kColBlockBytes, 1024);
+          const uint32_t a = s + 64 * (ks >> 2) + 8 * (ks & 3);
+          if (ks == 0 && j == 0) mma_ts<false>(o, a, bd, idesc_pv);
+          else mma_ts<true>(o, a, bd, idesc_pv);
+        }
+        mma_commit(bar(kBarPvDone + blk));
+        if (blk == kBlocks - 1) mma_commit(bar(kBarVEmpty + (j & 1)));
       };
       alive = mbar_wait(bar(kBarKFull), 0, abort_flag);
       if (alive) {
         tc_fence_after_sync();
-        issue_qk(0);
+        issue_qk(0, 0);
+        issue_qk(1, 0);
       }
-      for (int j = 0; j < n_tiles && alive; j += 2) {   // two tiles per turn: the stage index is a constant in each half
-        alive = mbar_wait(bar(kBarVFull), (j >> 1) & 1, abort_flag) && mbar_wait(bar(kBarPFull), j & 1, abort_flag);
-        if (!alive) break;
-        tc_fence_after_sync();
-        issue_pv(0, j == 0);
-        if (j + 1 >= n_tiles) break;
-        // the scores of the next tile overwrite P: issued behind P V, executed behind it
-        alive = mbar_wait(bar(kBarKFull + 1), (j >> 1) & 1, abort_flag);
-        if (!alive) break;
-        tc_fence_after_sync();
-        issue_qk(1);
-        alive = mbar_wait(bar(kBarVFull + 1), (j >> 1) & 1, abort_flag) && mbar_wait(bar(kBarPFull), (j + 1) & 1, abort_flag);
-        if (!alive) break;
-        tc_fence_after_sync();
-        issue_pv(1, false);
-        if (j + 2 >= n_tiles) break;
-        alive = mbar_wait(bar(kBarKFull), ((j + 2) >> 1) & 1, abort_flag);
-        if (!alive) break;
-        tc_fence_after_sync();
-        issue_qk(0);
+#pragma unroll 1
+      for (int j = 0; j < n_tiles && alive; ++j) {
+        alive = mbar_wait(bar(kBarVFull + (j & 1)), (j >> 1) & 1, abort_flag);
+#pragma unroll 1
+        for (int blk = 0; blk < kBlocks && alive; ++blk) {
+          alive = mbar_wait(bar(kBarPFull + blk), j & 1, abort_flag);
+          if (!alive) break;
+          tc_fence_after_sync();
+          issue_pv(blk, j);
+          if (j + 1 < n_tiles) {   // the scores of the next tile overwrite P: issued behind P V, executed behind it
+            if (blk == 0) alive = mbar_wait(bar(kBarKFull + ((j + 1) & 1)), ((j + 1) >> 1) & 1, abort_flag);
+            if (!alive) break;
+            tc_fence_after_sync();
+            issue_qk(blk, j + 1);
+          }
+        }
       }
-      if (alive) mbar_wait(bar(kBarPvDone), (n_tiles - 1) & 1, abort_flag);   // nothing in flight when TMEM is released
+      for (int blk = 0; blk < kBlocks && alive; ++blk)        // nothing in flight when TMEM is released
+        alive = mbar_wait(bar(kBarPvDone + blk), (n_tiles - 1) & 1, abort_flag);
     }
     __syncwarp();
     tc_fence_before_sync();
@@ -543,10 +544,10 @@ __global__ void __launch_bounds__(pfu::kThreads, 2) prefill_umma_kernel(const Pr
   __syncthreads();
   const bool failed = *abort_flag != 0;
   if (!failed) {
-    for (int t = warp; t < kRows; t += kThreads / 32) {
-      const int pos = p0 + t / G, hl = t % G;
+    for (int r = warp; r < kBlocks * kRows; r += kThreads / 32) {
+      const int pos = p0 + r / G, hl = r % G;
       if (pos >= q_len || hl >= g) continue;
-      const uint32_t src = base + kOffK + t * 256u + ((static_cast<uint32_t>(lane >> 1) ^ (t & 15u)) << 4) + (lane & 1) * 8u;
+      const uint32_t src = base + kOffK + r * 256u + ((static_cast<uint32_t>(lane >> 1) ^ (r & 15u)) << 4) + (lane & 1) * 8u;
       const uint4 raw4 = lds128(src & ~15u);   // (volatile read: the row was written by another warp)
       const uint2 raw = (lane & 1) ? make_uint2(raw4.z, raw4.w) : make_uint2(raw4.x, raw4.y);
       float v[4];
@@ -577,7 +578,7 @@ static int launch_prefill_umma(const PrefillUmmaParams& p, int max_query_len, in
       return check_launch("prefill: shared memory opt-in");
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
-  const int per_tile = pfu::kRows / G;
+  const int per_tile = pfu::kBlocks * pfu::kRows / G;
   const dim3 grid((max_query_len + per_tile - 1) / per_tile, p.H_kv, B);
   prefill_umma_kernel<G, KB, VB><<<grid, pfu::kThreads, pfu::kSmemBytes, st>>>(p);
   return check_launch("prefill kernel");
