@@ -9,12 +9,12 @@
 // 128 at a time; the two blocks run half a step apart, so one block's softmax overlaps the other's matrix products:
 //
 //   producer warps (8)    cache slots -> registers (one tile ahead) -> unit-level fp16 tiles in shared memory (128-byte
-//                         swizzled rows, the layout tcgen05.mma reads), norms to side arrays
+//                         swizzled rows, the layout tcgen05.mma reads; V rows already times their norm), key norms to a
+//                         side array
 //   MMA warp (1 thread)   per block: S = Q K^T (128x128x128, Q and K from shared memory) and O += P V (128x128x128, P from
 //                         tensor memory, V from shared memory)
 //   softmax warps (2 x 8) two threads per row (64 keys each): TMEM -> registers, scale by the key norm, mask, online
-//                         maximum with lazy rescaling of O, exp2, fold the value norm, fp16 P -> TMEM over the thread's
-//                         own score columns
+//                         maximum with lazy rescaling of O, exp2, fp16 P -> TMEM over the thread's own score columns
 //
 // Tensor memory (512 columns): S of block b at [128 b, 128 b + 128), O of block b at [256 + 128 b, ...).  P of the keys
 // [64 h, 64 h + 64) lives in the first 32 columns of the same thread's scores, [128 b + 64 h, + 32).
@@ -52,8 +52,7 @@ constexpr int kTileBytes = 32768, kColBlockBytes = 16384;
 constexpr int kOffLut = 196608;                // 16 KB of code tables
 constexpr int kLutBytes = 16384;
 constexpr int kOffKn = kOffLut + kLutBytes;    // 4 x 128 floats: key norm * softmax scale * log2(e) * alpha_k
-constexpr int kOffVn = kOffKn + 2048;          // 4 x 128 floats: value norm
-constexpr int kOffXch = kOffVn + 2048;         // 2 blocks x 2 parities x 2 halves x 128 floats: row maxima / sums of the two threads of a row
+constexpr int kOffXch = kOffKn + 2048;         // 2 blocks x 2 parities x 2 halves x 128 floats: row maxima / sums of the two threads of a row
 constexpr int kOffBar = kOffXch + 4096;        // mbarriers, TMEM address, flags
 constexpr int kSmemBytes = kOffBar + 256 + 1024;   // + slack for the 1024-byte alignment
 
@@ -138,8 +137,14 @@ __device__ __forceinline__ void fill_code_table(uint8_t* lut, int stride, const 
 // Expand 16 bytes of codes (one quad of a slot) of token row `nl` into fp16 chunks of a 128-row tile.
 // tile: shared address of column block 0 (block 1 is kColBlockBytes further).  quad: index of the 16 bytes in the row's codes.
 // lut_lane: table address + this lane's copy; stride: bytes per entry row.
-template <int BITS>
-__device__ __forceinline__ void expand_quad(uint32_t tile, uint32_t lut_lane, uint32_t stride, const uint4& w, int nl, int quad) {
+// scale: a half2 (norm, norm) every expanded pair is multiplied by, or 0 for none.
+__device__ __forceinline__ uint32_t hmul2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+template <int BITS, bool SCALED>
+__device__ __forceinline__ void expand_quad(uint32_t tile, uint32_t lut_lane, uint32_t stride, const uint4& w, int nl, int quad, uint32_t scale) {
   const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
   if (BITS == 4) {
 #pragma unroll
@@ -150,6 +155,10 @@ __device__ __forceinline__ void expand_quad(uint32_t tile, uint32_t lut_lane, ui
       v[1] = lds32(lut_lane + ((x >> 8) & 0xffu) * stride);
       v[2] = lds32(lut_lane + ((x >> 16) & 0xffu) * stride);
       v[3] = lds32(lut_lane + (x >> 24) * stride);
+      if (SCALED) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v[i] = hmul2(v[i], scale);
+      }
       const int c16 = quad * 4 + wi;                       // 16-byte chunk of the row: 8 coordinates
       sts128(tile + (c16 >> 3) * kColBlockBytes + sw128(nl, c16 & 7), v[0], v[1], v[2], v[3]);
     }
@@ -160,7 +169,8 @@ __device__ __forceinline__ void expand_quad(uint32_t tile, uint32_t lut_lane, ui
 #pragma unroll
       for (int hb = 0; hb < 2; ++hb) {                     // two code bytes = 8 coordinates = one chunk
         const uint32_t b0 = (x >> (16 * hb)) & 0xffu, b1 = (x >> (16 * hb + 8)) & 0xffu;
-        const uint2 lo = lds64(lut_lane + b0 * stride), hi = lds64(lut_lane + b1 * stride);
+        uint2 lo = lds64(lut_lane + b0 * stride), hi = lds64(lut_lane + b1 * stride);
+        if (SCALED) { lo.x = hmul2(lo.x, scale); lo.y = hmul2(lo.y, scale); hi.x = hmul2(hi.x, scale); hi.y = hmul2(hi.y, scale); }
         const int c16 = quad * 8 + wi * 2 + hb;
         sts128(tile + (c16 >> 3) * kColBlockBytes + sw128(nl, c16 & 7), lo.x, lo.y, hi.x, hi.y);
       }
@@ -169,37 +179,41 @@ __device__ __forceinline__ void expand_quad(uint32_t tile, uint32_t lut_lane, ui
 }
 
 // One thread's 64 scores of a tile (columns s_col .. s_col + 63 of its TMEM lane), scaled by the key norms kn[0..63].
-// MASK: keys beyond q_pos (the row's diagonal) count as minus infinity.
+// MASK: keys beyond q_pos (the row's diagonal) count as minus infinity.  The next 16 columns are requested before the
+// current ones are worked on (tcgen05.wait::ld covers every load issued so far).
 template <bool MASK>
 __device__ __forceinline__ float row_max(uint32_t s_col, const float* kn, int key0, int q_pos) {
   float mx = -INFINITY;
+  uint32_t s[2][16];
+  umma::tmem_ld16(s_col, s[0]);
 #pragma unroll
   for (int ch = 0; ch < 4; ++ch) {
-    uint32_t s[16];
-    umma::tmem_ld16(s_col + 16 * ch, s);
     umma::tmem_wait_ld();
+    if (ch < 3) umma::tmem_ld16(s_col + 16 * (ch + 1), s[(ch + 1) & 1]);
 #pragma unroll
     for (int c = 0; c < 16; ++c) {
-      float x = __uint_as_float(s[c]) * kn[16 * ch + c];
+      float x = __uint_as_float(s[ch & 1][c]) * kn[16 * ch + c];
       if (MASK) x = key0 + 16 * ch + c > q_pos ? -INFINITY : x;
       mx = fmaxf(mx, x);
     }
   }
   return mx;
 }
-// exp2(score * kn - m) for the same 64 scores; P = probability * vn as fp16 pairs into columns s_col .. s_col + 31.
-// Returns the sum of the probabilities.
+// exp2(score * kn - m) for the same 64 scores; P as fp16 pairs into columns s_col .. s_col + 31 (the value norms are
+// already inside the V tile).  Returns the sum of the probabilities.
 template <bool MASK>
-__device__ __forceinline__ float row_probabilities(uint32_t s_col, const float* kn, const float* vn, float m, int key0, int q_pos) {
+__device__ __forceinline__ float row_probabilities(uint32_t s_col, const float* kn, float m, int key0, int q_pos) {
   float sum0 = 0.f, sum1 = 0.f;
+  uint32_t s[2][16];
+  umma::tmem_ld16(s_col, s[0]);
 #pragma unroll
   for (int ch = 0; ch < 4; ++ch) {
-    uint32_t s[16], pk[8];
-    umma::tmem_ld16(s_col + 16 * ch, s);
+    uint32_t pk[8];
     umma::tmem_wait_ld();
+    if (ch < 3) umma::tmem_ld16(s_col + 16 * (ch + 1), s[(ch + 1) & 1]);
 #pragma unroll
     for (int c = 0; c < 16; c += 2) {
-      float a0 = fmaf(__uint_as_float(s[c]), kn[16 * ch + c], -m), a1 = fmaf(__uint_as_float(s[c + 1]), kn[16 * ch + c + 1], -m);
+      float a0 = fmaf(__uint_as_float(s[ch & 1][c]), kn[16 * ch + c], -m), a1 = fmaf(__uint_as_float(s[ch & 1][c + 1]), kn[16 * ch + c + 1], -m);
       if (MASK) {
         a0 = key0 + 16 * ch + c > q_pos ? -INFINITY : a0;
         a1 = key0 + 16 * ch + c + 1 > q_pos ? -INFINITY : a1;
@@ -207,7 +221,7 @@ __device__ __forceinline__ float row_probabilities(uint32_t s_col, const float* 
       const float e0 = fast_exp2(a0), e1 = fast_exp2(a1);
       sum0 += e0;
       sum1 += e1;
-      pk[c / 2] = pack_half2(e0 * vn[16 * ch + c], e1 * vn[16 * ch + c + 1]);
+      pk[c / 2] = pack_half2(e0, e1);
     }
     umma::tmem_st8(s_col + 8 * ch, pk);
   }
@@ -315,7 +329,6 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
 #pragma unroll 1
     for (int j = 0; j < n_tiles; ++j) {
       const float* kn = reinterpret_cast<const float*>(sm + kOffKn) + (j & 3) * kKeys + 64 * half;
-      const float* vn = reinterpret_cast<const float*>(sm + kOffVn) + (j & 3) * kKeys + 64 * half;
       // the norms come straight from the producers (slot j & 3 is rewritten only for tile j + 4), the scores from the MMA;
       // Q K^T of tile j was issued behind P V of tile j - 1 of this block, so its O is at rest as well
       if (gw.leader && !umma::mbar_wait(bar(kBarNorms + (j & 3)), (j >> 2) & 1, abort_flag)) {}   // (a failure shows in the next verdict)
@@ -353,7 +366,7 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
       }
       // pass 2: probabilities.  The scores are read again from TMEM, 16 columns at a time; the fp16 P of a chunk
       // (keys 2c, 2c+1 in column c) goes straight over score columns this thread has already consumed.
-      l_run += diag ? row_probabilities<true>(s_col, kn, vn, m_used, key0, q_pos) : row_probabilities<false>(s_col, kn, vn, m_used, key0, q_pos);
+      l_run += diag ? row_probabilities<true>(s_col, kn, m_used, key0, q_pos) : row_probabilities<false>(s_col, kn, m_used, key0, q_pos);
       tmem_wait_st();
       tc_fence_before_sync();
       __syncwarp();
@@ -413,8 +426,8 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
       if (static_cast<unsigned>(blk) >= static_cast<unsigned>(p.num_blocks)) { bad_block = true; blk = 0; }
       return p.cache + (static_cast<int64_t>(blk) * p.block_size + in_block) * row_stride + kvh * kSlotBytes;
     };
-    struct KRegs { uint4 w[kItK]; float2 n[kItK]; };
-    struct VRegs { uint4 w[kItV]; };
+    struct KRegs { uint4 w[kItK]; float n[kItK]; };
+    struct VRegs { uint4 w[kItV]; float n[kItV]; };
     int kblk[kItK], vblk[kItV];                               // block ids of the next tile to fetch
 #pragma unroll
     for (int it = 0; it < kItK; ++it) kblk[it] = block_id((pt + kProducerThreads * it) / KB, 0);
@@ -427,7 +440,7 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
         const int x = pt + kProducerThreads * it, nl = x / KB, quad = x % KB;
         const uint8_t* src = slot_ptr(kblk[it], nl, j);
         r.w[it] = __ldg(reinterpret_cast<const uint4*>(src + 16 * quad));
-        if (quad == 0) r.n[it] = __ldg(reinterpret_cast<const float2*>(src + 16 * KB + 16 * VB));
+        if (quad == 0) r.n[it] = __ldg(reinterpret_cast<const float*>(src + 16 * KB + 16 * VB));
         kblk[it] = block_id(nl, j + 1);
       }
     };
@@ -436,19 +449,20 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
 #pragma unroll
       for (int it = 0; it < kItV; ++it) {
         const int x = pt + kProducerThreads * it, nl = x / VB, quad = x % VB;
-        r.w[it] = __ldg(reinterpret_cast<const uint4*>(slot_ptr(vblk[it], nl, j) + 16 * KB + 16 * quad));
+        const uint8_t* src = slot_ptr(vblk[it], nl, j);
+        r.w[it] = __ldg(reinterpret_cast<const uint4*>(src + 16 * KB + 16 * quad));
+        r.n[it] = __ldg(reinterpret_cast<const float*>(src + 16 * KB + 16 * VB + 4));
         vblk[it] = block_id(nl, j + 1);
       }
     };
     auto expand_k = [&](int j, const KRegs& r) {
       const uint32_t tile = base + kOffK + (j & 1) * kTileBytes;
       float* kn = reinterpret_cast<float*>(sm + kOffKn) + (j & 3) * kKeys;
-      float* vn = reinterpret_cast<float*>(sm + kOffVn) + (j & 3) * kKeys;
 #pragma unroll
       for (int it = 0; it < kItK; ++it) {
         const int x = pt + kProducerThreads * it, nl = x / KB, quad = x % KB;
-        if (quad == 0) { kn[nl] = r.n[it].x * kscale; vn[nl] = r.n[it].y; }
-        expand_quad<KB>(tile, lutk_lane, lut_stride, r.w[it], nl, quad);
+        if (quad == 0) kn[nl] = r.n[it] * kscale;
+        expand_quad<KB, false>(tile, lutk_lane, lut_stride, r.w[it], nl, quad, 0u);
       }
       fence_async_smem();
       __syncwarp();
@@ -458,7 +472,8 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
 #pragma unroll
       for (int it = 0; it < kItV; ++it) {
         const int x = pt + kProducerThreads * it, nl = x / VB, quad = x % VB;
-        expand_quad<VB>(base + kOffV + (j & 1) * kTileBytes, lutv_lane, lut_stride, r.w[it], nl, quad);
+        // the value norm goes into the tile (fp16 product), so the probabilities need no per-key factor
+        expand_quad<VB, true>(base + kOffV + (j & 1) * kTileBytes, lutv_lane, lut_stride, r.w[it], nl, quad, pack_half2(r.n[it], r.n[it]));
       }
       fence_async_smem();
       __syncwarp();
