@@ -182,6 +182,13 @@ int cda_b200_varlen_fwd_hadamard(const void* Q, const void* k_rot, const void* v
                                  const int32_t* seqused_k, int64_t T, int B, int H_q, int H_kv,
                                  int max_query_len, int max_seq_len, float scale, void* stream);
 
+/* Decode `rows` rows of packed indices (16*bits bytes each) and fp32 norms into fp16 rows of 128: out = fp16(cb[idx] * norm),
+ * the rotated-frame K or V the "dequantise, then dense attention" baseline attends over.
+ * Replaces the dequant op behind dequantize_compressed_kv(k_idx, k_norm, v_idx, v_norm, cb_k, cb_v),
+ * cda/kernels_vllm_fa2_fork/interface.py:138-162 (one call per tensor). */
+int cda_b200_dequantize_rows(const void* idx, const float* norm, const float* cb, void* out, int64_t rows, int bits,
+                             void* stream);
+
 /* The paged prefill kernel hands tiles between its warps through mbarriers with bounded waits.  A wait that gives up
  * ends its CTA, leaves that CTA's output rows unwritten and sets a per-device flag that makes later prefill CTAs and
  * launches return at once.  Returns 1 if the flag is set on the current device, 0 if not, a negative status on a CUDA

@@ -38,6 +38,7 @@ PROTOTYPES = {
                                      _i, _f, _p]),
     "cda_b200_varlen_fwd_hadamard": (_i, [_p, _p, _p, _p, _p, _p, _p, _i64, _i, _i, _i, _i, _i, _f, _p]),
     "cda_b200_prefill_fault": (_i, []),
+    "cda_b200_dequantize_rows": (_i, [_p, _p, _p, _p, _i64, _i, _p]),
 }
 
 

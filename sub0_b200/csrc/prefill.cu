@@ -60,6 +60,28 @@ __global__ void __launch_bounds__(256) cache_to_dense_kernel(const uint8_t* __re
   *reinterpret_cast<uint2*>(v_out + row * kHeadDim + 4 * lane) = vz;
 }
 
+// Flat variant for the "dequantise, then dense attention" baseline: one row = one (key, KV head); indices and norms in
+// separate tensors (Compressor.encode's CompressedSlot, cda/algorithm/compression.py:196-205).
+template <int BITS>
+__global__ void __launch_bounds__(256) dequantize_rows_kernel(const uint8_t* __restrict__ idx, const float* __restrict__ norm,
+                                                              const float* __restrict__ cb, __half* __restrict__ out, int64_t rows) {
+  __shared__ float s_cb[16];
+  if (threadIdx.x < 16) s_cb[threadIdx.x] = threadIdx.x < (BITS == 4 ? 16 : 4) ? cb[threadIdx.x] : 0.f;
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  for (int64_t row = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5); row < rows; row += static_cast<int64_t>(gridDim.x) * 8) {
+    const uint8_t* src = idx + row * (16 * BITS);
+    const float n = norm[row];
+    int i4[4];
+    if (BITS == 4) { const uint8_t b0 = src[2 * lane], b1 = src[2 * lane + 1]; i4[0] = b0 >> 4; i4[1] = b0 & 15; i4[2] = b1 >> 4; i4[3] = b1 & 15; }
+    else { const uint8_t b0 = src[lane]; i4[0] = b0 >> 6; i4[1] = (b0 >> 4) & 3; i4[2] = (b0 >> 2) & 3; i4[3] = b0 & 3; }
+    float f[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) f[i] = s_cb[i4[i]] * n;      // Compressor.decode, compression.py:356-360
+    *reinterpret_cast<uint2*>(out + row * kHeadDim + 4 * lane) = pack_half4(f);
+  }
+}
+
 // ---- attention ------------------------------------------------------------------------------------------------------------------
 constexpr int kPfWarps = 4;
 constexpr int kPfThreads = kPfWarps * 32;
@@ -447,6 +469,23 @@ extern "C" int cda_b200_cache_to_dense_rotated(const void* kv_cache, const int32
   else CDA_LAUNCH_DENSE(2, 4);
 #undef CDA_LAUNCH_DENSE
   return check_launch("cache_to_dense_rotated");
+}
+
+extern "C" int cda_b200_dequantize_rows(const void* idx, const float* norm, const float* cb, void* out, int64_t rows, int bits,
+                                       void* stream) {
+  if (rows < 0) return fail(CDA_ERR_BAD_ARG, "dequantize_rows: negative rows");
+  if (!bits_ok(bits)) return fail(CDA_ERR_UNSUPPORTED, "dequantize_rows: bits must be 2 or 4");
+  if (rows == 0) return CDA_OK;
+  if (!idx || !norm || !cb || !out) return fail(CDA_ERR_BAD_ARG, "dequantize_rows: null pointer");
+  if (reinterpret_cast<uintptr_t>(out) & 7u) return fail(CDA_ERR_BAD_ALIGN, "dequantize_rows: out must be 8-byte aligned");
+  const int64_t want = (rows + 7) / 8, cap = static_cast<int64_t>(device_sm_count(-1)) * 8;
+  const unsigned grid = static_cast<unsigned>(want < cap ? want : cap);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (bits == 4)
+    dequantize_rows_kernel<4><<<grid, 256, 0, st>>>(static_cast<const uint8_t*>(idx), norm, cb, static_cast<__half*>(out), rows);
+  else
+    dequantize_rows_kernel<2><<<grid, 256, 0, st>>>(static_cast<const uint8_t*>(idx), norm, cb, static_cast<__half*>(out), rows);
+  return check_launch("dequantize_rows");
 }
 
 static int prefill_common_checks(const char* who, const void* Q, void* out, const int32_t* cu_q, int64_t T, int B, int H_q, int H_kv,
