@@ -1,15 +1,12 @@
-// Prefill path: (1) gather + decode of the paged cache to dense rotated-frame fp16, and (2) causal variable-length
-// flash attention whose K/V producer decodes codebook indices straight from the paged cache into shared memory,
-// with the Hadamard rotation of Q fused in front and the inverse rotation of O fused behind.
+// Dense helpers of the prefill path: (1) gather + decode of the paged cache to dense rotated-frame fp16 (and the flat
+// variant for separately stored indices and norms), (2) causal variable-length flash attention over such dense
+// rotated-frame K/V with the Hadamard rotation of Q fused in front and the inverse rotation of O fused behind, and the
+// C-ABI entry points of the whole prefill path.  The fused paged prefill kernel itself lives in prefill_umma.cu.
 //
-// Attention kernel (prefill_kernel): one CTA = 4 warps = 64 query rows of one (sequence, query head); each warp
-// owns 16 rows, keeps its rotated Q fragments in registers and walks the allowed keys 64 at a time:
-//   * PAGED source: the 64 slots of the next tile are fetched with 16-byte cp.async copies into a double-buffered
-//     staging area while the current tile is being multiplied; all threads then expand codes through fp16-pair
-//     tables into XOR-swizzled [64][128] fp16 K and V tiles.  Norms are not folded into the tiles: the K norm
-//     (times scale*log2e) multiplies score columns, the V norm multiplies probabilities.
-//   * DENSE source: tiles of already decoded rotated K/V rows are copied with cp.async (norm factors are 1).
-//   * S = Q K^T and O += P V run on mma.m16n8k16 (fp16 in, fp32 accumulate) with ldmatrix operand loads.
+// Attention kernel (dense_prefill_kernel): one CTA = 4 warps = 64 query rows of one (sequence, query head); each warp
+// owns 16 rows, keeps its rotated Q fragments in registers and walks the allowed keys 64 at a time: tiles of decoded
+// rotated K/V rows are copied with cp.async into XOR-swizzled [64][128] fp16 tiles; S = Q K^T and O += P V run on
+// mma.m16n8k16 (fp16 in, fp32 accumulate) with ldmatrix operand loads.
 // Epilogue: O/l is rounded to fp16, staged in shared memory, rotated back by butterflies and stored.
 #include <cmath>
 
@@ -88,20 +85,11 @@ constexpr int kPfThreads = kPfWarps * 32;
 constexpr int kBM = 64;    // query rows per CTA
 constexpr int kBN = 64;    // keys per tile
 constexpr int kTileBytes = kBN * kHeadDim * 2;   // 16 KB
-constexpr int kLutRep = 8;                       // table replication (conflict damping) in the prefill kernel
 
 struct PrefillParams {
   const __half* q;
   __half* out;
   const int32_t* cu_q;
-  // paged source
-  const uint8_t* cache;
-  const int32_t* block_table;
-  const int32_t* seq_lens;
-  const float* cb_k;
-  const float* cb_v;
-  int block_size, bt_stride, num_blocks;
-  // dense source
   const __half* k_rot;
   const __half* v_rot;
   const int32_t* cu_k;
@@ -109,20 +97,7 @@ struct PrefillParams {
   int H_q, H_kv, group;
   float scale_log2;
 };
-
-template <int KB, int VB>
-struct PfGeom {
-  static constexpr int kSlotBytes = 16 * KB + 16 * VB + 16;
-  static constexpr int kStagingBytes = kBN * kSlotBytes;
-  static constexpr int kLutKWords = (KB == 4 ? 256 : 16) * kLutRep;
-  static constexpr int kLutVWords = (VB == 4 ? 256 : 16) * kLutRep;
-  // layout: [K tile | V tile | norms (2 x 64 floats) | staging x 2 | lut K | lut V]; Q and the output are staged in the K/V tiles
-  static constexpr int kNormOff = 2 * kTileBytes;
-  static constexpr int kStageOff = kNormOff + 2 * kBN * 4;
-  static constexpr int kLutOff = kStageOff + 2 * kStagingBytes;
-  static constexpr int kSmemPaged = kLutOff + (kLutKWords + kLutVWords) * 4;
-  static constexpr int kSmemDense = kStageOff;
-};
+constexpr int kDenseSmem = 2 * kTileBytes;     // [K tile | V tile]; Q and the output are staged in the K tile
 
 // byte offset of 16-byte chunk `ch` (0..15) of row `row` in a swizzled [rows][128] fp16 tile
 __device__ __forceinline__ int tile_off(int row, int ch) { return row * 256 + ((ch ^ (row & 7)) << 4); }
@@ -134,59 +109,10 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, u
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
 }
 
-template <int BITS>
-__device__ __forceinline__ void build_lut_rep(uint32_t* lut, const float* __restrict__ cb, int tid, float inv_alpha) {
-  constexpr int L = BITS == 4 ? 16 : 4;
-  constexpr int E = BITS == 4 ? 256 : 16;
-  for (int w = tid; w < E * kLutRep; w += kPfThreads) {
-    const int e = w / kLutRep;
-    const int first = BITS == 4 ? (e >> 4) : (e >> 2);
-    const int second = BITS == 4 ? (e & 15) : (e & 3);
-    lut[w] = pack_half2(__ldg(cb + (first & (L - 1))) * inv_alpha, __ldg(cb + (second & (L - 1))) * inv_alpha);
-  }
-}
-
-// Expand `nbytes` packed index bytes (one 64-coordinate half row when BITS == 4 and nbytes == 32; the whole
-// row when BITS == 2) from `src` into the 8 16-byte chunks starting at chunk `ch0` of row `row` of a tile.
-template <int BITS>
-__device__ __forceinline__ void expand_half_row(const uint8_t* src, const uint32_t* lut, uint8_t* tile, int row, int ch0) {
-  // BITS == 4: 32 bytes -> 64 values -> 8 chunks.  BITS == 2: 16 bytes -> 64 values -> 8 chunks.
-  constexpr int kWords = BITS == 4 ? 8 : 4;
-  uint32_t w[kWords];
-#pragma unroll
-  for (int i = 0; i < kWords / 4; ++i) {
-    const uint4 t = *reinterpret_cast<const uint4*>(src + 16 * i);
-    w[4 * i] = t.x; w[4 * i + 1] = t.y; w[4 * i + 2] = t.z; w[4 * i + 3] = t.w;
-  }
-#pragma unroll
-  for (int chn = 0; chn < 8; ++chn) {
-    uint32_t v[4];
-    if (BITS == 4) {          // chunk = 8 values = 4 bytes = one word
-      const uint32_t x = w[chn];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) v[i] = lut[((x >> (8 * i)) & 0xffu) * kLutRep];
-    } else {                  // chunk = 8 values = 2 bytes = half a word
-      const uint32_t x = w[chn >> 1] >> (16 * (chn & 1));
-      v[0] = lut[((x >> 4) & 0xfu) * kLutRep];
-      v[1] = lut[(x & 0xfu) * kLutRep];
-      v[2] = lut[((x >> 12) & 0xfu) * kLutRep];
-      v[3] = lut[((x >> 8) & 0xfu) * kLutRep];
-    }
-    *reinterpret_cast<uint4*>(tile + tile_off(row, ch0 + chn)) = make_uint4(v[0], v[1], v[2], v[3]);
-  }
-}
-
-template <int KB, int VB, bool PAGED>
-__global__ void __launch_bounds__(kPfThreads) prefill_kernel(const PrefillParams p) {
-  using Gm = PfGeom<KB, VB>;
+__global__ void __launch_bounds__(kPfThreads) dense_prefill_kernel(const PrefillParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   uint8_t* k_tile = smem;
   uint8_t* v_tile = smem + kTileBytes;
-  float* nk_s = reinterpret_cast<float*>(smem + Gm::kNormOff);
-  float* nv_s = nk_s + kBN;
-  uint8_t* staging = smem + Gm::kStageOff;
-  uint32_t* lut_k = reinterpret_cast<uint32_t*>(smem + Gm::kLutOff);
-  uint32_t* lut_v = lut_k + Gm::kLutKWords;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int r = lane >> 2, c = lane & 3;
@@ -195,23 +121,12 @@ __global__ void __launch_bounds__(kPfThreads) prefill_kernel(const PrefillParams
   const int q_len = p.cu_q[b + 1] - q_begin;
   const int i0 = mblk * kBM;
   if (i0 >= q_len) return;
-  const int k_len = PAGED ? p.seq_lens[b] : p.seqused_k[b];
+  const int k_len = p.seqused_k[b];
   const int offset = k_len - q_len;                     // query i sees keys 0 .. i + offset
   const int head = hq / p.group;
   int k_hi = i0 + kBM + offset;                         // exclusive bound of keys any row of this CTA may see
   k_hi = k_hi < k_len ? k_hi : k_len;
   const int n_tiles = k_hi > 0 ? (k_hi + kBN - 1) / kBN : 0;
-
-  // fp16 tables hold level / alpha; alpha_k is folded into the score scale, alpha_v into the final normalisation
-  float alpha_k = 1.f, alpha_v = 1.f;
-  if (PAGED) {
-    __shared__ float s_err[64];
-    __shared__ int s_idx[64];
-    find_table_scales<(KB == 4 ? 16 : 4), (VB == 4 ? 16 : 4)>(p.cb_k, p.cb_v, s_err, s_idx, alpha_k, alpha_v);
-    build_lut_rep<KB>(lut_k, p.cb_k, tid, 1.0f / alpha_k);
-    build_lut_rep<VB>(lut_v, p.cb_v, tid, 1.0f / alpha_v);
-  }
-  const float k_scale = p.scale_log2 * alpha_k;
 
   // ---- rotate the 16 query rows of this warp and stage them (swizzled) in the K tile ---------------------------------------
   for (int rr = 0; rr < 16; ++rr) {
@@ -234,23 +149,8 @@ __global__ void __launch_bounds__(kPfThreads) prefill_kernel(const PrefillParams
     for (int s = 0; s < 8; ++s) ldmatrix_x4(base + tile_off(row, 2 * s + chsel), qa[s][0], qa[s][1], qa[s][2], qa[s][3]);
   }
 
-  // ---- producer helpers ----------------------------------------------------------------------------------------------------------------
-  const int32_t* bt_row = PAGED ? p.block_table + static_cast<int64_t>(b) * p.bt_stride : nullptr;
-  auto issue_staging = [&](int kt) {      // PAGED: raw slots of tile kt -> staging[kt & 1]
-    uint8_t* dst = staging + (kt & 1) * Gm::kStagingBytes;
-    constexpr int kPieces = Gm::kSlotBytes / 16;
-    for (int ch = tid; ch < kBN * kPieces; ch += kPfThreads) {
-      const int tok = ch / kPieces, piece = ch - tok * kPieces;
-      const int n = kt * kBN + tok;
-      if (n < k_len) {
-        int blk = __ldg(bt_row + n / p.block_size);
-        if (blk < 0 || blk >= p.num_blocks) blk = 0;
-        const uint8_t* src = p.cache + ((static_cast<int64_t>(blk) * p.block_size + n % p.block_size) * p.H_kv + head) * Gm::kSlotBytes + piece * 16;
-        cp_async16(smem_addr(dst + tok * Gm::kSlotBytes + piece * 16), src);
-      }
-    }
-  };
-  auto issue_dense = [&](int kt) {        // DENSE: fp16 rows of tile kt -> swizzled K and V tiles
+  // ---- producer -------------------------------------------------------------------------------------------------------------------------
+  auto issue_dense = [&](int kt) {        // fp16 rows of tile kt -> swizzled K and V tiles
     const int64_t k0 = p.cu_k[b];
     for (int ch = tid; ch < kBN * 16; ch += kPfThreads) {
       const int tok = ch >> 4, piece = ch & 15;
@@ -273,35 +173,14 @@ __global__ void __launch_bounds__(kPfThreads) prefill_kernel(const PrefillParams
 #pragma unroll
     for (int i = 0; i < 4; ++i) oacc[n][i] = 0.f;
 
-  if (PAGED && n_tiles > 0) issue_staging(0);
-  cp_async_commit();
-  __syncthreads();   // every warp has its Q fragments: the K tile may be overwritten; tables are visible
+  __syncthreads();   // every warp has its Q fragments: the K tile may be overwritten
 
   const int row_lo = i0 + warp * 16 + r;     // query index of accumulator rows (c0,c1); (c2,c3) are row_lo + 8
 #pragma unroll 1
   for (int kt = 0; kt < n_tiles; ++kt) {
-    if (PAGED) {
-      if (kt + 1 < n_tiles) issue_staging(kt + 1);
-      cp_async_commit();
-      cp_async_wait<1>();
-      __syncthreads();
-      // expand: thread -> (token = tid & 63, coordinate half = tid >> 6)
-      const int tok = tid & 63, half = tid >> 6;
-      const uint8_t* slot = staging + (kt & 1) * Gm::kStagingBytes + tok * Gm::kSlotBytes;
-      expand_half_row<KB>(slot + half * (8 * KB), lut_k + (lane & (kLutRep - 1)), k_tile, tok, 8 * half);
-      expand_half_row<VB>(slot + 16 * KB + half * (8 * VB), lut_v + (lane & (kLutRep - 1)), v_tile, tok, 8 * half);
-      if (half == 0) {
-        const bool ok = kt * kBN + tok < k_len;
-        const float2 nn = *reinterpret_cast<const float2*>(slot + 16 * KB + 16 * VB);
-        nk_s[tok] = ok ? nn.x * k_scale : 0.f;
-        nv_s[tok] = ok ? nn.y : 0.f;
-      }
-    } else {
-      issue_dense(kt);
-      cp_async_commit();
-      if (tid < kBN) { nk_s[tid] = p.scale_log2; nv_s[tid] = 1.f; }
-      cp_async_wait<0>();
-    }
+    issue_dense(kt);
+    cp_async_commit();
+    cp_async_wait<0>();
     __syncthreads();
 
     // ---- S = Q K^T (16 x 64 per warp) ---------------------------------------------------------------------------------------------------
@@ -324,14 +203,13 @@ __global__ void __launch_bounds__(kPfThreads) prefill_kernel(const PrefillParams
           mma_16816(sacc[2 * np + 1], qa[s][0], qa[s][1], qa[s][2], qa[s][3], b2, b3);
         }
     }
-    // ---- column scale (K norm * scale * log2e), causal / length mask, online softmax ---------------------------------------------------------
+    // ---- softmax scale * log2e, causal / length mask, online softmax ---------------------------------------------------------
     const int key0 = kt * kBN;
     const bool need_mask = key0 + kBN - 1 > i0 + warp * 16 + offset || key0 + kBN > k_len;
     float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
     for (int n = 0; n < 8; ++n) {
-      const float2 f = *reinterpret_cast<const float2*>(nk_s + n * 8 + 2 * c);
-      sacc[n][0] *= f.x; sacc[n][1] *= f.y; sacc[n][2] *= f.x; sacc[n][3] *= f.y;
+      sacc[n][0] *= p.scale_log2; sacc[n][1] *= p.scale_log2; sacc[n][2] *= p.scale_log2; sacc[n][3] *= p.scale_log2;
       if (need_mask) {
         const int key = key0 + n * 8 + 2 * c;
         const int lim0 = row_lo + offset, lim1 = row_lo + 8 + offset;    // last visible key of each row
@@ -360,16 +238,15 @@ __global__ void __launch_bounds__(kPfThreads) prefill_kernel(const PrefillParams
 #pragma unroll
     for (int n = 0; n < 16; ++n) { oacc[n][0] *= fs[0]; oacc[n][1] *= fs[0]; oacc[n][2] *= fs[1]; oacc[n][3] *= fs[1]; }
 
-    uint32_t pa[4][4];   // probabilities (times V norm) as A fragments: k-step s covers keys 16s .. 16s+15
+    uint32_t pa[4][4];   // probabilities as A fragments: k-step s covers keys 16s .. 16s+15
 #pragma unroll
     for (int n = 0; n < 8; ++n) {
       const float p0 = fast_exp2(sacc[n][0] - ms[0]), p1 = fast_exp2(sacc[n][1] - ms[0]);
       const float p2 = fast_exp2(sacc[n][2] - ms[1]), p3 = fast_exp2(sacc[n][3] - ms[1]);
       l_run[0] += p0 + p1;
       l_run[1] += p2 + p3;
-      const float2 g = *reinterpret_cast<const float2*>(nv_s + n * 8 + 2 * c);
-      pa[n >> 1][(n & 1) * 2] = pack_half2(p0 * g.x, p1 * g.y);
-      pa[n >> 1][(n & 1) * 2 + 1] = pack_half2(p2 * g.x, p3 * g.y);
+      pa[n >> 1][(n & 1) * 2] = pack_half2(p0, p1);
+      pa[n >> 1][(n & 1) * 2 + 1] = pack_half2(p2, p3);
     }
     // ---- O += P V -----------------------------------------------------------------------------------------------------------------------------
     {
@@ -386,7 +263,7 @@ __global__ void __launch_bounds__(kPfThreads) prefill_kernel(const PrefillParams
           mma_16816(oacc[2 * dp + 1], pa[s][0], pa[s][1], pa[s][2], pa[s][3], b2, b3);
         }
     }
-    if (!PAGED) __syncthreads();   // dense tiles are refilled at the top of the next iteration
+    __syncthreads();   // the tiles are refilled at the top of the next iteration
   }
   cp_async_wait<0>();
   __syncthreads();                 // all warps are done with the K/V tiles: reuse the K tile for the output
@@ -397,7 +274,7 @@ __global__ void __launch_bounds__(kPfThreads) prefill_kernel(const PrefillParams
     l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
     l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
   }
-  const float inv0 = l_run[0] > 0.f ? alpha_v / l_run[0] : 0.f, inv1 = l_run[1] > 0.f ? alpha_v / l_run[1] : 0.f;
+  const float inv0 = l_run[0] > 0.f ? 1.0f / l_run[0] : 0.f, inv1 = l_run[1] > 0.f ? 1.0f / l_run[1] : 0.f;
   {
     const int row0 = warp * 16 + r, row1 = row0 + 8;
 #pragma unroll
@@ -421,21 +298,18 @@ __global__ void __launch_bounds__(kPfThreads) prefill_kernel(const PrefillParams
   }
 }
 
-template <int KB, int VB, bool PAGED>
-static int launch_prefill(const PrefillParams& p, int max_query_len, int B, cudaStream_t st) {
-  using Gm = PfGeom<KB, VB>;
-  constexpr int smem = PAGED ? Gm::kSmemPaged : Gm::kSmemDense;
+static int launch_dense_prefill(const PrefillParams& p, int max_query_len, int B, cudaStream_t st) {
   static bool configured[64];
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64 || !configured[dev]) {
-    if (cudaFuncSetAttribute(prefill_kernel<KB, VB, PAGED>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+    if (cudaFuncSetAttribute(dense_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDenseSmem) != cudaSuccess)
       return check_launch("prefill: shared memory opt-in");
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   const dim3 grid((max_query_len + kBM - 1) / kBM, p.H_q, B);
-  prefill_kernel<KB, VB, PAGED><<<grid, kPfThreads, smem, st>>>(p);
-  return check_launch("prefill kernel");
+  dense_prefill_kernel<<<grid, kPfThreads, kDenseSmem, st>>>(p);
+  return check_launch("dense prefill kernel");
 }
 
 }  // namespace cda
@@ -538,5 +412,5 @@ extern "C" int cda_b200_varlen_fwd_hadamard(const void* Q, const void* k_rot, co
   p.k_rot = static_cast<const __half*>(k_rot); p.v_rot = static_cast<const __half*>(v_rot);
   p.cu_k = cu_seqlens_k; p.seqused_k = seqused_k;
   p.H_q = H_q; p.H_kv = H_kv; p.group = H_q / H_kv; p.scale_log2 = scale * kLog2e;
-  return launch_prefill<4, 4, false>(p, max_query_len, B, static_cast<cudaStream_t>(stream));
+  return launch_dense_prefill(p, max_query_len, B, static_cast<cudaStream_t>(stream));
 }
