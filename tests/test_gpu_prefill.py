@@ -150,3 +150,57 @@ def test_dense_source_and_raw_kv_paths():
         ref[q0:q1] = O.gqa_attention(Q[q0:q1].permute(1, 0, 2)[None], k.permute(1, 0, 2)[None], v.permute(1, 0, 2)[None],
                                      group=4, causal=True)[0].permute(1, 0, 2)
     torch.testing.assert_close(out2.cpu().float(), ref.float(), rtol=1e-2, atol=1e-2)
+
+
+@pytest.mark.parametrize("group,H_kv", [(4, 2), (8, 1)])
+def test_large_ragged_prefill_matches_the_dense_route(group, H_kv):
+    """At sizes the CPU oracle does not finish in seconds (tens of 128-key tiles per row block, a chunk with a long
+    compressed past): the fused tcgen05 kernel against the independent two-kernel route of this library -- bit-exact
+    dense loader, then the mma.sync attention kernel -- on a cache written by the GPU encoder."""
+    from sub0_b200 import codebook
+    from sub0_b200.kernels_cuda import fa2_cda
+    from sub0_b200.kernels_cuda.hmma_loader import load_fa2_cda_varlen_fused
+    from sub0_b200.kernels_cuda.wrappers import paged_encode_fused_cuda
+    lens, q_lens = [5000, 3333, 4096, 777], [5000, 3333, 700, 777]
+    H_q = H_kv * group
+    gen = torch.Generator().manual_seed(4242 + group)
+    cb = codebook.default_codebook(16).to(DEV)
+    nblk = [-(-n // 16) for n in lens]
+    order = torch.randperm(sum(nblk) + 2, generator=gen)
+    cache = torch.zeros((sum(nblk) + 2) * 16, H_kv, 144, dtype=torch.uint8, device=DEV)
+    bt = torch.zeros(len(lens), max(nblk), dtype=torch.int32)
+    used = 0
+    for b, n in enumerate(lens):
+        bt[b, :nblk[b]] = order[used:used + nblk[b]].to(torch.int32)
+        used += nblk[b]
+        k, v = Cs.rows(gen, n, H_kv, outliers=True).to(DEV), Cs.rows(gen, n, H_kv).to(DEV)
+        slots = (bt[b, torch.arange(n) // 16].long() * 16 + torch.arange(n) % 16).to(torch.int32).to(DEV)
+        paged_encode_fused_cuda(k, v, slots, cache, cb_K=cb, cb_V=cb)
+    cu = torch.zeros(len(lens) + 1, dtype=torch.int32)
+    cu[1:] = torch.tensor(q_lens).cumsum(0)
+    Q = Cs.rows(gen, int(cu[-1]), H_q).to(DEV)
+    bt, cu, sl = bt.to(DEV), cu.to(DEV), torch.tensor(lens, dtype=torch.int32, device=DEV)
+    out = torch.full_like(Q, float("nan"))
+    fa2_cda.fa2_cda_prefill_varlen_v1(Q, cache, bt, cu, sl, out, cb_K=cb, cb_V=cb, group_size=group, block_size=16,
+                                      max_query_len=max(q_lens), max_seq_len=max(lens), fuse_fa2_epilogue=True)
+    max_len = -(-max(lens) // 16) * 16
+    k_rot, v_rot = fa2_cda.paged_cache_to_dense_rotated(cache, bt, sl, cb_K=cb, cb_V=cb, block_size=16, max_seq_len=max_len)
+    ref = torch.full_like(Q, float("nan"))
+    cu_k = torch.arange(len(lens) + 1, dtype=torch.int32, device=DEV) * max_len
+    load_fa2_cda_varlen_fused().cda_fa2_varlen_fwd_hadamard(Q, k_rot, v_rot, ref, cu, cu_k, sl, max(q_lens), max_len, 1.0 / 128 ** 0.5)
+    torch.cuda.synchronize()
+    # two independent fp16 pipelines, each within the path's tolerance of the oracle: their distance may reach twice that
+    assert not bool(out.isnan().any()) and not bool(ref.isnan().any())
+    _, ratio, cos = Cs.close(out.cpu(), ref.cpu())
+    assert ratio <= 2.0 and cos >= 0.9999, f"large ragged g{group}: distance/tolerance {ratio:.3f}, cosine {cos:.6f}"
+    # the same cache, last tokens of every sequence as a chunk with a long compressed past: cheap enough for the CPU oracle
+    q2 = [200, 150, 300, 100]
+    cu2 = torch.zeros(len(lens) + 1, dtype=torch.int32)
+    cu2[1:] = torch.tensor(q2).cumsum(0)
+    Q2 = Cs.rows(gen, int(cu2[-1]), H_q)
+    want = O.paged_prefill(Q2, cache.cpu(), bt.cpu(), cu2, sl.cpu(), cb_K=cb.cpu(), cb_V=cb.cpu(), group=group, block_size=16)
+    out2 = torch.full_like(Q2, float("nan"), device=DEV)
+    fa2_cda.fa2_cda_prefill_varlen_v1(Q2.to(DEV), cache, bt, cu2.to(DEV), sl, out2, cb_K=cb, cb_V=cb, group_size=group, block_size=16,
+                                      max_query_len=max(q2), max_seq_len=max(lens), fuse_fa2_epilogue=True)
+    torch.cuda.synchronize()
+    assert_close(out2.cpu(), want, f"long past g{group}")
