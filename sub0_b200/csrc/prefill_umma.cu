@@ -59,7 +59,7 @@ constexpr int kSmemBytes = kOffBar + 256 + 1024;   // + slack for the 1024-byte 
 // barrier slots (8 bytes each) inside kOffBar
 constexpr int kBarKFull = 0, kBarKEmpty = 2, kBarVFull = 4, kBarVEmpty = 6, kBarSFull = 8, kBarPFull = 10, kBarPvDone = 12,
               kBarNorms = 14;   // 18 barriers
-constexpr int kOffTmemAddr = 160, kOffAbort = 164, kOffVerdict = 168;   // verdict words: 2 per waiting group (3 groups)
+constexpr int kOffTmemAddr = 160, kOffAbort = 164, kOffOutcome = 168;   // outcome words: 2 per waiting group (3 groups)
 
 __device__ __forceinline__ uint32_t lds32(uint32_t a) {
   uint32_t v;
@@ -89,21 +89,21 @@ __device__ __forceinline__ void unpack_half4(const uint2& raw, float (&v)[4]) {
 }
 // A group of warps waits for an mbarrier phase: only lane 0 of the group's first warp polls, the others are parked on
 // a named hardware barrier (a parked warp takes no issue slots from the warps that are working).  The poller always
-// arrives at the named barrier -- its own wait is bounded -- and publishes its verdict in one of two words used
+// arrives at the named barrier -- its own wait is bounded -- and publishes its outcome in one of two words used
 // alternately (it can be at most one call ahead of the slowest reader), so the result is the same for every thread
 // of the group and nobody is left behind at a later barrier.
 __device__ __forceinline__ void named_barrier(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 struct GroupWaiter {
-  volatile int* verdict;     // two words in shared memory
+  volatile int* outcome;     // two words in shared memory
   volatile int* abort_flag;
   int id, nthreads, turn;
   bool leader;               // lane 0 of the group's first warp
   __device__ __forceinline__ bool wait(uint32_t bar, uint32_t parity) {
-    if (leader) verdict[turn] = umma::mbar_wait(bar, parity, abort_flag) ? 1 : 0;
+    if (leader) outcome[turn] = umma::mbar_wait(bar, parity, abort_flag) ? 1 : 0;
     named_barrier(id, nthreads);
-    const bool ok = verdict[turn] != 0;
+    const bool ok = outcome[turn] != 0;
     turn ^= 1;
     return ok;
   }
@@ -325,13 +325,13 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
     const int bar_id = kBarIdSoftmax + blk, group_threads = kSoftmaxWarpsPerBlock * 32;
     float m_used = -INFINITY, l_run = 0.f;
     bool alive = true;
-    GroupWaiter gw{reinterpret_cast<volatile int*>(sm + kOffBar + kOffVerdict + 8 * blk), abort_flag, bar_id, group_threads, 0, w == 0 && lane == 0};
+    GroupWaiter gw{reinterpret_cast<volatile int*>(sm + kOffBar + kOffOutcome + 8 * blk), abort_flag, bar_id, group_threads, 0, w == 0 && lane == 0};
 #pragma unroll 1
     for (int j = 0; j < n_tiles; ++j) {
       const float* kn = reinterpret_cast<const float*>(sm + kOffKn) + (j & 3) * kKeys + 64 * half;
       // the norms come straight from the producers (slot j & 3 is rewritten only for tile j + 4), the scores from the MMA;
       // Q K^T of tile j was issued behind P V of tile j - 1 of this block, so its O is at rest as well
-      if (gw.leader && !umma::mbar_wait(bar(kBarNorms + (j & 3)), (j >> 2) & 1, abort_flag)) {}   // (a failure shows in the next verdict)
+      if (gw.leader && !umma::mbar_wait(bar(kBarNorms + (j & 3)), (j >> 2) & 1, abort_flag)) {}   // (a failure shows in the next outcome)
       alive = gw.wait(bar(kBarSFull + blk), j & 1);
       if (!alive) break;
       tc_fence_after_sync();
@@ -411,7 +411,7 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
     const int64_t row_stride = static_cast<int64_t>(p.H_kv) * kSlotBytes;
     const float kscale = p.scale_log2 * alpha_k;
     bool bad_block = false;
-    GroupWaiter gw{reinterpret_cast<volatile int*>(sm + kOffBar + kOffVerdict + 16), abort_flag, kBarIdProducer, kProducerThreads, 0, pt == 0};
+    GroupWaiter gw{reinterpret_cast<volatile int*>(sm + kOffBar + kOffOutcome + 16), abort_flag, kBarIdProducer, kProducerThreads, 0, pt == 0};
 
     // Block ids are read one fetch ahead of the slots they address, slot words one tile ahead of their expansion:
     // neither global-memory latency sits on the tile-to-tile chain.
