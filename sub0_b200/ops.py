@@ -310,6 +310,15 @@ def prefill_varlen(Q: Tensor, kv_cache: Tensor, block_table: Tensor, cu_seqlens_
                                       int(max_seq_len), cache.shape[0], cache.shape[2], kb, vb, s, _stream(Q.device)))
 
 
+def prefill_fault() -> bool:
+    """True if a CTA of the paged prefill kernel ever gave up on one of its bounded waits on the current device (its
+    rows of the output were then left unwritten, and later prefill launches return at once).  Synchronises the device."""
+    rc = lib.cda_b200_prefill_fault()
+    if rc < 0:
+        check(rc)
+    return rc != 0
+
+
 def varlen_fwd_hadamard(Q: Tensor, k_rot: Tensor, v_rot: Tensor, output: Tensor, cu_seqlens_q: Tensor,
                         cu_seqlens_k: Tensor, seqused_k: Tensor, max_query_len: int, max_seq_len: int,
                         scale: float) -> None:
