@@ -178,28 +178,4 @@ __device__ __forceinline__ void find_table_scales(const float* __restrict__ cb_a
   alpha_b = LB == 4 ? 1.0f + win[1] * (1.0f / 8192.0f) : 1.0f;
 }
 
-// ---- codebook look-up tables in shared memory ----------------------------------------------------
-// A table maps a code (one byte holding two 4-bit indices, or one nibble holding two 2-bit indices) to
-// the fp16 pair (level[first index], level[second index]); the first index is the higher bits, i.e.
-// the lower coordinate.  Every entry is replicated once per lane (entry e of lane l at word e*32+l) so
-// that a warp-wide gather with arbitrary codes never has a bank conflict.
-template <int BITS>
-struct Lut {
-  static constexpr int kEntries = BITS == 4 ? 256 : 16;
-  static constexpr int kWords = kEntries * 32;
-  static constexpr int kBytes = kWords * 4;
-};
-
-template <int BITS>
-__device__ __forceinline__ void build_lut(uint32_t* lut, const float* __restrict__ cb, int tid, int nthreads) {
-  constexpr int L = BITS == 4 ? 16 : 4;
-  constexpr int E = Lut<BITS>::kEntries;
-  for (int w = tid; w < E * 32; w += nthreads) {
-    const int e = w >> 5;
-    const int first = BITS == 4 ? (e >> 4) : (e >> 2);
-    const int second = BITS == 4 ? (e & 15) : (e & 3);
-    lut[w] = pack_half2(__ldg(cb + (first & (L - 1))), __ldg(cb + (second & (L - 1))));
-  }
-}
-
 }  // namespace cda

@@ -8,23 +8,10 @@
 
 namespace cda {
 
-// Nearest level of the ascending table `cb` (L entries), following Compressor.quantize_unit
-// (cda/algorithm/compression.py:298-313) literally: upper = number of levels strictly below x, clamped to L-1;
-// lower = upper-1 clamped to 0; upper wins only if strictly closer.  Used to derive the thresholds below and by the
-// reference kernels of the tests.
-template <int L>
-__device__ __forceinline__ int nearest_level(float x, const float* cb) {
-  int upper = 0;
-#pragma unroll
-  for (int i = 0; i < L; ++i) upper += (cb[i] < x) ? 1 : 0;
-  upper = min(upper, L - 1);
-  const int lower = max(upper - 1, 0);
-  const float d_upper = fabsf(cb[upper] - x);
-  const float d_lower = fabsf(x - cb[lower]);
-  return d_upper < d_lower ? upper : lower;
-}
-
-// The rule above is monotone in x, so it is the same as counting thresholds: index(x) = #{i : x > T[i]}, where T[i] is
+// Index selection of Compressor.quantize_unit (cda/algorithm/compression.py:298-313): upper = number of levels
+// strictly below x, clamped to L-1; lower = upper-1 clamped to 0; upper wins only if strictly closer
+// (fabsf(cb[upper] - x) < fabsf(x - cb[lower])), ties go to lower.
+// That rule is monotone in x, so it is the same as counting thresholds: index(x) = #{i : x > T[i]}, where T[i] is
 // the largest float in [cb[i], cb[i+1]] for which the rule still answers i.  T[i] is found by bisection over the
 // ordered integer image of the floats, evaluating the rule's own comparison fabsf(cb[i+1] - x) < fabsf(x - cb[i]) in
 // fp32 exactly as the rule does, so the result is bit-identical, ties and rounding included.
