@@ -383,8 +383,7 @@ __global__ void __launch_bounds__(W * 32, 1) decode_split_kernel(const DecodePar
   const int cta_groups = t_end > t_begin ? (t_end - t_begin + 15) >> 4 : 0;
   const int ng = cta_groups > sub ? (cta_groups - sub + R - 1) / R : 0;   // groups of this warp
 
-  const int part = split * R + sub;
-  const int64_t prow0 = (static_cast<int64_t>(part) * p.B + b) * p.H_q + head * g;   // partial row of query 0
+  const int64_t prow0 = (static_cast<int64_t>(split) * p.B + b) * p.H_q + head * g;   // partial row of query 0
 
   // ---- shared window layout: warp rings fill the space before the 64 KB-aligned table, the rest follow it -----------
   const uint32_t win0 = smem_addr(smem);
@@ -395,7 +394,7 @@ __global__ void __launch_bounds__(W * 32, 1) decode_split_kernel(const DecodePar
   const bool fits = win_end - win0 <= static_cast<uint32_t>(p.smem_bytes);
   if (cta_groups == 0 || !fits) {   // nothing in range (short sequence) or no room: empty partials, no set-up
     if (!fits && tid == 0) atomicOr(p.status, 2);
-    if (lane < g) *reinterpret_cast<float2*>(p.part_ml + (prow0 + lane) * 2) = make_float2(-INFINITY, 0.f);
+    if (sub == 0 && lane < g) *reinterpret_cast<float2*>(p.part_ml + (prow0 + lane) * 2) = make_float2(-INFINITY, 0.f);
     return;
   }
   const uint32_t ring = warp < rings_before ? win0 + warp * Cfg::kRingBytes
@@ -477,7 +476,7 @@ __global__ void __launch_bounds__(W * 32, 1) decode_split_kernel(const DecodePar
       cx.qf[4 * i] = t.x; cx.qf[4 * i + 1] = t.y; cx.qf[4 * i + 2] = t.z; cx.qf[4 * i + 3] = t.w;
     }
   }
-  __syncthreads();   // tables visible to every warp; every lane is done with its query rows (the only CTA barrier)
+  __syncthreads();   // tables visible to every warp; every lane is done with its query rows
 
   cx.base_k = lut_win | (lane << 2);
   cx.base_v = cx.base_k | 128u;
@@ -504,11 +503,12 @@ __global__ void __launch_bounds__(W * 32, 1) decode_split_kernel(const DecodePar
     for (; j0 + NS <= steady_end; j0 += NS) RingSteps<G, KB, VB, NS, 0, true>::run(cx, j0, false);
 #pragma unroll 1
     for (; j0 < ng; j0 += NS) RingSteps<G, KB, VB, NS, 0, false>::run(cx, j0, tail_masked);
-    cp_async_wait<0>();
     if (cx.bad_block) atomicOr(p.status, 1);
   }
+  cp_async_wait<0>();   // also the copies a warp without groups started above
+  __syncwarp();         // every lane is done reading the ring before it is reused below
 
-  // ---- write this warp's partial -------------------------------------------------------------------------------------------
+  // ---- combine the partials of the warps that share a head, write one partial per (split, head) ----------------------------
   float l0 = cx.l_run[0], l1 = cx.l_run[1];
 #pragma unroll
   for (int mask = 4; mask < 32; mask <<= 1) {
@@ -516,38 +516,64 @@ __global__ void __launch_bounds__(W * 32, 1) decode_split_kernel(const DecodePar
     l1 += __shfl_xor_sync(0xffffffffu, l1, mask);
   }
   const float m0 = l0 > 0.f ? cx.m_run[0] : -INFINITY, m1 = l1 > 0.f ? cx.m_run[1] : -INFINITY;
+  // every warp parks (O[q][128], m[q], l[q]) for its G query rows in its own ring: rows of 132 floats
+  constexpr int kRowFloats = kHeadDim + 4;   // 528-byte rows keep the 16-byte reads aligned
+  static_assert(G * kRowFloats * 4 <= Cfg::kRingBytes, "a warp's partial must fit its ring");
+  auto ring_of = [&](int w) -> float* {
+    const uint32_t a = w < rings_before ? win0 + w * Cfg::kRingBytes : lut_win + kLutWindow + (w - rings_before) * Cfg::kRingBytes;
+    return reinterpret_cast<float*>(smem + (a - win0));
+  };
+  {
+    float* st = ring_of(warp);
+    if (G == 4) {
+      const int parity = c >> 1, q0 = 2 * (c & 1);
 #pragma unroll
-  for (int u = 0; u < 4; ++u)
-#pragma unroll
-    for (int t = 0; t < NT; ++t)
-#pragma unroll
-      for (int i = 0; i < 4; ++i) cx.oacc[u][t][i] *= alpha_v;   // the V table holds level / alpha_v
-  if (G == 4) {
-    const int parity = c >> 1, q0 = 2 * (c & 1);
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int d = 16 * r + 4 * u + parity;
-      if (q0 < g) { p.part_o[(prow0 + q0) * kHeadDim + d] = cx.oacc[u][0][0]; p.part_o[(prow0 + q0) * kHeadDim + d + 2] = cx.oacc[u][0][2]; }
-      if (q0 + 1 < g) { p.part_o[(prow0 + q0 + 1) * kHeadDim + d] = cx.oacc[u][0][1]; p.part_o[(prow0 + q0 + 1) * kHeadDim + d + 2] = cx.oacc[u][0][3]; }
-    }
-    if (r == 0 && c < 2) {
-      if (q0 < g) *reinterpret_cast<float2*>(p.part_ml + (prow0 + q0) * 2) = make_float2(m0, l0);
-      if (q0 + 1 < g) *reinterpret_cast<float2*>(p.part_ml + (prow0 + q0 + 1) * 2) = make_float2(m1, l1);
-    }
-  } else {
-    const int q0 = 2 * c;
-#pragma unroll
-    for (int u = 0; u < 4; ++u)
-#pragma unroll
-      for (int t = 0; t < NT; ++t) {
-        const int d = 16 * r + 4 * u + t;
-        if (q0 < g) { p.part_o[(prow0 + q0) * kHeadDim + d] = cx.oacc[u][t][0]; p.part_o[(prow0 + q0) * kHeadDim + d + 2] = cx.oacc[u][t][2]; }
-        if (q0 + 1 < g) { p.part_o[(prow0 + q0 + 1) * kHeadDim + d] = cx.oacc[u][t][1]; p.part_o[(prow0 + q0 + 1) * kHeadDim + d + 2] = cx.oacc[u][t][3]; }
+      for (int u = 0; u < 4; ++u) {
+        const int d = 16 * r + 4 * u + parity;
+        st[q0 * kRowFloats + d] = cx.oacc[u][0][0] * alpha_v; st[q0 * kRowFloats + d + 2] = cx.oacc[u][0][2] * alpha_v;
+        st[(q0 + 1) * kRowFloats + d] = cx.oacc[u][0][1] * alpha_v; st[(q0 + 1) * kRowFloats + d + 2] = cx.oacc[u][0][3] * alpha_v;
       }
-    if (r == 0) {
-      if (q0 < g) *reinterpret_cast<float2*>(p.part_ml + (prow0 + q0) * 2) = make_float2(m0, l0);
-      if (q0 + 1 < g) *reinterpret_cast<float2*>(p.part_ml + (prow0 + q0 + 1) * 2) = make_float2(m1, l1);
+      if (r == 0 && c < 2) {
+        st[q0 * kRowFloats + kHeadDim] = m0; st[q0 * kRowFloats + kHeadDim + 1] = l0;
+        st[(q0 + 1) * kRowFloats + kHeadDim] = m1; st[(q0 + 1) * kRowFloats + kHeadDim + 1] = l1;
+      }
+    } else {
+      const int q0 = 2 * c;
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+          const int d = 16 * r + 4 * u + t;
+          st[q0 * kRowFloats + d] = cx.oacc[u][t][0] * alpha_v; st[q0 * kRowFloats + d + 2] = cx.oacc[u][t][2] * alpha_v;
+          st[(q0 + 1) * kRowFloats + d] = cx.oacc[u][t][1] * alpha_v; st[(q0 + 1) * kRowFloats + d + 2] = cx.oacc[u][t][3] * alpha_v;
+        }
+      if (r == 0) {
+        st[q0 * kRowFloats + kHeadDim] = m0; st[q0 * kRowFloats + kHeadDim + 1] = l0;
+        st[(q0 + 1) * kRowFloats + kHeadDim] = m1; st[(q0 + 1) * kRowFloats + kHeadDim + 1] = l1;
+      }
     }
+  }
+  __syncthreads();
+  if (sub != 0) return;
+  // the first warp of every head adds up its R warps (lane l owns coordinates 4l .. 4l+3 of each query row)
+  for (int q = 0; q < g; ++q) {
+    float mt = -INFINITY;
+    for (int s2 = 0; s2 < R; ++s2) mt = fmaxf(mt, ring_of((warp & (hpc - 1)) + s2 * hpc)[q * kRowFloats + kHeadDim]);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float lt = 0.f;
+    if (mt != -INFINITY) {
+      for (int s2 = 0; s2 < R; ++s2) {
+        const float* src = ring_of((warp & (hpc - 1)) + s2 * hpc) + q * kRowFloats;
+        const float ms = src[kHeadDim];
+        if (ms == -INFINITY) continue;
+        const float wgt = fast_exp2(ms - mt);
+        const float4 o = *reinterpret_cast<const float4*>(src + 4 * lane);
+        acc.x += o.x * wgt; acc.y += o.y * wgt; acc.z += o.z * wgt; acc.w += o.w * wgt;
+        lt += src[kHeadDim + 1] * wgt;
+      }
+    }
+    *reinterpret_cast<float4*>(p.part_o + (prow0 + q) * kHeadDim + 4 * lane) = acc;
+    if (lane == 0) *reinterpret_cast<float2*>(p.part_ml + (prow0 + q) * 2) = make_float2(mt, lt);
   }
 }
 
@@ -733,7 +759,7 @@ static Plan make_plan(int B, int H_kv, int max_seq_len, int num_splits, int sms)
   int tps = ((n + S - 1) / S + 15) / 16 * 16;
   pl.tokens_per_split = tps;
   pl.splits = (n + tps - 1) / tps;
-  pl.parts = pl.splits * pl.warps_per_head;
+  pl.parts = pl.splits;            // the warps of a head are combined inside the CTA
   return pl;
 }
 

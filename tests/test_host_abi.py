@@ -93,10 +93,8 @@ def test_split_planning_properties(lib):
         s = L.cda_b200_decode_plan_splits(B, Hkv, n, -1)
         assert 1 <= s <= max(1, -(-n // 16))
         ws = L.cda_b200_decode_workspace_bytes(B, Hkv * 4, Hkv, n, 0, -1)
-        heads_per_cta = max(h for h in (1, 2, 4, 8) if h <= Hkv and Hkv % h == 0)
-        parts = s * (16 // heads_per_cta)
-        assert ws == 256 + parts * B * Hkv * 4 * 130 * 4
-        assert L.cda_b200_decode_workspace_bytes(B, Hkv * 4, Hkv, n, 3, -1) <= 256 + 3 * (16 // heads_per_cta) * B * Hkv * 4 * 520
+        assert ws == 256 + s * B * Hkv * 4 * 130 * 4       # one partial row of 128 + 2 floats per split and query head
+        assert L.cda_b200_decode_workspace_bytes(B, Hkv * 4, Hkv, n, 3, -1) <= 256 + 3 * B * Hkv * 4 * 520
     assert L.cda_b200_decode_plan_splits(32, 8, 65536, -1) == 9       # 288 CTAs: two rounds of 148 SMs, 97 % full
     assert L.cda_b200_decode_plan_splits(4, 8, 65536, -1) == 37       # 148 CTAs: exactly one round
     assert L.cda_b200_decode_plan_splits(32, 8, 4096, -1) == 4        # one round; a second would double the fixed cost
