@@ -554,30 +554,57 @@ __global__ void __launch_bounds__(W * 32, 1) decode_split_kernel(const DecodePar
     }
   }
   __syncthreads();
-  if (sub != 0) return;
-  // the first warp of every head adds up its R warps (lane l owns coordinates 4l .. 4l+3 of each query row)
-  for (int q = 0; q < g; ++q) {
-    float mt = -INFINITY;
-    for (int s2 = 0; s2 < R; ++s2) mt = fmaxf(mt, ring_of((warp & (hpc - 1)) + s2 * hpc)[q * kRowFloats + kHeadDim]);
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    float lt = 0.f;
-    if (mt != -INFINITY) {
-      for (int s2 = 0; s2 < R; ++s2) {
-        const float* src = ring_of((warp & (hpc - 1)) + s2 * hpc) + q * kRowFloats;
-        const float ms = src[kHeadDim];
-        if (ms == -INFINITY) continue;
-        const float wgt = fast_exp2(ms - mt);
-        const float4 o = *reinterpret_cast<const float4*>(src + 4 * lane);
-        acc.x += o.x * wgt; acc.y += o.y * wgt; acc.z += o.z * wgt; acc.w += o.w * wgt;
-        lt += src[kHeadDim + 1] * wgt;
-      }
+  // (head, query row) pairs are dealt over all warps; lane s < R holds the (m, l) of the head's s-th warp, lane l adds
+  // up coordinates 4l .. 4l+3 of the row
+  const int items = hpc * g;
+  const int64_t prow_cta = (static_cast<int64_t>(split) * p.B + b) * p.H_q + hg * hpc * g;
+  for (int it = warp; it < items; it += W) {
+    const int hh = it & (hpc - 1), q = it / hpc;
+    float ms = -INFINITY, ls = 0.f;
+    if (lane < R) {
+      const float2 ml = *reinterpret_cast<const float2*>(ring_of(hh + lane * hpc) + q * kRowFloats + kHeadDim);
+      ms = ml.x; ls = ml.y;
     }
-    *reinterpret_cast<float4*>(p.part_o + (prow0 + q) * kHeadDim + 4 * lane) = acc;
-    if (lane == 0) *reinterpret_cast<float2*>(p.part_ml + (prow0 + q) * 2) = make_float2(mt, lt);
+    float mt = ms;
+#pragma unroll
+    for (int mask = 1; mask < 32; mask <<= 1) mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, mask));
+    const float wgt = ms == -INFINITY ? 0.f : fast_exp2(ms - mt);
+    const float lt = warp_sum(ls * wgt);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+    for (int s2 = 0; s2 < R; ++s2) {
+      const float w2 = __shfl_sync(0xffffffffu, wgt, s2);
+      const float4 o = *reinterpret_cast<const float4*>(ring_of(hh + s2 * hpc) + q * kRowFloats + 4 * lane);
+      acc.x += o.x * w2; acc.y += o.y * w2; acc.z += o.z * w2; acc.w += o.w * w2;
+    }
+    const int64_t prow = prow_cta + hh * g + q;
+    *reinterpret_cast<float4*>(p.part_o + prow * kHeadDim + 4 * lane) = acc;
+    if (lane == 0) *reinterpret_cast<float2*>(p.part_ml + prow * 2) = make_float2(mt, lt);
   }
 }
 
 // ---- merge --------------------------------------------------------------------------------------------------
+// Last step of a merge: lane l holds coordinates 4l .. 4l+3 of the summed row, every lane the row's l and maximum.
+__device__ __forceinline__ void merge_finish(const float (&ot)[4], float lt, float mt, int64_t row, int lane, int mode,
+                                             int unrotate, __half* __restrict__ out, float* __restrict__ out_o,
+                                             float* __restrict__ out_m, float* __restrict__ out_l) {
+  if (mode == 1) {
+    *reinterpret_cast<float4*>(out_o + row * kHeadDim + 4 * lane) = make_float4(ot[0], ot[1], ot[2], ot[3]);
+    if (lane == 0) { out_m[row] = mt == -INFINITY ? -INFINITY : mt * kLn2; out_l[row] = lt; }
+    return;
+  }
+  const float inv = 1.0f / fmaxf(lt, 1e-30f);   // merge_partials clamps the denominator (attention.py:271)
+  float v[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) v[i] = round_to_half(ot[i] * inv);   // the oracle rounds O_rot to fp16 before un-rotating
+  if (unrotate) {
+    fht128_warp(v, lane);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] *= kRsqrtD;
+  }
+  *reinterpret_cast<uint2*>(out + row * kHeadDim + 4 * lane) = pack_half4(v);
+}
+
 // One CTA (16 warps) per output row.  A first pass over the (m) column finds the row's maximum; then warp w sums
 // partials w, w+16, ... weighted by exp2(m_p - max), four at a time so that their loads are in flight together,
 // and the sixteen warp sums are added through shared memory.  m values are multiplied by `m_to_log2` on load (1 for
@@ -638,21 +665,60 @@ __global__ void __launch_bounds__(kMergeWarps * 32) decode_merge_kernel(
     const float4 t = *reinterpret_cast<const float4*>(&s_o[w][4 * lane]);
     ot[0] += t.x; ot[1] += t.y; ot[2] += t.z; ot[3] += t.w;
   }
-  if (mode == 1) {
-    *reinterpret_cast<float4*>(out_o + row * kHeadDim + 4 * lane) = make_float4(ot[0], ot[1], ot[2], ot[3]);
-    if (lane == 0) { out_m[row] = mt == -INFINITY ? -INFINITY : mt * kLn2; out_l[row] = lt; }
-    return;
+  merge_finish(ot, lt, mt, row, lane, mode, unrotate, out, out_o, out_m, out_l);
+}
+
+// Merge of at most 32 partials per row: one warp per row, no shared memory.  Lane p holds (m, l) of partial p; the O
+// rows are read eight at a time.
+constexpr int kMergeSmallRows = 4, kMergeSmallMaxP = 32;
+__global__ void __launch_bounds__(kMergeSmallRows * 32) decode_merge_small_kernel(
+    const float* __restrict__ part_o, const float* __restrict__ part_m, const float* __restrict__ part_l, int ml_stride, int P,
+    int64_t rows, float m_to_log2, int mode, int unrotate, __half* __restrict__ out, float* __restrict__ out_o,
+    float* __restrict__ out_m, float* __restrict__ out_l) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * kMergeSmallRows + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  float mp = -INFINITY, lp = 0.f;
+  if (lane < P) {
+    const int64_t pr = static_cast<int64_t>(lane) * rows + row;
+    mp = part_m[pr * ml_stride] * m_to_log2;
+    lp = part_l[pr * ml_stride];
   }
-  const float inv = 1.0f / fmaxf(lt, 1e-30f);   // merge_partials clamps the denominator (attention.py:271)
-  float v[4];
+  float mt = mp;
 #pragma unroll
-  for (int i = 0; i < 4; ++i) v[i] = round_to_half(ot[i] * inv);   // the oracle rounds O_rot to fp16 before un-rotating
-  if (unrotate) {
-    fht128_warp(v, lane);
+  for (int mask = 16; mask > 0; mask >>= 1) mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, mask));
+  const float bw = mp == -INFINITY ? 0.f : fast_exp2(mp - mt);   // an empty range weighs nothing
+  const float lt = warp_sum(lp * bw);
+  float ot[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int base = 0; base < P; base += 8) {
+    float4 op[8];
+    float w8[8];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) v[i] *= kRsqrtD;
+    for (int u = 0; u < 8; ++u) {
+      const int pi = base + u < P ? base + u : base;
+      w8[u] = base + u < P ? __shfl_sync(0xffffffffu, bw, pi) : 0.f;
+      op[u] = *reinterpret_cast<const float4*>(part_o + (static_cast<int64_t>(pi) * rows + row) * kHeadDim + 4 * lane);
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      if (w8[u] == 0.f) continue;                                 // an empty range's O row may never have been written
+      ot[0] += op[u].x * w8[u]; ot[1] += op[u].y * w8[u]; ot[2] += op[u].z * w8[u]; ot[3] += op[u].w * w8[u];
+    }
   }
-  *reinterpret_cast<uint2*>(out + row * kHeadDim + 4 * lane) = pack_half4(v);
+  merge_finish(ot, lt, mt, row, lane, mode, unrotate, out, out_o, out_m, out_l);
+}
+
+// Picks the merge kernel by the number of partials per row.
+static void launch_merge(const float* po, const float* pm, const float* pl_, int ml_stride, int P, int64_t rows, float m_to_log2,
+                         int mode, int unrotate, __half* out, float* out_o, float* out_m, float* out_l, cudaStream_t st) {
+  if (P <= kMergeSmallMaxP) {
+    const unsigned grid = static_cast<unsigned>((rows + kMergeSmallRows - 1) / kMergeSmallRows);
+    decode_merge_small_kernel<<<grid, kMergeSmallRows * 32, 0, st>>>(po, pm, pl_, ml_stride, P, rows, m_to_log2, mode, unrotate, out,
+                                                                     out_o, out_m, out_l);
+  } else {
+    decode_merge_kernel<<<static_cast<unsigned>(rows), kMergeWarps * 32, 0, st>>>(po, pm, pl_, ml_stride, P, rows, m_to_log2, mode,
+                                                                                  unrotate, out, out_o, out_m, out_l);
+  }
 }
 
 // ---- scalar cross-check kernel ----------------------------------------------------------------------------------
@@ -730,8 +796,10 @@ static int pick_heads_per_cta(int H_kv) {
 
 // Choose the number of key-range splits.  One CTA occupies one SM and CTAs of one launch all carry the same work, so
 // the launch runs in ceil(CTAs / SMs) rounds, each as long as one CTA: a fixed part (launch, table and query set-up,
-// first copies, partial write and its share of the merge; measured at about the streaming time of 360 tokens) plus
-// the CTA's tokens.  Take the split count with the smallest estimate; splits never go below 128 tokens.
+// first copies, partial write and its share of the merge; measured at about the streaming time of 360 tokens when
+// the CTA's warps cover eight heads, and proportionally more tokens when they share fewer heads and so pass over a
+// token faster) plus the CTA's tokens.  Take the split count with the smallest estimate; splits never go below 128
+// tokens.
 static Plan make_plan(int B, int H_kv, int max_seq_len, int num_splits, int sms) {
   constexpr int kFloorTokens = 128, kFixedTokens = 360, kMaxSplits = 4096;
   Plan pl;
@@ -745,13 +813,14 @@ static Plan make_plan(int B, int H_kv, int max_seq_len, int num_splits, int sms)
     const int64_t other = static_cast<int64_t>(B > 0 ? B : 1) * pl.head_groups;
     int s_max = (n + kFloorTokens - 1) / kFloorTokens;
     if (s_max > kMaxSplits) s_max = kMaxSplits;
+    const int fixed = kFixedTokens * 8 / pl.heads_per_cta;
     int64_t best = -1;
     S = 1;
     for (int s = 1; s <= s_max; ++s) {
       const int tps_s = ((n + s - 1) / s + 15) / 16 * 16;
       const int64_t ctas = static_cast<int64_t>((n + tps_s - 1) / tps_s) * other;
       const int64_t rounds = (ctas + sms - 1) / sms;
-      const int64_t est = rounds * (kFixedTokens + tps_s);
+      const int64_t est = rounds * (fixed + tps_s);
       if (best < 0 || est < best) { best = est; S = s; }
       if (rounds > 16 && est > 2 * best) break;   // finer splits only add rounds from here on
     }
@@ -916,8 +985,7 @@ extern "C" int cda_b200_decode(const void* Q, const void* kv_cache, const int32_
   if (rc != CDA_OK) return rc;
   const int64_t rows = static_cast<int64_t>(B) * H_q;
   if (rows > 0x7fffffffLL) return fail(CDA_ERR_N_TOO_LARGE, "decode: B*H_q too large");
-  decode_merge_kernel<<<static_cast<unsigned>(rows), kMergeWarps * 32, 0, st>>>(po, ml, ml + 1, 2, pl.parts, rows, 1.0f, 0, 1,
-                                                                  static_cast<__half*>(out), nullptr, nullptr, nullptr);
+  launch_merge(po, ml, ml + 1, 2, pl.parts, rows, 1.0f, 0, 1, static_cast<__half*>(out), nullptr, nullptr, nullptr, st);
   return check_launch("decode merge kernel");
 }
 
@@ -938,7 +1006,7 @@ extern "C" int cda_b200_decode_partial(const void* Q, const void* kv_cache, cons
   if (rc != CDA_OK) return rc;
   const int64_t rows = static_cast<int64_t>(B) * H_q;
   if (rows > 0x7fffffffLL) return fail(CDA_ERR_N_TOO_LARGE, "decode_partial: B*H_q too large");
-  decode_merge_kernel<<<static_cast<unsigned>(rows), kMergeWarps * 32, 0, st>>>(po, ml, ml + 1, 2, pl.parts, rows, 1.0f, 1, 0, nullptr, O, m, l);
+  launch_merge(po, ml, ml + 1, 2, pl.parts, rows, 1.0f, 1, 0, nullptr, O, m, l, st);
   return check_launch("decode partial merge kernel");
 }
 
@@ -949,8 +1017,8 @@ extern "C" int cda_b200_merge_partials(const float* O, const float* m, const flo
   if (!O || !m || !l || !out) return fail(CDA_ERR_BAD_ARG, "merge_partials: null pointer");
   if (!aligned16(O) || (reinterpret_cast<uintptr_t>(out) & 7u)) return fail(CDA_ERR_BAD_ALIGN, "merge_partials: misaligned buffer");
   if (R > 0x7fffffffLL) return fail(CDA_ERR_N_TOO_LARGE, "merge_partials: too many rows");
-  decode_merge_kernel<<<static_cast<unsigned>(R), kMergeWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
-      O, m, l, 1, S, R, kLog2e, 0, unrotate ? 1 : 0, static_cast<__half*>(out), nullptr, nullptr, nullptr);
+  launch_merge(O, m, l, 1, S, R, kLog2e, 0, unrotate ? 1 : 0, static_cast<__half*>(out), nullptr, nullptr, nullptr,
+               static_cast<cudaStream_t>(stream));
   return check_launch("merge_partials");
 }
 
@@ -1012,7 +1080,6 @@ extern "C" int cda_b200_decode_static(const void* Q, const void* kv_cache, const
   Plan pl; float* ml; float* po;
   rc = run_split("decode_static", a, scratch, kStaticScratchBytes, splits, st, &pl, &ml, &po);
   if (rc != CDA_OK) return rc;
-  decode_merge_kernel<<<static_cast<unsigned>(rows), kMergeWarps * 32, 0, st>>>(po, ml, ml + 1, 2, pl.parts, rows, 1.0f, 0, 1,
-                                                                  static_cast<__half*>(out), nullptr, nullptr, nullptr);
+  launch_merge(po, ml, ml + 1, 2, pl.parts, rows, 1.0f, 0, 1, static_cast<__half*>(out), nullptr, nullptr, nullptr, st);
   return check_launch("decode_static merge kernel");
 }
