@@ -1,9 +1,10 @@
 // Paged encode (Hadamard rotation -> L2 norm -> nearest codebook level -> packed slot), the index
 // selection on its own, and the stand-alone 128-point Hadamard transform.
 //
-// One warp owns one 128-vector: lane l holds coordinates 4l..4l+3, the rotation is 2 in-register and
-// 5 shuffle butterfly stages, the norm a shuffle reduction.  The kernels are HBM-bound: 2 x 256 B
-// read and one payload (136 B for k4v4) written per (token, KV head).
+// Paged encode: one warp owns 16 vectors, rotated on the tensor cores (see rotate16).  The other kernels: one warp owns
+// one 128-vector, lane l holds coordinates 4l..4l+3, the rotation is 2 in-register and 5 shuffle butterfly stages, the
+// norm a shuffle reduction.  The kernels are HBM-bound on paper: 2 x 256 B read and one payload (136 B for k4v4)
+// written per (token, KV head).
 #include "common.cuh"
 
 namespace cda {
@@ -82,12 +83,147 @@ __device__ __forceinline__ float quantize_row(const float (&v)[4], const float* 
   return norm;
 }
 
+// ---- tensor-core rotation of 16 rows at a time --------------------------------------------------------------------------
+// The Sylvester matrix factors over the bits of the coordinate index: H128[i][j] = prod_b (-1)^(i_b j_b).  Bits {4,3,1,0}
+// ("lo", 16 values) are contracted by mma.m16n8k16 against a +-1 fp16 matrix (products exact, fp32 accumulation), bits
+// {6,5,2} ("hi", 8 values) by three in-register butterfly stages on the accumulators.  With that split lane c of a quad
+// reads, for each of the four 64-byte quarters of a row, the 16 contiguous bytes 8c .. 8c+7 (bits 4,3 = c; bit 2 picks the
+// half of the 16 bytes; bits 1,0 the fp16 inside the register pair), and ends up owning the same eight coordinates of the
+// rotated row: what it packs is one contiguous 32-bit (4-bit codes) or 16-bit (2-bit codes) piece of the slot.
+struct RotFrag {   // B operand: H16 restricted to this lane's contraction slots, for the two 8-column halves
+  uint32_t b0[2], b1[2];
+};
+__device__ __forceinline__ RotFrag make_rot_frag(int lane) {
+  const int n = lane >> 2, c = lane & 3;
+  RotFrag f;
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int out = 4 * (n >> 1) + 2 * t + (n & 1);                 // lo index of output column n of half t
+    uint32_t h[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) h[e] = (__popc((4 * c + e) & out) & 1) ? 0xBC00u : 0x3C00u;   // -1 : +1
+    f.b0[t] = h[0] | (h[1] << 16);
+    f.b1[t] = h[2] | (h[3] << 16);
+  }
+  return f;
+}
+// The 2 x 64 bytes of rows `row_lo` and `row_hi` that lane c of a quad contracts (A operands of rotate16).
+struct RowFrags {
+  uint4 lo[4], hi[4];
+};
+__device__ __forceinline__ void load_row_frags(const __half* __restrict__ x, int64_t row_lo, int64_t row_hi, int c, RowFrags& a) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    a.lo[j] = __ldg(reinterpret_cast<const uint4*>(x + row_lo * kHeadDim + 32 * j + 8 * c));
+    a.hi[j] = __ldg(reinterpret_cast<const uint4*>(x + row_hi * kHeadDim + 32 * j + 8 * c));
+  }
+}
+// y[g][t][i]: rotated (unscaled) coordinates 64 g2 + 32 g1 + 8c + 4 g0 + 2t + (i & 1) of the low row (i < 2) and the high
+// row (i >= 2) of the fragments, g = (g2 g1 g0).
+__device__ __forceinline__ void rotate16(const RowFrags& a, const RotFrag& f, float (&y)[8][2][4]) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) y[2 * j][t][i] = y[2 * j + 1][t][i] = 0.f;
+      mma_16816(y[2 * j][t], a.lo[j].x, a.hi[j].x, a.lo[j].y, a.hi[j].y, f.b0[t], f.b1[t]);
+      mma_16816(y[2 * j + 1][t], a.lo[j].z, a.hi[j].z, a.lo[j].w, a.hi[j].w, f.b0[t], f.b1[t]);
+    }
+#pragma unroll
+  for (int bit = 1; bit < 8; bit <<= 1)
+#pragma unroll
+    for (int g = 0; g < 8; ++g)
+      if (!(g & bit)) {
+#pragma unroll
+        for (int t = 0; t < 2; ++t)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float a = y[g][t][i], b = y[g | bit][t][i];
+            y[g][t][i] = a + b;
+            y[g | bit][t][i] = a - b;
+          }
+      }
+}
+// Scales the accumulators by 1/sqrt(128) and rounds them to fp16, as the rotation's output is: hp[g][t][h] = coordinates
+// (e = 0, 1) of row h as an fp16 pair.  Half the registers of y, so that the next fragments can be in flight meanwhile.
+__device__ __forceinline__ void scale_and_pack(const float (&y)[8][2][4], uint32_t (&hp)[8][2][2]) {
+#pragma unroll
+  for (int g = 0; g < 8; ++g)
+#pragma unroll
+    for (int t = 0; t < 2; ++t)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) hp[g][t][h] = pack_half2(y[g][t][2 * h] * kRsqrtD, y[g][t][2 * h + 1] * kRsqrtD);
+}
+// Quantises the two rows held in hp and writes this lane's pieces of their index fields.  Returns the two norms (the same in the four lanes of a quad).
+//
+// x / norm: the rotated coordinates are fp16 values, so a non-zero one is at least 2^-24 in size and the norm at most
+// 2^24; with y = RN(1/norm), q = RN(x y) and r = x - q norm (exact in one FMA: no intermediate leaves the normal
+// range), RN(q + r y) is the correctly rounded quotient (Markstein's division step), i.e. the value of x / norm; only
+// a zero loses its sign (-0 comes out as +0), which no comparison below can see.
+template <int BITS>
+__device__ __forceinline__ float2 quantize_pair(const uint32_t (&hp)[8][2][2], const float* T, uint8_t* dst_lo, uint8_t* dst_hi,
+                                                int c, bool ok_lo, bool ok_hi) {
+  constexpr int L = BITS == 4 ? 16 : 4;
+  float ss[2] = {0.f, 0.f};
+#pragma unroll
+  for (int g = 0; g < 8; ++g)
+#pragma unroll
+    for (int t = 0; t < 2; ++t)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const float2 v = __half22float2(*reinterpret_cast<const __half2*>(&hp[g][t][h]));
+        ss[h] = fmaf(v.x, v.x, ss[h]);
+        ss[h] = fmaf(v.y, v.y, ss[h]);
+      }
+  float norm[2], rcp[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    ss[h] += __shfl_xor_sync(0xffffffffu, ss[h], 1);
+    ss[h] += __shfl_xor_sync(0xffffffffu, ss[h], 2);
+    norm[h] = fmaxf(sqrtf(ss[h]), kNormFloor);
+    rcp[h] = __frcp_rn(norm[h]);
+  }
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    uint8_t* dst = h ? dst_hi : dst_lo;
+    const bool ok = h ? ok_hi : ok_lo;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {                                    // quarter of the row: g2 g1 = w
+      uint32_t word = 0;
+#pragma unroll
+      for (int g0 = 0; g0 < 2; ++g0)
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          const float2 v2 = __half22float2(*reinterpret_cast<const __half2*>(&hp[2 * w + g0][t][h]));
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const float v = e ? v2.y : v2.x;
+            const float q0 = __fmul_rn(v, rcp[h]);
+            const float rem = __fmaf_rn(-q0, norm[h], v);
+            const float u = __fmaf_rn(rem, rcp[h], q0);
+            const uint32_t idx = static_cast<uint32_t>(count_thresholds<L>(u, T));
+            const int pos = 4 * g0 + 2 * t + e;                      // coordinate inside this lane's eight
+            if (BITS == 4) word |= idx << (8 * (pos >> 1) + ((pos & 1) ? 0 : 4));
+            else word |= idx << (8 * (pos >> 2) + 6 - 2 * (pos & 3));
+          }
+        }
+      if (ok) {
+        if (BITS == 4) *reinterpret_cast<uint32_t*>(dst + 16 * w + 4 * c) = word;
+        else *reinterpret_cast<uint16_t*>(dst + 8 * w + 2 * c) = static_cast<uint16_t>(word);
+      }
+    }
+  }
+  return make_float2(norm[0], norm[1]);
+}
+
+// One warp per 16 rows (row = token * H_kv + head); lane 4r + c works on rows r and r + 8 of the tile.
 template <int KB, int VB>
-__global__ void __launch_bounds__(256) paged_encode_kernel(const __half* __restrict__ K, const __half* __restrict__ V,
-                                                           const int32_t* __restrict__ slot_mapping,
-                                                           uint8_t* __restrict__ cache, const float* __restrict__ cb_K,
-                                                           const float* __restrict__ cb_V, int64_t rows, int H_kv,
-                                                           int64_t num_slots, int slot_bytes) {
+__global__ void __launch_bounds__(256, 2) paged_encode_kernel(const __half* __restrict__ K, const __half* __restrict__ V,
+                                                              const int32_t* __restrict__ slot_mapping,
+                                                              uint8_t* __restrict__ cache, const float* __restrict__ cb_K,
+                                                              const float* __restrict__ cb_V, int64_t rows, int H_kv,
+                                                              int64_t num_slots, int slot_bytes) {
   __shared__ float s_cb[2][16], s_thr[2][16];
   if (threadIdx.x < 16) {
     s_cb[0][threadIdx.x] = threadIdx.x < (KB == 4 ? 16 : 4) ? cb_K[threadIdx.x] : 0.f;
@@ -97,35 +233,58 @@ __global__ void __launch_bounds__(256) paged_encode_kernel(const __half* __restr
   build_thresholds<(KB == 4 ? 16 : 4)>(s_cb[0], s_thr[0], threadIdx.x);
   build_thresholds<(VB == 4 ? 16 : 4)>(s_cb[1], s_thr[1], static_cast<int>(threadIdx.x) - 32);
   __syncthreads();
-  const int lane = threadIdx.x & 31;
+  const int lane = threadIdx.x & 31, r = lane >> 2, c = lane & 3;
   constexpr int kKBytes = 16 * KB, kVBytes = 16 * VB;
-  // grid-stride over rows (row = t * H_kv + h): the threshold set-up is paid once per CTA
-  // (token, head) of the row advance with the row, so the 64-bit division happens once per warp
-  const int64_t stride = static_cast<int64_t>(gridDim.x) * 8;
-  const int64_t t_step = stride / H_kv;
-  const int h_step = static_cast<int>(stride - t_step * H_kv);
-  int64_t row = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
-  int64_t t = row / H_kv;
-  int h = static_cast<int>(row - t * H_kv);
-  for (; row < rows; row += stride, t += t_step, h += h_step) {
-    if (h >= H_kv) { h -= H_kv; ++t; }
-    const int64_t slot = slot_mapping[t];
-    if (slot < 0 || slot >= num_slots) continue;
-    uint8_t* dst = cache + (slot * H_kv + h) * slot_bytes;
-
-    float v[4], w[4];
-    load_half4(K + row * kHeadDim + 4 * lane, v);
-    load_half4(V + row * kHeadDim + 4 * lane, w);
-    fht128_warp(v, lane);
-    fht128_warp(w, lane);
+  const RotFrag frag = make_rot_frag(lane);
+  const int64_t tiles = (rows + 15) >> 4;
+  const bool small = rows < 0x7fffffffLL;                            // then token = row / H_kv is a 32-bit division
+  const int64_t tile_step = static_cast<int64_t>(gridDim.x) * 8;
+  RowFrags fr;
+  bool first = true;
+  for (int64_t tile = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5); tile < tiles; tile += tile_step) {
+    int64_t row[2] = {tile * 16 + r, tile * 16 + r + 8};
+    uint8_t* dst[2];
+    bool ok[2];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {                       // Compressor.rotate casts back to fp16
-      v[i] = round_to_half(v[i] * kRsqrtD);
-      w[i] = round_to_half(w[i] * kRsqrtD);
+    for (int h = 0; h < 2; ++h) {
+      ok[h] = row[h] < rows;
+      if (!ok[h]) row[h] = rows - 1;                                 // read a valid row, write nothing
+      int64_t t;
+      int head;
+      if (small) {
+        const uint32_t t32 = static_cast<uint32_t>(row[h]) / static_cast<uint32_t>(H_kv);
+        t = t32;
+        head = static_cast<int>(static_cast<uint32_t>(row[h]) - t32 * static_cast<uint32_t>(H_kv));
+      } else {
+        t = row[h] / H_kv;
+        head = static_cast<int>(row[h] - t * H_kv);
+      }
+      const int64_t slot = slot_mapping[t];
+      ok[h] = ok[h] && slot >= 0 && slot < num_slots;
+      dst[h] = cache + ((ok[h] ? slot : 0) * H_kv + head) * slot_bytes;
     }
-    const float nk = quantize_row<KB>(v, s_thr[0], dst, lane);
-    const float nv = quantize_row<VB>(w, s_thr[1], dst + kKBytes, lane);
-    if (lane == 0) *reinterpret_cast<float2*>(dst + kKBytes + kVBytes) = make_float2(nk, nv);
+    // K fragments were requested a turn ago; V's are requested before K is quantised, the next tile's K before V is
+    if (first) { load_row_frags(K, row[0], row[1], c, fr); first = false; }
+    float y[8][2][4];
+    uint32_t hp[8][2][2];
+    rotate16(fr, frag, y);
+    load_row_frags(V, row[0], row[1], c, fr);
+    scale_and_pack(y, hp);
+    const float2 nk = quantize_pair<KB>(hp, s_thr[0], dst[0], dst[1], c, ok[0], ok[1]);
+    rotate16(fr, frag, y);
+    {
+      const int64_t next = tile + tile_step;
+      if (next < tiles) {
+        const int64_t n_lo = next * 16 + r, n_hi = n_lo + 8;
+        load_row_frags(K, n_lo < rows ? n_lo : rows - 1, n_hi < rows ? n_hi : rows - 1, c, fr);
+      }
+    }
+    scale_and_pack(y, hp);
+    const float2 nv = quantize_pair<VB>(hp, s_thr[1], dst[0] + kKBytes, dst[1] + kKBytes, c, ok[0], ok[1]);
+    if (c == 0) {
+      if (ok[0]) *reinterpret_cast<float2*>(dst[0] + kKBytes + kVBytes) = make_float2(nk.x, nv.x);
+      if (ok[1]) *reinterpret_cast<float2*>(dst[1] + kKBytes + kVBytes) = make_float2(nk.y, nv.y);
+    }
   }
 }
 
@@ -184,9 +343,10 @@ extern "C" int cda_b200_paged_encode(const void* K, const void* V, const int32_t
   if (!aligned16(K) || !aligned16(V) || !aligned16(flat_cache))
     return fail(CDA_ERR_BAD_ALIGN, "paged_encode: K, V and the cache must be 16-byte aligned");
   const int64_t rows = T * H_kv;
-  const int64_t blocks = blocks_for_rows(rows);
-  if (blocks > 0x7fffffffLL) return fail(CDA_ERR_N_TOO_LARGE, "paged_encode: T*H_kv too large");
-  const dim3 grid(persistent_grid(rows)), block(256);
+  if (blocks_for_rows(rows) > 0x7fffffffLL) return fail(CDA_ERR_N_TOO_LARGE, "paged_encode: T*H_kv too large");
+  // a CTA of 8 warps takes 128 rows per turn; two CTAs fit on an SM
+  const int64_t want = (rows + 127) / 128, cap = static_cast<int64_t>(device_sm_count(-1)) * 2;
+  const dim3 grid(static_cast<unsigned>(want < cap ? want : cap)), block(256);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const __half* k = static_cast<const __half*>(K);
   const __half* v = static_cast<const __half*>(V);

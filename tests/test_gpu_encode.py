@@ -98,7 +98,7 @@ def test_paged_encode_matches_oracle(ops, T, kb, vb):
         far = int((ulp_diff(g_.norm, w_.norm) > 4).sum())
         assert float(rel.max()) <= 1e-3 and far <= 2 + 0.15 * g_.norm.numel(), far
         flips = (O.unpack_indices(g_.idx, bits) != O.unpack_indices(w_.idx, bits)).float().mean()
-        # the rotation is a butterfly here and a dense fp32 matmul in the oracle: rounding x_rot to fp16 can differ by
+        # the rotation sums in another order here than the oracle's dense fp32 matmul: rounding x_rot to fp16 can differ by
         # one fp16 ulp in rare elements, which moves an index only next to a decision boundary
         assert float(flips) <= 2e-4, float(flips)
     # exact check of the selection itself: re-quantise the oracle's rotated rows with the kernel's stored norms
@@ -106,6 +106,37 @@ def test_paged_encode_matches_oracle(ops, T, kb, vb):
     exact = O.quantize_rotated(x_rot, cbk, norm=Kg.norm)
     mism = (O.unpack_indices(exact.idx, kb) != O.unpack_indices(Kg.idx, kb)).float().mean()
     assert float(mism) <= 2e-4
+
+
+@pytest.mark.parametrize("kb,vb", [(4, 4), (4, 2), (2, 2), (2, 4)])
+def test_paged_encode_bit_exact_on_exactly_rotatable_rows(ops, kb, vb):
+    """Rows of small integers (times a power of two) rotate without any rounding in whatever order the sums are taken,
+    so the kernel and this test hold identical rotated rows; with the kernel's own norm the oracle's quotients and
+    comparisons must then give the kernel's indices bit for bit (division, thresholds and packing of the paged path)."""
+    from sub0_b200.kernels_cuda.wrappers import paged_encode_fused_cuda
+    gen = torch.Generator().manual_seed(100 * kb + vb)
+    T, H = 777, 5                                                             # 3885 rows: the last 16-row tile is ragged
+    def ints():
+        x = torch.randint(-8, 9, (T, H, 128), generator=gen).float()
+        x *= torch.tensor(2.0) ** torch.randint(-6, 4, (T, H, 1), generator=gen).float()
+        x[torch.rand(T, H, generator=gen) < 0.02] = 0                         # all-zero rows: norm floor
+        return x.to(torch.float16)
+    K, V = ints(), ints()
+    W = O.slot_bytes(kb, vb)
+    slots = torch.randperm(T + 9, generator=gen)[:T].to(torch.int32)
+    cache_d = torch.zeros(T + 9, H, W, dtype=torch.uint8, device=DEV)
+    cbk, cbv = Cs.cb_for(kb), Cs.cb_for(vb)
+    paged_encode_fused_cuda(K.to(DEV), V.to(DEV), slots.to(DEV), cache_d, cb_K=cbk.to(DEV), cb_V=cbv.to(DEV))
+    Kg, Vg = O.unpack_slots(cache_d.cpu(), slots, kb, vb)
+    h_int = O.sylvester_hadamard() * (128 ** 0.5)                             # entries +-1
+    scale = torch.tensor(0.08838834764831845, dtype=torch.float32)
+    for x, g_, cb in ((K, Kg, cbk), (V, Vg, cbv)):
+        exact = (x.double() @ h_int.double()).float()                         # sums of at most 128 * 8 * 8: exact
+        x_rot = (exact * scale).to(torch.float16).float()                     # one fp32 product, rounded to fp16
+        want_norm = x_rot.double().norm(dim=-1).clamp_min(1e-12).float()
+        assert int(ulp_diff(g_.norm, want_norm).max()) <= 16                  # fp32 sum of 128 squares, order unspecified
+        want = O.quantize_rotated(x_rot, cb, norm=g_.norm)
+        assert torch.equal(want.idx, g_.idx)
 
 
 @pytest.mark.parametrize("rows", [1, 33, 1000])
