@@ -55,6 +55,21 @@ __device__ __forceinline__ int count_thresholds(float x, const float* T) {
   lo += x > T[lo] ? 1 : 0;
   return lo;
 }
+// The same count times four: the running value is the byte offset of the next threshold to look at, so every step is
+// one load at (offset + constant), one comparison and one conditional add.
+template <int L>
+__device__ __forceinline__ uint32_t count_thresholds_x4(float x, const float* T) {
+  const char* base = reinterpret_cast<const char*>(T);
+  auto at = [&](uint32_t off) { return *reinterpret_cast<const float*>(base + off); };
+  uint32_t lo = 0;
+  if (L == 16) {
+    lo = x > at(28) ? 32u : 0u;
+    lo += x > at(lo + 12) ? 16u : 0u;
+  }
+  lo += x > at(lo + 4) ? 8u : 0u;
+  lo += x > at(lo) ? 4u : 0u;
+  return lo;
+}
 
 // v: this lane's four rotated fp32 coordinates.  Writes the packed indices of the row to `idx_dst`
 // (16*BITS bytes per row) and returns the row norm (identical in every lane).  T: thresholds of the codebook.
@@ -196,17 +211,18 @@ __device__ __forceinline__ float2 quantize_pair(const uint32_t (&hp)[8][2][2], c
 #pragma unroll
         for (int t = 0; t < 2; ++t) {
           const float2 v2 = __half22float2(*reinterpret_cast<const __half2*>(&hp[2 * w + g0][t][h]));
+          uint32_t i4[2];                                            // four times the indices of coordinates e = 0, 1
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
             const float v = e ? v2.y : v2.x;
             const float q0 = __fmul_rn(v, rcp[h]);
             const float rem = __fmaf_rn(-q0, norm[h], v);
             const float u = __fmaf_rn(rem, rcp[h], q0);
-            const uint32_t idx = static_cast<uint32_t>(count_thresholds<L>(u, T));
-            const int pos = 4 * g0 + 2 * t + e;                      // coordinate inside this lane's eight
-            if (BITS == 4) word |= idx << (8 * (pos >> 1) + ((pos & 1) ? 0 : 4));
-            else word |= idx << (8 * (pos >> 2) + 6 - 2 * (pos & 3));
+            i4[e] = count_thresholds_x4<L>(u, T);
           }
+          const int pair = 2 * g0 + t;                               // which two of this lane's eight coordinates
+          if (BITS == 4) word += ((i4[0] << 2) + (i4[1] >> 2)) << (8 * pair);               // one byte, first code on top
+          else word += (i4[0] + (i4[1] >> 2)) << (8 * g0 + 4 - 4 * t);                      // half a byte, first code on top
         }
       if (ok) {
         if (BITS == 4) *reinterpret_cast<uint32_t*>(dst + 16 * w + 4 * c) = word;
