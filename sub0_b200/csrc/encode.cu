@@ -98,30 +98,7 @@ __device__ __forceinline__ float quantize_row(const float (&v)[4], const float* 
   return norm;
 }
 
-// ---- tensor-core rotation of 16 rows at a time --------------------------------------------------------------------------
-// The Sylvester matrix factors over the bits of the coordinate index: H128[i][j] = prod_b (-1)^(i_b j_b).  Bits {4,3,1,0}
-// ("lo", 16 values) are contracted by mma.m16n8k16 against a +-1 fp16 matrix (products exact, fp32 accumulation), bits
-// {6,5,2} ("hi", 8 values) by three in-register butterfly stages on the accumulators.  With that split lane c of a quad
-// reads, for each of the four 64-byte quarters of a row, the 16 contiguous bytes 8c .. 8c+7 (bits 4,3 = c; bit 2 picks the
-// half of the 16 bytes; bits 1,0 the fp16 inside the register pair), and ends up owning the same eight coordinates of the
-// rotated row: what it packs is one contiguous 32-bit (4-bit codes) or 16-bit (2-bit codes) piece of the slot.
-struct RotFrag {   // B operand: H16 restricted to this lane's contraction slots, for the two 8-column halves
-  uint32_t b0[2], b1[2];
-};
-__device__ __forceinline__ RotFrag make_rot_frag(int lane) {
-  const int n = lane >> 2, c = lane & 3;
-  RotFrag f;
-#pragma unroll
-  for (int t = 0; t < 2; ++t) {
-    const int out = 4 * (n >> 1) + 2 * t + (n & 1);                 // lo index of output column n of half t
-    uint32_t h[4];
-#pragma unroll
-    for (int e = 0; e < 4; ++e) h[e] = (__popc((4 * c + e) & out) & 1) ? 0xBC00u : 0x3C00u;   // -1 : +1
-    f.b0[t] = h[0] | (h[1] << 16);
-    f.b1[t] = h[2] | (h[3] << 16);
-  }
-  return f;
-}
+// ---- tensor-core rotation of 16 rows at a time (RotFrag, make_rot_frag: common.cuh) --------------------------------------
 // The 2 x 64 bytes of rows `row_lo` and `row_hi` that lane c of a quad contracts (A operands of rotate16).
 struct RowFrags {
   uint4 lo[4], hi[4];

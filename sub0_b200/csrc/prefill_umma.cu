@@ -228,6 +228,59 @@ __device__ __forceinline__ float row_probabilities(uint32_t s_col, const float* 
   return sum0 + sum1;
 }
 
+// Rows of 128 fp16 parked in shared memory: 256-byte rows, 16-byte chunk c of row r at chunk position c ^ (r & 15).
+__device__ __forceinline__ uint32_t staged_chunk(uint32_t area, uint32_t row, uint32_t chunk) {
+  return area + row * 256u + ((chunk ^ (row & 15u)) << 4);
+}
+// Hadamard rotation (times `scale`, rounded to fp16) of the 16 staged rows 16 * tile .. 16 * tile + 15 on the tensor
+// cores (common.cuh: RotFrag).  Lane 4r + c ends up with coordinates 32 w + 8 c .. 32 w + 8 c + 7 (w = 0..3) of rows r and
+// r + 8 and hands each such 16-byte piece to emit(row, w, piece).  Two passes, one per 8-column half of the MMA output,
+// keep the accumulators at 32 registers; the first pass's results wait as fp16 pairs.
+template <class Emit>
+__device__ __forceinline__ void rotate_staged_rows(uint32_t area, int tile, int lane, float scale, Emit emit) {
+  const int r = lane >> 2, c = lane & 3;
+  const uint32_t row_lo = 16u * tile + r, row_hi = row_lo + 8u;
+  const RotFrag f = make_rot_frag(lane);
+  uint32_t first[8][2];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    float y[8][4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint4 lo = lds128(staged_chunk(area, row_lo, 4 * j + c)), hi = lds128(staged_chunk(area, row_hi, 4 * j + c));
+#pragma unroll
+      for (int i = 0; i < 4; ++i) y[2 * j][i] = y[2 * j + 1][i] = 0.f;
+      mma_16816(y[2 * j], lo.x, hi.x, lo.y, hi.y, f.b0[t], f.b1[t]);
+      mma_16816(y[2 * j + 1], lo.z, hi.z, lo.w, hi.w, f.b0[t], f.b1[t]);
+    }
+#pragma unroll
+    for (int bit = 1; bit < 8; bit <<= 1)
+#pragma unroll
+      for (int g = 0; g < 8; ++g)
+        if (!(g & bit)) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float a = y[g][i], b = y[g | bit][i];
+            y[g][i] = a + b;
+            y[g | bit][i] = a - b;
+          }
+        }
+    if (t == 0) {
+#pragma unroll
+      for (int g = 0; g < 8; ++g)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) first[g][h] = pack_half2(y[g][2 * h] * scale, y[g][2 * h + 1] * scale);
+    } else {
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int w = 0; w < 4; ++w)   // coordinates 4 g0 + 2 t + e of the piece: g0 = 0 (t = 0, 1), then g0 = 1
+          emit(h ? row_hi : row_lo, w, make_uint4(first[2 * w][h], pack_half2(y[2 * w][2 * h] * scale, y[2 * w][2 * h + 1] * scale),
+                                                  first[2 * w + 1][h], pack_half2(y[2 * w + 1][2 * h] * scale, y[2 * w + 1][2 * h + 1] * scale)));
+    }
+  }
+}
+
 }  // namespace pfu
 
 template <int G, int KB, int VB>
@@ -292,19 +345,23 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
   }
   fill_code_table<KB>(sm + kOffLut, lut_stride, p.cb_k, 1.0f / alpha_k, tid, kThreads);
   if (!same_cb) fill_code_table<VB>(sm + kOffLut + lutv_off, lut_stride, p.cb_v, 1.0f / alpha_v, tid, kThreads);
-  // Q: one warp per row loads, rotates and stores the fp16 row as the A operand of Q K^T (K-major, 128-byte swizzle)
-  for (int r = warp; r < kBlocks * kRows; r += kThreads / 32) {
+  // Q: the raw rows are parked in the (still unused) K stages with one 16-byte load per thread and chunk, all in flight
+  // together; then warps 0..15 rotate 16 rows each and store them as the A operand of Q K^T (K-major, 128-byte swizzle)
+  for (int i = tid; i < kBlocks * kRows * 16; i += kThreads) {
+    const int r = i >> 4, chunk = i & 15;
     const int pos = p0 + r / G, hl = r % G;
-    float v[4] = {0.f, 0.f, 0.f, 0.f};
-    if (pos < q_len && hl < g) {
-      load_half4(p.q + (static_cast<int64_t>(q_begin + pos) * p.H_q + kvh * g + hl) * kHeadDim + 4 * lane, v);
-      fht128_warp(v, lane);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) v[i] *= kRsqrtD;
-    }
-    const uint2 h = pack_half4(v);
-    const uint32_t t = static_cast<uint32_t>(r & (kRows - 1));
-    sts64(base + kOffQ + (r / kRows) * kTileBytes + (lane >> 4) * kColBlockBytes + sw128(t, (lane & 15) >> 1) + (lane & 1) * 8u, h.x, h.y);
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (pos < q_len && hl < g)
+      v = __ldg(reinterpret_cast<const uint4*>(p.q + (static_cast<int64_t>(q_begin + pos) * p.H_q + kvh * g + hl) * kHeadDim) + chunk);
+    sts128(staged_chunk(base + kOffK, r, chunk), v.x, v.y, v.z, v.w);
+  }
+  __syncthreads();
+  if (warp < kBlocks * kRows / 16) {
+    rotate_staged_rows(base + kOffK, warp, lane, kRsqrtD, [&](uint32_t row, int w, const uint4& piece) {
+      const uint32_t t = row & (kRows - 1);
+      sts128(base + kOffQ + (row / kRows) * kTileBytes + (w >> 1) * kColBlockBytes + sw128(t, 4 * (w & 1) + (lane & 3)), piece.x, piece.y,
+             piece.z, piece.w);
+    });
   }
   fence_async_smem();
   tc_fence_before_sync();
@@ -559,18 +616,12 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
   __syncthreads();
   const bool failed = *abort_flag != 0;
   if (!failed) {
-    for (int r = warp; r < kBlocks * kRows; r += kThreads / 32) {
-      const int pos = p0 + r / G, hl = r % G;
-      if (pos >= q_len || hl >= g) continue;
-      const uint32_t src = base + kOffK + r * 256u + ((static_cast<uint32_t>(lane >> 1) ^ (r & 15u)) << 4) + (lane & 1) * 8u;
-      const uint4 raw4 = lds128(src & ~15u);   // (volatile read: the row was written by another warp)
-      const uint2 raw = (lane & 1) ? make_uint2(raw4.z, raw4.w) : make_uint2(raw4.x, raw4.y);
-      float v[4];
-      unpack_half4(raw, v);
-      fht128_warp(v, lane);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) v[i] *= kRsqrtD;
-      *reinterpret_cast<uint2*>(p.out + (static_cast<int64_t>(q_begin + pos) * p.H_q + kvh * g + hl) * kHeadDim + 4 * lane) = pack_half4(v);
+    if (warp < kBlocks * kRows / 16) {
+      rotate_staged_rows(base + kOffK, warp, lane, kRsqrtD, [&](uint32_t row, int w, const uint4& piece) {
+        const int pos = p0 + static_cast<int>(row) / G, hl = static_cast<int>(row) % G;
+        if (pos < q_len && hl < g)
+          *reinterpret_cast<uint4*>(p.out + (static_cast<int64_t>(q_begin + pos) * p.H_q + kvh * g + hl) * kHeadDim + 32 * w + 8 * (lane & 3)) = piece;
+      });
     }
   } else if (tid == 0) {
     atomicOr(&g_prefill_fault, 1);
