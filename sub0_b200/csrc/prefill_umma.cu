@@ -315,6 +315,19 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
   const uint32_t bar0 = base + kOffBar;
   auto bar = [&](int i) { return bar0 + 8u * i; };
 
+  // The raw Q rows are requested first, one 16-byte chunk per thread and turn, so that their latency runs under the
+  // table set-up; they are parked in the (still unused) K stages further down.
+  constexpr int kQTurns = (kBlocks * kRows * 16 + kThreads - 1) / kThreads;
+  uint4 q_raw[kQTurns];
+#pragma unroll
+  for (int k = 0; k < kQTurns; ++k) {
+    const int i = tid + k * kThreads, r = i >> 4, chunk = i & 15;
+    const int pos = p0 + r / G, hl = r % G;
+    q_raw[k] = make_uint4(0u, 0u, 0u, 0u);
+    if (i < kBlocks * kRows * 16 && pos < q_len && hl < g)
+      q_raw[k] = __ldg(reinterpret_cast<const uint4*>(p.q + (static_cast<int64_t>(q_begin + pos) * p.H_q + kvh * g + hl) * kHeadDim) + chunk);
+  }
+
   __shared__ float s_err[64];
   __shared__ int s_idx[64];
   float alpha_k, alpha_v;
@@ -345,15 +358,12 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
   }
   fill_code_table<KB>(sm + kOffLut, lut_stride, p.cb_k, 1.0f / alpha_k, tid, kThreads);
   if (!same_cb) fill_code_table<VB>(sm + kOffLut + lutv_off, lut_stride, p.cb_v, 1.0f / alpha_v, tid, kThreads);
-  // Q: the raw rows are parked in the (still unused) K stages with one 16-byte load per thread and chunk, all in flight
-  // together; then warps 0..15 rotate 16 rows each and store them as the A operand of Q K^T (K-major, 128-byte swizzle)
-  for (int i = tid; i < kBlocks * kRows * 16; i += kThreads) {
-    const int r = i >> 4, chunk = i & 15;
-    const int pos = p0 + r / G, hl = r % G;
-    uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (pos < q_len && hl < g)
-      v = __ldg(reinterpret_cast<const uint4*>(p.q + (static_cast<int64_t>(q_begin + pos) * p.H_q + kvh * g + hl) * kHeadDim) + chunk);
-    sts128(staged_chunk(base + kOffK, r, chunk), v.x, v.y, v.z, v.w);
+  // Q: park the raw rows; then warps 0..15 rotate 16 rows each and store them as the A operand of Q K^T (K-major,
+  // 128-byte swizzle)
+#pragma unroll
+  for (int k = 0; k < kQTurns; ++k) {
+    const int i = tid + k * kThreads;
+    if (i < kBlocks * kRows * 16) sts128(staged_chunk(base + kOffK, i >> 4, i & 15), q_raw[k].x, q_raw[k].y, q_raw[k].z, q_raw[k].w);
   }
   __syncthreads();
   if (warp < kBlocks * kRows / 16) {
