@@ -2,10 +2,9 @@
 (``cda.algorithm.compression`` / ``cda.algorithm.attention``) on CPU.
 
 The reference tree is only needed to (re)generate; the ``.npz`` files are committed and the tests read
-them alone.  Usage (from the repository root, with the reference checkout at ``$CDA_REFERENCE`` or
-``/root/reference``)::
+them alone.  Usage (from the repository root; ``CDA_REFERENCE`` is the path of the reference checkout)::
 
-    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py
+    CDA_REFERENCE=<reference checkout> PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py
 
 All inputs are seeded; the reference has no fixtures of its own, so these files are the pin.
 """
@@ -18,7 +17,9 @@ from pathlib import Path
 import numpy as np
 import torch
 
-REF = os.environ.get("CDA_REFERENCE", "/root/reference")
+REF = os.environ.get("CDA_REFERENCE")
+if not REF:
+    raise SystemExit("set CDA_REFERENCE to the path of the reference checkout")
 sys.path.insert(0, REF)
 from cda.algorithm import attention as ref_attn          # noqa: E402
 from cda.algorithm import compression as ref_comp        # noqa: E402
