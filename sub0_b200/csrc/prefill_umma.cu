@@ -466,6 +466,14 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
           sts128(base + kOffK + row * 256u + ((chunk ^ (row & 15u)) << 4), h[0], h[1], h[2], h[3]);
         }
       }
+      // ---- epilogue part 2: once the block's 128 rows are parked, its eight warps rotate 16 of them each and store them; the
+      // other block may still be in its last tile (`alive` is the same for every thread of the group)
+      named_barrier(bar_id, group_threads);
+      rotate_staged_rows(base + kOffK, warp, lane, kRsqrtD, [&](uint32_t row, int w, const uint4& piece) {
+        const int pos = p0 + static_cast<int>(row) / G, hl = static_cast<int>(row) % G;
+        if (pos < q_len && hl < g)
+          *reinterpret_cast<uint4*>(p.out + (static_cast<int64_t>(q_begin + pos) * p.H_q + kvh * g + hl) * kHeadDim + 32 * w + 8 * (lane & 3)) = piece;
+      });
     }
     tc_fence_before_sync();
   } else if (warp < kSoftmaxWarps + kProducerWarps) {
@@ -622,22 +630,12 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
     tc_fence_before_sync();
   }
 
-  // ---- epilogue part 2: every warp rotates rows back and stores them ---------------------------------------------------------
+  // ---- end: a CTA in which a wait gave up raises the device-wide flag; tensor memory is released either way ---------------
   __syncthreads();
-  const bool failed = *abort_flag != 0;
-  if (!failed) {
-    if (warp < kBlocks * kRows / 16) {
-      rotate_staged_rows(base + kOffK, warp, lane, kRsqrtD, [&](uint32_t row, int w, const uint4& piece) {
-        const int pos = p0 + static_cast<int>(row) / G, hl = static_cast<int>(row) % G;
-        if (pos < q_len && hl < g)
-          *reinterpret_cast<uint4*>(p.out + (static_cast<int64_t>(q_begin + pos) * p.H_q + kvh * g + hl) * kHeadDim + 32 * w + 8 * (lane & 3)) = piece;
-      });
-    }
-  } else if (tid == 0) {
+  if (*abort_flag != 0 && tid == 0) {
     atomicOr(&g_prefill_fault, 1);
     if (p.status) atomicOr(p.status, 4);
   }
-  __syncthreads();
   if (warp == kMmaWarp) {
     tc_fence_after_sync();
     tmem_dealloc(tmem, kTmemCols);
