@@ -298,11 +298,13 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
   uint8_t* sm = smem_raw + (base - raw_addr);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int kvh = blockIdx.y, b = blockIdx.z;
+  // Grid (sequence, KV head, tile rank): CTAs are handed out in x-fastest order, so every sequence's longest rows go first
+  // and the last CTAs of the launch are the shortest rows of the longest sequence (close to longest-job-first).
+  const int kvh = blockIdx.y, b = blockIdx.x;
   const int q_begin = p.cu_q[b], q_len = p.cu_q[b + 1] - q_begin;
   const int seq_len = p.seq_lens[b];
   const int n_qtiles = (q_len + kPosPerTile - 1) / kPosPerTile;
-  const int qt = n_qtiles - 1 - static_cast<int>(blockIdx.x);   // longest rows first
+  const int qt = n_qtiles - 1 - static_cast<int>(blockIdx.z);   // longest rows first
   if (qt < 0 || seq_len <= 0 || q_len > seq_len) return;
   if (*reinterpret_cast<volatile int*>(&g_prefill_fault)) return;
   const int p0 = qt * kPosPerTile;                               // first query position (within the new tokens) of this tile
@@ -653,7 +655,9 @@ static int launch_prefill_umma(const PrefillUmmaParams& p, int max_query_len, in
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   const int per_tile = pfu::kBlocks * pfu::kRows / G;
-  const dim3 grid((max_query_len + per_tile - 1) / per_tile, p.H_kv, B);
+  const int q_tiles = (max_query_len + per_tile - 1) / per_tile;
+  if (q_tiles > 65535 || p.H_kv > 65535) return fail(CDA_ERR_N_TOO_LARGE, "prefill: max_query_len %d or H_kv %d exceeds the grid limits", max_query_len, p.H_kv);
+  const dim3 grid(B, p.H_kv, q_tiles);
   prefill_umma_kernel<G, KB, VB><<<grid, pfu::kThreads, pfu::kSmemBytes, st>>>(p);
   return check_launch("prefill kernel");
 }
