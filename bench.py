@@ -1,20 +1,27 @@
 #!/usr/bin/env python
-"""Decode benchmark: one layer of single-query GQA attention over the paged k4v4 cache.
+"""Benchmarks of the compressed-domain attention path.  Headline: one layer of single-query GQA decode over the paged
+k4v4 cache.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--batch B] [--ctx N]
-    python bench.py --workload encode|prefill [--steps K] [--warmup W]      (secondary kernels, one GPU)
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--batch B] [--ctx N] [--group G] [--k-bits 4|2] [--v-bits 4|2]                      decode (default)
+    python bench.py --workload decode_seqsplit [--gpus N] [--ctx N] [--group G]     one long sequence, keys split over ranks
+    python bench.py --workload encode|prefill [--steps K] [--warmup W]              the other two kernels, one GPU
 
-Workload (N=1): Mistral-7B head geometry (32 query heads, 8 KV heads, d=128, GQA 4), k4v4, B=32 sequences of
-N=65536 tokens, block size 16, 144-byte slots, seeded synthetic data (N(0,1) fp16 with x8 outlier channels in K),
-block table = seeded random permutation of the pages.  At N>1 GPUs the 8 KV heads (and their query heads) are
-sharded across ranks, total work fixed ("strong" scaling); no collective is on the data path.
+decode (N=1): Mistral-7B head geometry (32 query heads, 8 KV heads, d=128, GQA 4), k4v4, B=32 sequences of N=65536
+tokens, block size 16, 144-byte slots, seeded synthetic data (N(0,1) fp16 with x8 outlier channels in K), block table =
+seeded random permutation of the pages (the figure for the identity order the reference's benchmark uses is reported
+beside it).  `--group 8 --batch 64 --ctx 32768` is the Llama-3-70B cell.  At N>1 GPUs the 8 KV heads (and their query
+heads) are sharded across ranks, total work fixed ("strong" scaling); no collective is on the data path.
 
-A step is one decode call (split kernel + merge kernel) replayed from a CUDA graph, as the reference times it.  The
-metric is achieved HBM GB/s over ALGORITHMIC bytes (136-byte slot payloads + Q/out + block table), whole job.
-`e2e` is the same metric through the public wrappers with host buffers: pinned H2D of the step's inputs (Q, the new
-token's K/V, slot mapping, block table, sequence lengths), paged encode of the new token, decode, D2H of the output;
-the step's calls are captured once in a CUDA graph and replayed with a synchronise per step (`eager_value`: the same
-calls issued from Python every step).
+decode_seqsplit: B=1, N=1048576, 64 query heads / 8 KV heads; rank r holds keys [r N/W, (r+1) N/W) of every head.  A
+step is partial kernel + merge-to-packed kernel, ONE all-gather of (64, 130) fp32 per rank, merge kernel -- captured in
+one CUDA graph.  Rank 0 checks the merged output of one KV head against the CPU oracle over all ranks' slots.
+
+A decode step is one call (split kernel + merge kernel) replayed from a CUDA graph, as the reference times it.  The
+metric is achieved HBM GB/s over ALGORITHMIC bytes (slot payloads + Q/out + block table), whole job.  `e2e` is the same
+metric through the public wrappers with host buffers: ONE pinned H2D copy of the step's inputs (Q, the new token's K/V,
+slot ids, sequence lengths, the block-table column that changed), paged encode of the new token, decode, D2H of the
+output, synchronised every step (`eager_value`: the same calls issued from Python every step instead of replayed).
 
 `--impl reference` times the reference algorithm's CPU restatement (oracle/) on the host cores, on a bounded sample.
 """
@@ -33,22 +40,55 @@ ROOT = Path(__file__).resolve().parent
 if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
-H_KV, GROUP, BLOCK = 8, 4, 16
-METRIC = "cda_decode_k4v4_hbm_gbs"
+H_KV, BLOCK = 8, 16
 UNIT = "GB/s"
 # dram bytes (read + write) per algorithmic byte of the split kernel, from the ncu capture of the B=16, N=65536 cell
 DRAM_TRAFFIC_RATIO = 1.062
+RTOL, ATOL = 2e-3, 1e-3            # stated output tolerance of the path: |got - want| <= 1e-3 + 2e-3 |want|
+
+
+def payload_bytes(k_bits, v_bits):
+    return 16 * k_bits + 16 * v_bits + 8
 
 
 def algorithmic_bytes(B, N, H_kv, H_q, k_bits=4, v_bits=4, block=BLOCK):
-    payload = 16 * k_bits + 16 * v_bits + 8
-    return B * H_kv * N * payload + B * H_q * 128 * 2 * 2 + B * (-(-N // block)) * 4 + B * 4
+    return B * H_kv * N * payload_bytes(k_bits, v_bits) + B * H_q * 128 * 2 * 2 + B * (-(-N // block)) * 4 + B * 4
 
 
-def config(args, n_gpus):
-    return {"workload": f"decode k4v4 B={args.batch} N={args.ctx} H_q={H_KV * GROUP} H_kv={H_KV} d=128 block={BLOCK}",
-            "timing": "CUDA-graph replay, CUDA events, max over ranks", "sharding": f"kv-head x{n_gpus}",
+def metric_name(args):
+    return f"cda_decode_k{args.k_bits}v{args.v_bits}_hbm_gbs"
+
+
+def config(args, n_gpus, device_timing=True):
+    H_q = H_KV * args.group
+    if args.workload == "decode_seqsplit":
+        return {"workload": f"decode_seqsplit k4v4 B=1 N={args.ctx} H_q={H_q} H_kv={H_KV} d=128 block={BLOCK}",
+                "timing": "CUDA-graph replay (partial + all-gather + merge), CUDA events, max over ranks" if device_timing
+                          else "host wall clock per call (CPU)",
+                "sharding": f"sequence x{n_gpus}: rank r owns keys [r N/W, (r+1) N/W)",
+                "l2": "inputs (cache) larger than L2; no flush needed", "page_order": "seeded random permutation"}
+    return {"workload": f"decode k{args.k_bits}v{args.v_bits} B={args.batch} N={args.ctx} H_q={H_q} H_kv={H_KV} d=128 block={BLOCK}",
+            "timing": "CUDA-graph replay, CUDA events, max over ranks" if device_timing else "host wall clock per call (CPU)",
+            "sharding": f"kv-head x{n_gpus}",
             "l2": "inputs (cache) larger than L2; no flush needed", "page_order": "seeded random permutation"}
+
+
+def measured_peak(key, fallback):
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            return float(json.loads(path.read_text())[key]), "measured"
+        except Exception:
+            pass
+    return fallback, "fallback"
+
+
+def violations(got, want):
+    """(elements outside the stated tolerance, worst |err| / bound, max |err|) of fp16 outputs against the oracle."""
+    g, w = got.float(), want.float()
+    err = (g - w).abs()
+    ratio = err / (ATOL + RTOL * w.abs())
+    return int((ratio > 1.0).sum()), float(ratio.max()), float(err.max())
 
 
 # ---- clocks ---------------------------------------------------------------------------------------------------------------
@@ -98,70 +138,109 @@ class ClockSampler:
                 "samples": len(self.samples)}
 
 
-# ---- reference arm (CPU) ----------------------------------------------------------------------------------------------------
+def dist_env(args):
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run --nproc-per-node {args.gpus}")
+    return world, rank, local
 
-def cpu_sample_case(args, n_seq):
-    """n_seq sequences of the workload built entirely on the CPU with the oracle's encoder."""
+
+# ---- reference arm (CPU): decode ---------------------------------------------------------------------------------------------
+
+def cpu_sample_case(args, n_seq, ctx, group):
+    """n_seq sequences of `ctx` tokens of the workload built entirely on the CPU with the oracle's encoder."""
     import torch
     from oracle import cda_oracle as O
-    cb = O.default_codebook(16)
-    N, blocks = args.ctx, -(-args.ctx // BLOCK)
-    cache = torch.zeros(n_seq * blocks * BLOCK, H_KV, 144, dtype=torch.uint8)
-    gen = torch.Generator().manual_seed(0xCDA + N + 97 * args.batch)
+    cbk, cbv = O.default_codebook(16 if args.k_bits == 4 else 4), O.default_codebook(16 if args.v_bits == 4 else 4)
+    blocks = -(-ctx // BLOCK)
+    cache = torch.zeros(n_seq * blocks * BLOCK, H_KV, O.slot_bytes(args.k_bits, args.v_bits), dtype=torch.uint8)
+    gen = torch.Generator().manual_seed(0xCDA + ctx + 97 * args.batch)
     bt = torch.randperm(n_seq * blocks, generator=gen).view(n_seq, blocks).to(torch.int32)
-    Q = torch.randn(n_seq, H_KV * GROUP, 128, generator=gen).half()
+    Q = torch.randn(n_seq, H_KV * group, 128, generator=gen).half()
     for b in range(n_seq):
-        K = torch.randn(N, H_KV, 128, generator=gen)
+        K = torch.randn(ctx, H_KV, 128, generator=gen)
         K[..., [3, 37, 64, 101]] *= 8.0
-        V = torch.randn(N, H_KV, 128, generator=gen)
-        O.pack_slots(cache, O.slots_of_sequence(bt[b], N, BLOCK).to(torch.int32), O.encode(K.half(), cb), O.encode(V.half(), cb))
-    return Q, cache, bt, torch.full((n_seq,), N, dtype=torch.int32), cb
+        V = torch.randn(ctx, H_KV, 128, generator=gen)
+        O.pack_slots(cache, O.slots_of_sequence(bt[b], ctx, BLOCK).to(torch.int32), O.encode(K.half(), cbk), O.encode(V.half(), cbv),
+                     args.k_bits, args.v_bits)
+    return Q, cache, bt, torch.full((n_seq,), ctx, dtype=torch.int32), cbk, cbv
 
 
-def time_oracle(Q, cache, bt, seq, cb, steps, warmup):
-    import torch
+def time_oracle(Q, cache, bt, seq, cbk, cbv, group, k_bits, v_bits, steps, warmup):
     from oracle import cda_oracle as O
     times = []
     for i in range(warmup + steps):
         t0 = time.perf_counter()
-        O.paged_decode(Q, cache, bt, seq, cb_K=cb, cb_V=cb, group=GROUP, block_size=BLOCK)
+        O.paged_decode(Q, cache, bt, seq, cb_K=cbk, cb_V=cbv, group=group, block_size=BLOCK, k_bits=k_bits, v_bits=v_bits)
         if i >= warmup:
             times.append(time.perf_counter() - t0)
     return times
 
 
-def run_reference(args):
+def run_reference_decode(args):
+    """The reference's own CPU implementation of the path (its Python algorithm, restated in oracle/) on all host cores.
+    Bounded sample: one sequence, all 8 KV heads, truncated to a context that keeps the whole run near 90 s of CPU work.
+    CPU time is linear in the context length, so the GB/s figure does not depend on the truncation."""
     import torch
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    # Bounded sample: one sequence, all 8 KV heads, truncated to a context that keeps the whole run near 90 s of CPU
-    # work.  CPU time is linear in the context length, so the GB/s figure does not depend on the truncation.
-    probe = argparse.Namespace(**vars(args))
-    probe.ctx = min(args.ctx, 8192)
-    case = cpu_sample_case(probe, 1)
-    per_token = min(time_oracle(*case, 2, 1)) / probe.ctx
+    group = args.group
+    case = cpu_sample_case(args, 1, min(args.ctx, 8192), group)
+    per_token = min(time_oracle(*case, group, args.k_bits, args.v_bits, 2, 1)) / min(args.ctx, 8192)
     budget = 90.0 / (args.steps + args.warmup)
     ctx = int(max(1024, min(args.ctx, budget / per_token))) // 16 * 16
-    samp = argparse.Namespace(**vars(args))
-    samp.ctx = ctx
-    Q, cache, bt, seq, cb = cpu_sample_case(samp, 1)
-    times = time_oracle(Q, cache, bt, seq, cb, args.steps, args.warmup)
+    Q, cache, bt, seq, cbk, cbv = cpu_sample_case(args, 1, ctx, group)
+    times = time_oracle(Q, cache, bt, seq, cbk, cbv, group, args.k_bits, args.v_bits, args.steps, args.warmup)
     t = sum(times) / len(times)
-    gbs = algorithmic_bytes(1, ctx, H_KV, H_KV * GROUP) / t / 1e9
-    sample = (f"1 of {args.batch} sequences, first {ctx} of {args.ctx} tokens, all 8 KV heads, per step; "
+    gbs = algorithmic_bytes(1, ctx, H_KV, H_KV * group, args.k_bits, args.v_bits) / t / 1e9
+    what = "1 sequence" if args.workload == "decode_seqsplit" else f"1 of {args.batch} sequences"
+    sample = (f"{what}, first {ctx} of {args.ctx} tokens, all 8 KV heads, per step; "
               "CPU restatement (oracle/) of cda.algorithm.attention.attention_compressed, torch CPU")
-    line = {"impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "f32", "data": "synthetic", "config": config(args, args.gpus),
+    line = {"impl": "reference", "metric": metric_name(args), "value": gbs, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": t * 1e3, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic", "config": config(args, args.gpus, device_timing=False),
             "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
             "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
 
 
-# ---- our arm ---------------------------------------------------------------------------------------------------------------------
+# ---- our arm: decode, KV-head sharding -------------------------------------------------------------------------------------------
+
+def graph_of(call, warm, torch):
+    """Warm `call` up on a side stream, capture it once, replay it three times."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(max(warm, 3)):
+            call()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        call()
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    return graph
+
+
+def timed_replays(graph, steps, barrier, torch):
+    """Per-step device times (ms) of `steps` back-to-back replays and their total, events on the launching stream."""
+    barrier()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+    ev[0].record()
+    for i in range(steps):
+        graph.replay()
+        ev[i + 1].record()
+    barrier()
+    return [ev[i].elapsed_time(ev[i + 1]) for i in range(steps)], ev[0].elapsed_time(ev[-1])
+
 
 def run_ours(args):
     import torch
@@ -170,11 +249,7 @@ def run_ours(args):
     from sub0_b200.kernels_cuda.wrappers import decode_hmma_v1, paged_encode_fused_cuda
     from sub0_b200.synth import build_decode_workload, sequence_tensors
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if world != args.gpus:
-        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run --nproc-per-node {args.gpus}")
+    world, rank, local = dist_env(args)
     if H_KV % world:
         raise SystemExit("the 8 KV heads must divide evenly over the ranks")
     torch.cuda.set_device(local)
@@ -188,9 +263,17 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    B, N = args.batch, args.ctx
+    def max_over_ranks(x):
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    B, N, GROUP = args.batch, args.ctx, args.group
+    kb, vb = args.k_bits, args.v_bits
     hpr = H_KV // world
-    wl = build_decode_workload(B, N, H_kv=H_KV, group=GROUP, device=dev, head_lo=rank * hpr, head_hi=(rank + 1) * hpr)
+    wl = build_decode_workload(B, N, H_kv=H_KV, group=GROUP, k_bits=kb, v_bits=vb, device=dev, head_lo=rank * hpr,
+                               head_hi=(rank + 1) * hpr)
     out = torch.empty_like(wl.Q)
     ws = ops.new_workspace(ops.decode_workspace_bytes(B, hpr * GROUP, hpr, N), dev)
 
@@ -198,31 +281,10 @@ def run_ours(args):
         decode_hmma_v1(wl.Q, wl.cache, wl.block_table, wl.seq_lens, out, cb_K=wl.cb_K, cb_V=wl.cb_V, group_size=GROUP,
                        block_size=BLOCK, max_seq_len=N, workspace=ws)
 
-    # warm-up (untimed) + capture
-    side = torch.cuda.Stream()
-    side.wait_stream(torch.cuda.current_stream())
-    with torch.cuda.stream(side):
-        for _ in range(max(args.warmup, 3)):
-            call()
-    torch.cuda.current_stream().wait_stream(side)
-    torch.cuda.synchronize()
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph):
-        call()
-    for _ in range(3):
-        graph.replay()
-
+    graph = graph_of(call, args.warmup, torch)
     sampler = ClockSampler(local)
-    barrier()
     sampler.start()
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
-    ev[0].record()
-    for i in range(args.steps):
-        graph.replay()
-        ev[i + 1].record()
-    barrier()
-    per_step = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]        # ms, device clock, launching stream
-    total_ms = ev[0].elapsed_time(ev[-1])
+    per_step, total_ms = timed_replays(graph, args.steps, barrier, torch)
     if len(sampler.samples) < 5:                                                     # short run: keep the same load going
         t_end = time.perf_counter() + 0.3
         while time.perf_counter() < t_end:
@@ -230,40 +292,90 @@ def run_ours(args):
                 graph.replay()
             torch.cuda.synchronize()
     sampler.stop()
-
-    t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    total_ms = float(t.item())
-    ms_step = total_ms / args.steps
-    bytes_job = algorithmic_bytes(B, N, H_KV, H_KV * GROUP)
+    ms_step = max_over_ranks(total_ms) / args.steps
+    bytes_job = algorithmic_bytes(B, N, H_KV, H_KV * GROUP, kb, vb)
     value = bytes_job / (ms_step * 1e-3) / 1e9
 
+    # ---- sustained figure: at least 2 s of back-to-back replays (the board reaches its power limit) -----------------------------
+    sustained = None
+    if not args.no_sustained:
+        n_rep = max(args.steps, int(2.2 / (ms_step * 1e-3)))
+        _, tot = timed_replays(graph, n_rep, barrier, torch)
+        sus_ms = max_over_ranks(tot) / n_rep
+        sustained = {"replays": n_rep, "ms_per_step": sus_ms, "value": bytes_job / (sus_ms * 1e-3) / 1e9}
+
+    # ---- identity page order (the reference's benchmark uses block_table = arange) ------------------------------------------------
+    identity = None
+    if not args.no_identity_order:
+        inv = torch.empty(wl.block_table.numel(), dtype=torch.int64, device=dev)
+        inv[wl.block_table.flatten().long()] = torch.arange(wl.block_table.numel(), device=dev)
+        # physical page p holds logical page inv[p]; re-order the pages so that logical page i sits in physical page i
+        pages = wl.cache.view(-1, BLOCK, wl.cache.shape[1], wl.cache.shape[2])
+        chunk = 4096
+        ident_cache = torch.empty_like(wl.cache)
+        ipages = ident_cache.view_as(pages)
+        flat_bt = wl.block_table.flatten().long()
+        for s0 in range(0, flat_bt.numel(), chunk):
+            ipages[s0:s0 + chunk] = pages[flat_bt[s0:s0 + chunk]]
+        ident_bt = torch.arange(wl.block_table.numel(), dtype=torch.int32, device=dev).view_as(wl.block_table)
+        out_i = torch.empty_like(out)
+
+        def call_i():
+            decode_hmma_v1(wl.Q, ident_cache, ident_bt, wl.seq_lens, out_i, cb_K=wl.cb_K, cb_V=wl.cb_V, group_size=GROUP,
+                           block_size=BLOCK, max_seq_len=N, workspace=ws)
+
+        g_i = graph_of(call_i, 3, torch)
+        _, tot = timed_replays(g_i, args.steps, barrier, torch)
+        id_ms = max_over_ranks(tot) / args.steps
+        graph.replay()
+        torch.cuda.synchronize()
+        identity = {"ms_per_step": id_ms, "value": bytes_job / (id_ms * 1e-3) / 1e9, "same_output": bool(torch.equal(out_i, out))}
+        del ident_cache, ipages, g_i, inv
+        torch.cuda.empty_cache()
+
     # ---- e2e: host buffers in, host buffer out, every step ----------------------------------------------------------------
-    pin = lambda t_: t_.cpu().pin_memory()
-    hQ, hbt, hsl = pin(wl.Q), pin(wl.block_table), pin(wl.seq_lens)
+    # One pinned staging buffer holds everything that changes between decode steps -- Q, the new token's K and V, its slot
+    # ids, the sequence lengths and the one block-table column that can change -- and crosses PCIe in a single copy; the
+    # kernels read views of its device twin.  The block table itself and the KV cache are resident state.
     _, Kall, Vall = sequence_tensors(0xCDA + 7, 0, B, H_KV, GROUP, dev)           # one new token per sequence
-    hK, hV = pin(Kall[:, rank * hpr:(rank + 1) * hpr].contiguous()), pin(Vall[:, rank * hpr:(rank + 1) * hpr].contiguous())
+    newK = Kall[:, rank * hpr:(rank + 1) * hpr].contiguous()
+    newV = Vall[:, rank * hpr:(rank + 1) * hpr].contiguous()
     pos = N - 1
-    hslots = pin((wl.block_table[:, pos // BLOCK].long() * BLOCK + pos % BLOCK).to(torch.int32))
+    col = pos // BLOCK
+    parts = {"Q": wl.Q, "K": newK, "V": newV,
+             "slots": (wl.block_table[:, col].long() * BLOCK + pos % BLOCK).to(torch.int32),
+             "seq_lens": wl.seq_lens, "bt_col": wl.block_table[:, col].contiguous()}
+    offs, at = {}, 0
+    for k_, t_ in parts.items():
+        offs[k_] = at
+        at += (t_.numel() * t_.element_size() + 255) // 256 * 256
+    h_stage = torch.empty(at, dtype=torch.uint8).pin_memory()
+    d_stage = torch.empty(at, dtype=torch.uint8, device=dev)
+
+    def view(buf, k_):
+        t_ = parts[k_]
+        nb = t_.numel() * t_.element_size()
+        return buf[offs[k_]:offs[k_] + nb].view(t_.dtype).view(t_.shape)
+
+    for k_, t_ in parts.items():
+        view(h_stage, k_).copy_(t_.cpu())
+    dQ, dK, dV, dslots, dsl, dcol = (view(d_stage, k_) for k_ in ("Q", "K", "V", "slots", "seq_lens", "bt_col"))
+    d_bt = wl.block_table.clone()
     hout = torch.empty(out.shape, dtype=out.dtype).pin_memory()
-    dQ, dbt, dsl = torch.empty_like(wl.Q), torch.empty_like(wl.block_table), torch.empty_like(wl.seq_lens)
-    dK, dV = torch.empty(hK.shape, dtype=hK.dtype, device=dev), torch.empty(hV.shape, dtype=hV.dtype, device=dev)
-    dslots = torch.empty(B, dtype=torch.int32, device=dev)
-    h2d = sum(x.numel() * x.element_size() for x in (hQ, hbt, hsl, hK, hV, hslots))
+    h2d = sum(t_.numel() * t_.element_size() for t_ in parts.values())
     d2h = hout.numel() * hout.element_size()
+
+    def enqueue():
+        d_stage.copy_(h_stage, non_blocking=True)
+        d_bt[:, col].copy_(dcol)
+        paged_encode_fused_cuda(dK, dV, dslots, wl.cache, cb_K=wl.cb_K, cb_V=wl.cb_V)
+        decode_hmma_v1(dQ, wl.cache, d_bt, dsl, out, cb_K=wl.cb_K, cb_V=wl.cb_V, group_size=GROUP, block_size=BLOCK,
+                       max_seq_len=N, workspace=ws)
+        hout.copy_(out, non_blocking=True)
 
     def e2e_step():
         enqueue()
         torch.cuda.current_stream().synchronize()
-
-    def enqueue():
-        dQ.copy_(hQ, non_blocking=True); dbt.copy_(hbt, non_blocking=True); dsl.copy_(hsl, non_blocking=True)
-        dK.copy_(hK, non_blocking=True); dV.copy_(hV, non_blocking=True); dslots.copy_(hslots, non_blocking=True)
-        paged_encode_fused_cuda(dK, dV, dslots, wl.cache, cb_K=wl.cb_K, cb_V=wl.cb_V)
-        decode_hmma_v1(dQ, wl.cache, dbt, dsl, out, cb_K=wl.cb_K, cb_V=wl.cb_V, group_size=GROUP, block_size=BLOCK,
-                       max_seq_len=N, workspace=ws)
-        hout.copy_(out, non_blocking=True)
 
     def timed(step):
         for _ in range(3):
@@ -275,13 +387,8 @@ def run_ours(args):
             step()
         e1.record()
         barrier()
-        t_ = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
-        if world > 1:
-            dist.all_reduce(t_, op=dist.ReduceOp.MAX)
-        return float(t_.item()) / args.steps
+        return max_over_ranks(e0.elapsed_time(e1)) / args.steps
 
-    # (1) every call made from Python each step; (2) the same calls captured once in a CUDA graph (copy nodes read the
-    # pinned host buffers at replay time, the way a serving engine replays its decode step) -- the reported figure
     eager_ms = timed(e2e_step)
     for _ in range(3):
         e2e_step()
@@ -301,65 +408,245 @@ def run_ours(args):
 
     line = None
     if rank == 0:
-        peaks_path = ROOT / "MEASURED_PEAKS.json"
-        peak, peak_src = 6650.0, "fallback"
-        if peaks_path.exists():
-            try:
-                peak, peak_src = float(json.loads(peaks_path.read_text())["hbm_gbs"]), "measured"
-            except Exception:
-                pass
-        rank_bytes = algorithmic_bytes(B, N, hpr, hpr * GROUP)
+        peak, peak_src = measured_peak("hbm_gbs", 6650.0)
+        rank_bytes = algorithmic_bytes(B, N, hpr, hpr * GROUP, kb, vb)
         launch_ms = statistics.mean(per_step)
         achieved = rank_bytes / (launch_ms * 1e-3) / 1e9
-        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        roof = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": UNIT, "frac": achieved / peak,
+                "frac_of_min_step": rank_bytes / (min(per_step) * 1e-3) / 1e9 / peak,
+                "peak_source": peak_src, "traffic": rank_bytes * DRAM_TRAFFIC_RATIO if (kb, vb) == (4, 4) else None,
+                "kind": "burst: mean of the timed replays, which end before the board reaches its power limit; "
+                        "`sustained` is the same step over >= 2 s of replays",
+                "note": "rank-0 launch = split kernel + merge kernel (merge < 2 % of the time); algorithmic bytes of this "
+                        "rank's shard; traffic = these bytes x 1.062, the ratio of dram__bytes_read+write to algorithmic "
+                        "bytes in the ncu capture of the B=16 cell (144-byte slots vs 136-byte payloads, plus partials), "
+                        "which grows with the units processed; the peak is a best-of-10 burst figure"}
+        if sustained is not None:
+            roof["sustained"] = {"achieved": sustained["value"] / world, "frac": sustained["value"] / world / peak,
+                                 "ms_per_step": sustained["ms_per_step"], "replays": sustained["replays"]}
+        line = {"metric": metric_name(args), "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": ms_step, "us_per_layer_median": statistics.median(per_step) * 1e3,
                 "us_per_layer_min": min(per_step) * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
                 "dtype": "f16", "data": "synthetic", "config": config(args, world),
                 "frac_of_8000_gbs_nominal": value / (8000.0 * world),
-                "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": UNIT, "frac": achieved / peak,
-                             "frac_of_min_step": rank_bytes / (min(per_step) * 1e-3) / 1e9 / peak,
-                             "peak_source": peak_src, "traffic": rank_bytes * DRAM_TRAFFIC_RATIO,
-                             "note": "rank-0 launch = split kernel + merge kernel (merge < 5 % of the time); algorithmic "
-                                     "bytes of this rank's shard; traffic = these bytes x 1.062, the ratio of "
-                                     "dram__bytes_read+write to algorithmic bytes in the ncu capture of the B=16 cell "
-                                     "(144-byte slots vs 136-byte payloads, plus partials), which grows with the units "
-                                     "processed; the peak is a best-of-10 burst figure, frac_of_min_step is the like-for-like "
-                                     "fraction, frac the one sustained over all steps"},
+                "roofline": roof,
                 "e2e": {"value": e2e_val, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d * world,
                         "d2h_bytes_per_step": d2h * world,
                         "eager_value": e2e_eager_val, "eager_ms_per_step": eager_ms,
-                        "what": "pinned H2D of Q/new K,V/slots/block table/seq lens + paged encode + decode + D2H of the output, synchronised every step; the KV cache is resident state; value = the step's calls captured once in a CUDA graph and replayed (copy nodes read the pinned buffers at replay), eager_value = the same calls issued from Python every step"},
+                        "what": "one pinned H2D copy of Q / new K,V / slot ids / seq lens / the changed block-table column + "
+                                "paged encode + decode + D2H of the output, synchronised every step; the KV cache and the rest "
+                                "of the block table are resident state; value = the step's calls captured once in a CUDA graph "
+                                "and replayed (the copy node reads the pinned buffer at replay), eager_value = the same calls "
+                                "issued from Python every step"},
                 "gpu_launches": 2 * args.steps, "clocks": sampler.summary()}
+        if identity is not None:
+            line["identity_page_order"] = identity
+        if sustained is not None:
+            line["sustained_value"] = sustained["value"]
 
     # ---- CPU baseline + parity on a bounded sample (rank 0, N=1 only) ----------------------------------------------------------------
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         from oracle import cda_oracle as O
         cores = os.cpu_count() or 1
         torch.set_num_threads(cores)
-        n_seq = 1
         blocks = -(-N // BLOCK)
         sel = [B - 1]
         rows = wl.block_table[sel].long().flatten()
         slot_ids = (rows[:, None] * BLOCK + torch.arange(BLOCK, device=dev)[None, :]).flatten()
         sub_cache = wl.cache[slot_ids].cpu()
-        sub_bt = torch.arange(n_seq * blocks, dtype=torch.int32).view(n_seq, blocks)
-        cb = wl.cb_K.cpu()
+        sub_bt = torch.arange(blocks, dtype=torch.int32).view(1, blocks)
+        cbk, cbv = wl.cb_K.cpu(), wl.cb_V.cpu()
         Qs = wl.Q[sel].cpu()
-        seq = torch.full((n_seq,), N, dtype=torch.int32)
+        seq = torch.full((1,), N, dtype=torch.int32)
         graph.replay()
         torch.cuda.synchronize()
-        times = time_oracle(Qs, sub_cache, sub_bt, seq, cb, 2, 1)
-        want = O.paged_decode(Qs, sub_cache, sub_bt, seq, cb_K=cb, cb_V=cb, group=GROUP, block_size=BLOCK)
+        times = time_oracle(Qs, sub_cache, sub_bt, seq, cbk, cbv, GROUP, kb, vb, 2, 1)
+        want = O.paged_decode(Qs, sub_cache, sub_bt, seq, cb_K=cbk, cb_V=cbv, group=GROUP, block_size=BLOCK, k_bits=kb, v_bits=vb)
         got = out[sel].cpu()
-        err = (got.float() - want.float()).abs()
-        ok = bool((err <= 1e-3 + 2e-3 * want.float().abs()).all())
+        bad, worst, max_err = violations(got, want)
         tcpu = sum(times) / len(times)
-        line["cpu_baseline"] = {"value": algorithmic_bytes(n_seq, N, H_KV, H_KV * GROUP) / tcpu / 1e9, "unit": UNIT, "cores": cores,
+        line["cpu_baseline"] = {"value": algorithmic_bytes(1, N, H_KV, H_KV * GROUP, kb, vb) / tcpu / 1e9, "unit": UNIT, "cores": cores,
                                 "kind": "port", "ms_per_sample": tcpu * 1e3,
-                                "sample": f"{n_seq} of {B} sequences (N={N}, all 8 KV heads), the bytes the GPU encoded; oracle port, torch CPU"}
-        line["parity_sample"] = {"ok": ok, "max_abs_err": float(err.max()), "rows": int(got.shape[0] * got.shape[1])}
+                                "sample": f"1 of {B} sequences (N={N}, all 8 KV heads), the bytes the GPU encoded; oracle port, torch CPU"}
+        line["parity_sample"] = {"ok": bad == 0, "violations": bad, "worst_err_over_bound": worst, "max_abs_err": max_err,
+                                 "elements": int(got.numel()), "bound": "|got - want| <= 1e-3 + 2e-3 |want| on every element"}
+        if bad:
+            print(json.dumps(line))
+            raise SystemExit(f"parity: {bad} output elements outside the stated tolerance (worst x{worst:.2f})")
     if rank == 0:
         print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+# ---- our arm: one long sequence, keys split over the ranks ---------------------------------------------------------------------------
+
+def run_seqsplit(args):
+    import torch
+    import torch.distributed as dist
+    from sub0_b200 import ops
+    from sub0_b200.codebook import default_codebook
+    from sub0_b200.sharding import sequence_shard
+    from sub0_b200.synth import OUTLIER_CHANNELS
+
+    world, rank, local = dist_env(args)
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x):
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    N, GROUP = args.ctx, args.group
+    H_q = H_KV * GROUP
+    lo, hi = sequence_shard(rank, world, N, BLOCK)
+    n_loc = hi - lo
+    cb = default_codebook(16, device=dev)
+    # the same Q on every rank; keys and values of token t depend on (seed, t // chunk) only, so any sharding sees the same data
+    gq = torch.Generator(device=dev).manual_seed(0xCDA + N)
+    Q = torch.randn(1, H_q, 128, generator=gq, device=dev, dtype=torch.float32).to(torch.float16)
+    blocks = -(-n_loc // BLOCK)
+    cache = torch.zeros(max(blocks, 1) * BLOCK, H_KV, 144, dtype=torch.uint8, device=dev)
+    order = torch.randperm(max(blocks, 1), generator=torch.Generator().manual_seed(0xCDA + rank)).to(torch.int32).to(dev)
+    chunk = 65536
+    for c0 in range(lo // chunk * chunk, hi, chunk):
+        g = torch.Generator(device=dev).manual_seed(0xCDA + 1_000_003 * (c0 // chunk + 1))
+        K = torch.randn(chunk, H_KV, 128, generator=g, device=dev, dtype=torch.float32)
+        K[..., list(OUTLIER_CHANNELS)] *= 8.0
+        V = torch.randn(chunk, H_KV, 128, generator=g, device=dev, dtype=torch.float32)
+        a, b = max(c0, lo), min(c0 + chunk, hi)
+        pos = torch.arange(a - lo, b - lo, device=dev)
+        slots = (order[pos // BLOCK].long() * BLOCK + pos % BLOCK).to(torch.int32)
+        ops.paged_encode(K[a - c0:b - c0].to(torch.float16), V[a - c0:b - c0].to(torch.float16), slots, cache, cb, cb)
+    bt = order.view(1, -1).contiguous()
+    sl = torch.tensor([n_loc], dtype=torch.int32, device=dev)
+    ws = ops.new_workspace(ops.decode_workspace_bytes(1, H_q, H_KV, max(n_loc, 1)), dev)
+    packed = torch.empty(1, H_q, 130, dtype=torch.float32, device=dev)
+    gathered = torch.empty(world, 1, H_q, 130, dtype=torch.float32, device=dev)
+    out = torch.empty(1, H_q, 128, dtype=torch.float16, device=dev)
+
+    def partial():
+        ops.decode_partial(Q, cache, bt, sl, cb_K=cb, cb_V=cb, block_size=BLOCK, max_seq_len=max(n_loc, 1), workspace=ws, out=packed)
+
+    def exchange():
+        if world > 1:
+            dist.all_gather_into_tensor(gathered.view(-1), packed.view(-1))
+        else:
+            gathered.copy_(packed.view_as(gathered))
+
+    def step_full():
+        partial()
+        exchange()
+        ops.merge_partials(gathered, out)
+
+    def step_no_exchange():                       # same kernels, the all-gather left out (merges stale remote rows)
+        partial()
+        gathered[rank].copy_(packed)
+        ops.merge_partials(gathered, out)
+
+    step_full()
+    torch.cuda.synchronize()
+    g_full = graph_of(step_full, args.warmup, torch)
+    sampler = ClockSampler(local)
+    sampler.start()
+    per_step, total_ms = timed_replays(g_full, args.steps, barrier, torch)
+    sampler.stop()
+    ms_step = max_over_ranks(total_ms) / args.steps
+    g_local = graph_of(step_no_exchange, 3, torch)
+    _, tot = timed_replays(g_local, args.steps, barrier, torch)
+    ms_local = max_over_ranks(tot) / args.steps
+    g_full.replay()
+    torch.cuda.synchronize()
+
+    # ---- parity: KV head 0 of every rank's slots on rank 0, oracle over the whole sequence -----------------------------------------
+    head_slots = torch.empty(n_loc, 144, dtype=torch.uint8, device=dev)
+    pos = torch.arange(n_loc, device=dev)
+    head_slots.copy_(cache[(order[pos // BLOCK].long() * BLOCK + pos % BLOCK), 0])
+    if world > 1:
+        sizes = [sequence_shard(r, world, N, BLOCK) for r in range(world)]
+        if len({b_ - a_ for a_, b_ in sizes}) != 1:
+            raise SystemExit("decode_seqsplit: the context must split evenly over the ranks")
+        all_slots = torch.empty(world * n_loc, 144, dtype=torch.uint8, device=dev)
+        dist.all_gather_into_tensor(all_slots.view(-1), head_slots.view(-1))
+    else:
+        all_slots = head_slots
+    bytes_job = algorithmic_bytes(1, N, H_KV, H_q)
+    line = None
+    if rank == 0:
+        from oracle import cda_oracle as O
+        cores = os.cpu_count() or 1
+        torch.set_num_threads(cores)
+        t0 = time.perf_counter()
+        want = O.paged_decode(Q[:, :GROUP].cpu(), all_slots.cpu().view(N, 1, 144), torch.arange(-(-N // BLOCK), dtype=torch.int32)[None],
+                              torch.tensor([N], dtype=torch.int32), cb_K=cb.cpu(), cb_V=cb.cpu(), group=GROUP, block_size=BLOCK)
+        t_cpu = time.perf_counter() - t0
+        bad, worst, max_err = violations(out[:, :GROUP].cpu(), want)
+        peak, peak_src = measured_peak("hbm_gbs", 6650.0)
+        rank_bytes = algorithmic_bytes(1, n_loc, H_KV, H_q)
+        achieved = rank_bytes / (statistics.mean(per_step) * 1e-3) / 1e9
+        value = bytes_job / (ms_step * 1e-3) / 1e9
+        line = {"metric": "cda_decode_seqsplit_k4v4_hbm_gbs", "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms_step, "us_per_layer_median": statistics.median(per_step) * 1e3,
+                "us_without_allgather": ms_local * 1e3, "allgather_bytes_per_rank": H_q * 130 * 4,
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+                "config": config(args, world), "frac_of_8000_gbs_nominal": value / (8000.0 * world),
+                "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": UNIT, "frac": achieved / peak,
+                             "peak_source": peak_src, "traffic": None,
+                             "note": "rank-0 step = partial (split + merge-to-packed kernels) + all-gather + merge kernel over "
+                                     "this rank's key range; latency-bound at 8 ranks (17.8 us of traffic per rank at 8 TB/s)"},
+                "e2e": None, "gpu_launches": 3 * args.steps, "clocks": sampler.summary(),
+                "parity_sample": {"ok": bad == 0, "violations": bad, "worst_err_over_bound": worst, "max_abs_err": max_err,
+                                  "elements": int(want.numel()),
+                                  "what": "KV head 0 (its 8 query heads) over all ranks' slots against the CPU oracle",
+                                  "bound": "|got - want| <= 1e-3 + 2e-3 |want| on every element"},
+                "cpu_baseline": {"value": algorithmic_bytes(1, N, 1, GROUP) / t_cpu / 1e9, "unit": UNIT, "cores": cores, "kind": "port",
+                                 "sample": f"KV head 0 of 8 over the whole sequence (N={N}), one pass, oracle port, torch CPU"}}
+    # e2e through host buffers: pinned Q in, pinned output back, every step
+    hQ = Q.cpu().pin_memory()
+    hout = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+    dQ = torch.empty_like(Q)
+
+    def e2e_enqueue():
+        dQ.copy_(hQ, non_blocking=True)
+        ops.decode_partial(dQ, cache, bt, sl, cb_K=cb, cb_V=cb, block_size=BLOCK, max_seq_len=max(n_loc, 1), workspace=ws, out=packed)
+        exchange()
+        ops.merge_partials(gathered, out)
+        hout.copy_(out, non_blocking=True)
+
+    for _ in range(3):
+        e2e_enqueue()
+        torch.cuda.synchronize()
+    g_e2e = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g_e2e):
+        e2e_enqueue()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        g_e2e.replay()
+        torch.cuda.current_stream().synchronize()
+    e1.record()
+    barrier()
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / args.steps
+    if rank == 0:
+        line["e2e"] = {"value": bytes_job / (e2e_ms * 1e-3) / 1e9, "unit": UNIT, "ms_per_step": e2e_ms,
+                       "h2d_bytes_per_step": hQ.numel() * 2 * world, "d2h_bytes_per_step": hout.numel() * 2 * world,
+                       "what": "pinned H2D of Q + partial + all-gather + merge + D2H of the output, one CUDA graph replayed and "
+                               "synchronised every step; the KV cache is resident state"}
+        print(json.dumps(line))
+        if line["parity_sample"]["violations"]:
+            raise SystemExit("decode_seqsplit parity: output outside the stated tolerance")
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -373,14 +660,63 @@ def prompt_lengths(n_seq=8, lo=512, hi=8192):
     return [rng.randint(lo, hi) for _ in range(n_seq)]
 
 
-def measured_peak(key, fallback):
-    path = ROOT / "MEASURED_PEAKS.json"
-    if path.exists():
-        try:
-            return float(json.loads(path.read_text())[key]), "measured"
-        except Exception:
-            pass
-    return fallback, "fallback"
+def prompt_flops(lens, H_q):
+    return sum(4 * H_q * 128 * L * (L + 1) // 2 for L in lens)
+
+
+def run_prompt_reference(args):
+    """CPU arm of `--workload encode|prefill`: the oracle's encoder over a bounded number of rows / the oracle's causal
+    attention over the shortest prompt and one KV head, on all host cores."""
+    import torch
+    from oracle import cda_oracle as O
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    lens = prompt_lengths()
+    T, GROUP = sum(lens), 4
+    H_q = H_KV * GROUP
+    cb = O.default_codebook(16)
+    gen = torch.Generator().manual_seed(0xCDA + T)
+    times = []
+    if args.workload == "encode":
+        rows = 8192
+        K = torch.randn(rows, H_KV, 128, generator=gen)
+        K[..., [3, 37, 64, 101]] *= 8.0
+        K, V = K.half(), torch.randn(rows, H_KV, 128, generator=gen).half()
+        for i in range(args.warmup + args.steps):
+            t0 = time.perf_counter()
+            O.encode(K, cb), O.encode(V, cb)
+            if i >= args.warmup:
+                times.append(time.perf_counter() - t0)
+        t = sum(times) / len(times)
+        value, unit, metric = (rows * H_KV * (2 * 256 + 136) + 4 * rows) / t / 1e9, "GB/s", "cda_paged_encode_k4v4_hbm_gbs"
+        sample = f"{rows} of {T} tokens x 8 KV heads (K and V) per step, oracle port of Compressor.encode, torch CPU"
+    else:
+        L = min(min(lens), 2048)
+        K = torch.randn(L, 1, 128, generator=gen)
+        K[..., [3, 37, 64, 101]] *= 8.0
+        cache = torch.zeros(-(-L // BLOCK) * BLOCK, 1, 144, dtype=torch.uint8)
+        bt = torch.arange(-(-L // BLOCK), dtype=torch.int32)[None]
+        O.pack_slots(cache, O.slots_of_sequence(bt[0], L, BLOCK).to(torch.int32), O.encode(K.half(), cb),
+                     O.encode(torch.randn(L, 1, 128, generator=gen).half(), cb))
+        Q = torch.randn(L, GROUP, 128, generator=gen).half()
+        cu, sl = torch.tensor([0, L], dtype=torch.int32), torch.tensor([L], dtype=torch.int32)
+        for i in range(args.warmup + args.steps):
+            t0 = time.perf_counter()
+            O.paged_prefill(Q, cache, bt, cu, sl, cb_K=cb, cb_V=cb, group=GROUP, block_size=BLOCK)
+            if i >= args.warmup:
+                times.append(time.perf_counter() - t0)
+        t = sum(times) / len(times)
+        value, unit, metric = prompt_flops([L], GROUP) / t / 1e12, "TFLOP/s", "cda_prefill_k4v4_tflops"
+        sample = f"one prompt of {L} tokens, 1 of 8 KV heads (4 query heads) per step, oracle port of attention_compressed(causal=True), torch CPU"
+    print(json.dumps({"impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus, "steps": args.steps,
+                      "warmup": args.warmup, "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                      "dtype": "f32", "data": "synthetic",
+                      "config": {"workload": f"{args.workload} k4v4, 8 prompts of {lens} tokens (T={T}), H_q={H_q} H_kv={H_KV} d=128 block={BLOCK}",
+                                 "timing": "host wall clock per call (CPU)"},
+                      "cpu_baseline": {"value": value, "unit": unit, "cores": cores, "kind": "port", "sample": sample},
+                      "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
 
 
 def run_prompt_workload(args):
@@ -397,6 +733,7 @@ def run_prompt_workload(args):
     from sub0_b200.kernels_cuda.wrappers import paged_encode_fused_cuda
     from sub0_b200 import ops
 
+    GROUP = 4
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
     lens = prompt_lengths()
@@ -421,9 +758,9 @@ def run_prompt_workload(args):
     slots = torch.cat(slot_parts).to(torch.int32).to(dev)
     bt = bt.to(dev)
     seq_lens = torch.tensor(lens, dtype=torch.int32, device=dev)
-    cu = torch.zeros(len(lens) + 1, dtype=torch.int32)
-    cu[1:] = torch.tensor(lens).cumsum(0)
-    cu = cu.to(dev)
+    cu_host = torch.zeros(len(lens) + 1, dtype=torch.int32)
+    cu_host[1:] = torch.tensor(lens).cumsum(0)
+    cu = cu_host.to(dev)
     cb = codebook.default_codebook(16).to(dev)
     cache = torch.zeros(n_blocks * BLOCK, H_KV, ops.slot_bytes(4, 4), dtype=torch.uint8, device=dev)
     out = torch.empty_like(Q)
@@ -461,24 +798,105 @@ def run_prompt_workload(args):
             torch.cuda.synchronize()
     sampler.stop()
     ms = statistics.mean(per)
+
+    # e2e: the step's inputs start in pinned host memory, its result ends there
+    if args.workload == "encode":
+        hK, hV, hs = K.cpu().pin_memory(), V.cpu().pin_memory(), slots.cpu().pin_memory()
+        dK, dV, ds = torch.empty_like(K), torch.empty_like(V), torch.empty_like(slots)
+        last = slots[-1:].long()
+        hres = torch.empty(1, H_KV, 144, dtype=torch.uint8).pin_memory()
+
+        def e2e():
+            dK.copy_(hK, non_blocking=True); dV.copy_(hV, non_blocking=True); ds.copy_(hs, non_blocking=True)
+            paged_encode_fused_cuda(dK, dV, ds, cache, cb_K=cb, cb_V=cb)
+            hres.copy_(cache[last], non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+        h2d, d2h = (hK.numel() + hV.numel()) * 2 + hs.numel() * 4, hres.numel()
+    else:
+        hQ = Q.cpu().pin_memory()
+        dQ = torch.empty_like(Q)
+        hres = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+
+        def e2e():
+            dQ.copy_(hQ, non_blocking=True)
+            fa2_cda_prefill_varlen_v1(dQ, cache, bt, cu, seq_lens, out, cb_K=cb, cb_V=cb, rotation_fp32=rot, group_size=GROUP,
+                                      block_size=BLOCK, max_query_len=max(lens), max_seq_len=max(lens), causal=True,
+                                      fuse_fa2_epilogue=True)
+            hres.copy_(out, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+        h2d, d2h = hQ.numel() * 2, hres.numel() * 2
+    for _ in range(3):
+        e2e()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        e2e()
+    e1.record()
+    torch.cuda.synchronize()
+    e2e_ms = e0.elapsed_time(e1) / args.steps
+
     if args.workload == "encode":
         units = T * H_KV * (2 * 256 + 136) + 4 * T
-        value, unit, metric = units / (ms * 1e-3) / 1e9, "GB/s", "cda_paged_encode_k4v4_hbm_gbs"
+        scale, unit, metric = 1e9, "GB/s", "cda_paged_encode_k4v4_hbm_gbs"
         peak, src = measured_peak("hbm_gbs", 6650.0)
-        roof = {"bound": "hbm", "achieved": value, "peak": peak, "unit": unit, "frac": value / peak, "peak_source": src,
-                "traffic": None}
+        bound = "hbm"
     else:
-        units = sum(4 * H_q * 128 * L * (L + 1) // 2 for L in lens)
-        value, unit, metric = units / (ms * 1e-3) / 1e12, "TFLOP/s", "cda_prefill_k4v4_tflops"
+        units = prompt_flops(lens, H_q)
+        scale, unit, metric = 1e12, "TFLOP/s", "cda_prefill_k4v4_tflops"
         peak, src = measured_peak("bf16_tflops", 1590.0)
-        roof = {"bound": "tensor", "achieved": value, "peak": peak, "unit": unit, "frac": value / peak, "peak_source": src,
-                "traffic": None}
-    print(json.dumps({"metric": metric, "value": value, "unit": unit, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
-                      "ms_per_step": ms, "ms_min": min(per), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-                      "dtype": "f16", "data": "synthetic",
-                      "config": {"workload": f"{args.workload} k4v4, 8 prompts of {lens} tokens (T={T}), H_q={H_q} H_kv={H_KV} d=128 block={BLOCK}",
-                                 "timing": "one call per step, CUDA events", "l2": "256 MiB buffer written between steps"},
-                      "roofline": roof, "gpu_launches": args.steps, "clocks": sampler.summary()}))
+        bound = "tensor"
+    value = units / (ms * 1e-3) / scale
+    line = {"metric": metric, "value": value, "unit": unit, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms, "ms_min": min(per), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f16", "data": "synthetic",
+            "config": {"workload": f"{args.workload} k4v4, 8 prompts of {lens} tokens (T={T}), H_q={H_q} H_kv={H_KV} d=128 block={BLOCK}",
+                       "timing": "one call per step, CUDA events", "l2": "256 MiB buffer written between steps"},
+            "roofline": {"bound": bound, "achieved": value, "peak": peak, "unit": unit, "frac": value / peak, "peak_source": src,
+                         "traffic": None},
+            "e2e": {"value": units / (e2e_ms * 1e-3) / scale, "unit": unit, "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h},
+            "gpu_launches": args.steps, "clocks": sampler.summary()}
+
+    # ---- CPU baseline and parity on a bounded sample ----------------------------------------------------------------------------------
+    if not args.no_cpu_baseline:
+        from oracle import cda_oracle as O
+        cores = os.cpu_count() or 1
+        torch.set_num_threads(cores)
+        cbc = cb.cpu()
+        if args.workload == "encode":
+            rows = 4096
+            Kc, Vc = K[:rows].cpu(), V[:rows].cpu()
+            t0 = time.perf_counter()
+            ks, vs = O.encode(Kc, cbc), O.encode(Vc, cbc)
+            t_cpu = time.perf_counter() - t0
+            got_k, got_v = O.unpack_slots(cache.cpu(), slots[:rows].cpu().long())
+            flips = float((got_k.idx != ks.idx).float().mean() + (got_v.idx != vs.idx).float().mean()) / 2
+            line["cpu_baseline"] = {"value": (rows * H_KV * (2 * 256 + 136) + 4 * rows) / t_cpu / 1e9, "unit": unit, "cores": cores,
+                                    "kind": "port", "sample": f"first {rows} of {T} tokens x 8 KV heads, K and V, one pass of the oracle encoder"}
+            line["parity_sample"] = {"ok": flips <= 2e-4, "index_mismatch_fraction": flips, "rows": rows * H_KV * 2,
+                                     "bound": "free-running encoders (rotation summed in different orders): <= 2e-4 of indices"}
+        else:
+            b = min(range(len(lens)), key=lambda i: lens[i])
+            L = lens[b]
+            q0 = int(cu_host[b])
+            head = 0
+            Qs = Q[q0:q0 + L, head * GROUP:(head + 1) * GROUP].cpu()
+            rows_ = bt[b, :blocks_per[b]].long()
+            slot_ids = (rows_[:, None] * BLOCK + torch.arange(BLOCK, device=dev)[None, :]).flatten()[:-(-L // BLOCK) * BLOCK]
+            sub = cache[slot_ids, head:head + 1].cpu()
+            t0 = time.perf_counter()
+            want = O.paged_prefill(Qs, sub, torch.arange(blocks_per[b], dtype=torch.int32)[None], torch.tensor([0, L], dtype=torch.int32),
+                                   torch.tensor([L], dtype=torch.int32), cb_K=cbc, cb_V=cbc, group=GROUP, block_size=BLOCK)
+            t_cpu = time.perf_counter() - t0
+            got = out[q0:q0 + L, head * GROUP:(head + 1) * GROUP].cpu()
+            long_rows = torch.arange(L) + 1 >= 4096
+            bad, worst, max_err = violations(got[long_rows], want[long_rows]) if bool(long_rows.any()) else (0, 0.0, 0.0)
+            cos = float(torch.nn.functional.cosine_similarity(got.float().flatten(), want.float().flatten(), dim=0))
+            line["cpu_baseline"] = {"value": prompt_flops([L], GROUP) / t_cpu / 1e12, "unit": unit, "cores": cores, "kind": "port",
+                                    "sample": f"shortest prompt ({L} tokens), KV head 0 (4 query heads), one pass of the oracle"}
+            line["parity_sample"] = {"ok": bad == 0 and cos >= 0.9999, "violations_rows_with_4096_keys": bad, "cosine": cos,
+                                     "max_abs_err_all_rows": float((got.float() - want.float()).abs().max()), "rows": int(L * GROUP)}
+    print(json.dumps(line))
 
 
 def main():
@@ -487,18 +905,35 @@ def main():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--batch", type=int, default=32)
-    ap.add_argument("--ctx", type=int, default=65536)
+    ap.add_argument("--batch", type=int, default=None)
+    ap.add_argument("--ctx", type=int, default=None)
+    ap.add_argument("--group", type=int, default=None, choices=[1, 2, 4, 8], help="query heads per KV head (8 KV heads)")
+    ap.add_argument("--k-bits", type=int, default=4, choices=[2, 4])
+    ap.add_argument("--v-bits", type=int, default=4, choices=[2, 4])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="decode", choices=["decode", "encode", "prefill"],
-                    help="decode is the headline; encode / prefill time the other two kernels of the path on 8 ragged prompts")
+    ap.add_argument("--no-sustained", action="store_true", help="skip the >= 2 s sustained replay loop")
+    ap.add_argument("--no-identity-order", action="store_true", help="skip the identity-page-order figure")
+    ap.add_argument("--workload", default="decode", choices=["decode", "decode_seqsplit", "encode", "prefill"],
+                    help="decode is the headline; decode_seqsplit = one 1M-token sequence split over the ranks; encode / prefill "
+                         "time the other two kernels of the path on 8 ragged prompts")
     args = ap.parse_args()
-    if args.workload != "decode":
-        if args.impl != "ours" or args.gpus != 1:
-            raise SystemExit("--workload encode/prefill: one GPU, --impl ours only")
-        run_prompt_workload(args)
+    seq = args.workload == "decode_seqsplit"
+    if args.batch is None:
+        args.batch = 1 if seq else 32
+    if args.ctx is None:
+        args.ctx = 1_048_576 if seq else 65536
+    if args.group is None:
+        args.group = 8 if seq else 4
+    if args.workload in ("encode", "prefill"):
+        if args.gpus != 1:
+            raise SystemExit("--workload encode/prefill: one GPU (replicas only)")
+        run_prompt_reference(args) if args.impl == "reference" else run_prompt_workload(args)
     elif args.impl == "reference":
-        run_reference(args)
+        run_reference_decode(args)
+    elif seq:
+        if args.batch != 1 or (args.k_bits, args.v_bits) != (4, 4):
+            raise SystemExit("--workload decode_seqsplit: B=1, k4v4")
+        run_seqsplit(args)
     else:
         run_ours(args)
 

@@ -83,7 +83,9 @@ int cda_b200_quantize_rotated(const float* x_rot, int64_t rows, const float* cb,
  * Replaces hadamard128_fp16(x, y, scale), cda/kernels_cuda/fa2_cda.py:50-53. */
 int cda_b200_hadamard128(const void* x, void* y, int64_t rows, float scale, void* stream);
 
-/* Number of key-range splits the decode entry points use when num_splits == 0 is passed.
+/* Number of partial results per output row (key ranges per sequence) the decode entry points produce when
+ * num_splits == 0 is passed.  The planned decomposition cuts the concatenation of all sequences into equal chunks,
+ * one per SM, so this is the largest number of chunks one sequence touches.
  * Counterpart of the tile heuristic _choose_tile_n, cda/kernels_cuda/wrappers.py:41-76. */
 int cda_b200_decode_plan_splits(int B, int H_kv, int max_seq_len, int device);
 
@@ -105,6 +107,15 @@ int cda_b200_decode(const void* Q, const void* kv_cache, const int32_t* block_ta
                     int64_t num_slots, int slot_bytes, int k_bits, int v_bits, float scale, int num_splits,
                     void* stream);
 
+/* cda_b200_decode that also returns the log-sum-exp of the scaled scores, lse (B, H_q) fp32, natural log
+ * (-inf for a sequence without keys): what an attention backend hands to a cross-rank LSE correction.
+ * The reference backend cannot return it (can_return_lse_for_decode = False, cda_attn_v2.py:621). */
+int cda_b200_decode_lse(const void* Q, const void* kv_cache, const int32_t* block_table, const int32_t* seq_lens,
+                        const float* cb_K, const float* cb_V, void* out, float* lse, void* workspace,
+                        size_t workspace_bytes, int B, int H_q, int H_kv, int block_size, int block_table_stride,
+                        int max_seq_len, int64_t num_slots, int slot_bytes, int k_bits, int v_bits, float scale,
+                        int num_splits, void* stream);
+
 /* Same pass, but returns the un-normalised partial of the keys this cache holds, in the rotated frame:
  * O (B,H_q,128) fp32 = sum exp(s-m) V, m (B,H_q) fp32 = max s (natural-log domain, -inf if no key),
  * l (B,H_q) fp32 = sum exp(s-m).  This is what a sequence-sharded rank contributes.
@@ -116,6 +127,15 @@ int cda_b200_decode_partial(const void* Q, const void* kv_cache, const int32_t* 
                             int block_size, int block_table_stride, int max_seq_len, int64_t num_slots,
                             int slot_bytes, int k_bits, int v_bits, float scale, int num_splits, void* stream);
 
+/* cda_b200_decode_partial writing one packed row per (sequence, query head): packed (B, H_q, 130) fp32 =
+ * 128 un-normalised O values, then m, then l -- a single contiguous message for the all-gather of a
+ * sequence-sharded decode.  packed must be 8-byte aligned.  Same contract as cda_b200_decode_partial. */
+int cda_b200_decode_partial_packed(const void* Q, const void* kv_cache, const int32_t* block_table,
+                                   const int32_t* seq_lens, const float* cb_K, const float* cb_V, float* packed,
+                                   void* workspace, size_t workspace_bytes, int B, int H_q, int H_kv, int block_size,
+                                   int block_table_stride, int max_seq_len, int64_t num_slots, int slot_bytes,
+                                   int k_bits, int v_bits, float scale, int num_splits, void* stream);
+
 /* Merge S partials per row: O (S,R,128), m (S,R), l (S,R) fp32 as produced by cda_b200_decode_partial
  * -> out (R,128) fp16; with unrotate != 0 the merged row is rounded to fp16 and rotated back to the model
  * frame (what decode does), otherwise it stays in the rotated frame.
@@ -123,17 +143,23 @@ int cda_b200_decode_partial(const void* Q, const void* kv_cache, const int32_t* 
 int cda_b200_merge_partials(const float* O, const float* m, const float* l, int S, int64_t R, void* out,
                             int unrotate, void* stream);
 
+/* cda_b200_merge_partials on packed partials (S, R, 130) fp32 as written by cda_b200_decode_partial_packed
+ * (e.g. the all-gathered partials of S ranks).  Follows merge_partials, cda/algorithm/attention.py:239-272. */
+int cda_b200_merge_partials_packed(const float* packed, int S, int64_t R, void* out, int unrotate, void* stream);
+
 /* cda_b200_decode for callers that cannot hand over a workspace: the split-KV scratch is an 8 MiB array compiled into
  * the library (file-scope device memory; every GPU that loads the library holds it until the process exits).  Meant for
  * hosts where device allocation is off limits at call time -- a runtime whose memory pool is fixed at start-up and
  * handed out in full, a plugin that may only touch the buffers it is given, code running while the allocator is
  * locked.  The call itself allocates nothing (no cudaMalloc / cudaFree, no library that allocates): it clears the
  * 256-byte status block with a stream-ordered memset and launches the same two kernels as cda_b200_decode.
- *   num_splits   0 = planned count; whatever is asked, the count is lowered until the partials fit in 8 MiB.
- *   returns      CDA_ERR_WORKSPACE (with the sizes in the message) when even an unsplit pass does not fit, i.e.
- *                when B * H_q * 520 B * (16 / min(H_kv, 8)) + 256 exceeds 8 MiB.
+ *   num_splits   0 = planned decomposition; whatever is asked, the number of partials per row is lowered until they
+ *                fit in 8 MiB.
+ *   returns      CDA_ERR_WORKSPACE (with the sizes in the message) when even one partial per row does not fit, i.e.
+ *                when B * H_q * 520 B + 256 exceeds 8 MiB.
  * The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device current);
- * make that first call outside any stream capture.  All calls share the one array and it keeps the previous call's
+ * make that first call at start-up and outside any stream capture: with lazy module loading that first call is also
+ * when the driver reserves the 8 MiB on that device, so it must come before the host hands out all device memory.  All calls share the one array and it keeps the previous call's
  * contents: calls whose kernels may overlap on the GPU (different streams, or graphs replayed concurrently) race on
  * it -- serialise them or use cda_b200_decode with separate workspaces.
  * Has no counterpart in the reference (its decode kernel allocates its scratch on every call, wrappers.py:97-99). */
@@ -144,13 +170,13 @@ int cda_b200_decode_static(const void* Q, const void* kv_cache, const int32_t* b
 
 /* Slow one-warp-per-query-head decode without tensor cores or splitting; decodes K/V exactly as
  * Compressor.decode does (cb[idx]*norm rounded to fp16).  A device-side cross-check, same arguments
- * and result as cda_b200_decode minus the workspace.  Contract: cda/algorithm/attention.py:426-482. */
+ * and result as cda_b200_decode minus the workspace (out 8-byte aligned).  Contract: cda/algorithm/attention.py:426-482. */
 int cda_b200_decode_scalar(const void* Q, const void* kv_cache, const int32_t* block_table,
                            const int32_t* seq_lens, const float* cb_K, const float* cb_V, void* out, int B,
                            int H_q, int H_kv, int block_size, int block_table_stride, int64_t num_slots,
                            int slot_bytes, int k_bits, int v_bits, float scale, void* stream);
 
-/* Gather + decode every sequence to dense rotated-frame fp16: k_out, v_out (B*max_seq_len, H_kv, 128),
+/* Gather + decode every sequence to dense rotated-frame fp16: k_out, v_out (B*max_seq_len, H_kv, 128), 8-byte aligned,
  * rows at or beyond seq_lens[b] zero.
  * Replaces cda_fa2_paged_cache_to_dense_rotated(kv_cache, block_table, seq_lens, cb_K, cb_V, block_size,
  * max_seq_len), cda/kernels_cuda/fa2_cda.py:86-95 (there the kernel allocates the outputs). */
@@ -163,7 +189,8 @@ int cda_b200_cache_to_dense_rotated(const void* kv_cache, const int32_t* block_t
  * K/V tiles are decoded from the cache into shared memory, the output is rotated back in the epilogue.
  * Query i of sequence b (0 <= i < q_len_b = cu_seqlens_q[b+1]-cu_seqlens_q[b]) attends keys
  * 0 .. seq_lens[b]-q_len_b+i (bottom-right alignment, fa2_cda.py:121-125).
- *   Q, out (T, H_q, 128) fp16      cu_seqlens_q (B+1) int32      seq_lens (B) int32
+ *   Q, out (T, H_q, 128) fp16, 16-byte aligned      cu_seqlens_q (B+1) int32      seq_lens (B) int32
+ * Input errors the kernel meets (out-of-range block ids, q_len > seq_len) are reported by cda_b200_prefill_status().
  * Replaces fa2_cda_prefill_varlen_v1(..., fuse_fa2_epilogue=True), cda/kernels_cuda/fa2_cda.py:98-230,
  * i.e. cda_fa2_paged_cache_to_dense_rotated + cda_fa2_varlen_fwd_hadamard without the dense K/V round
  * trip through HBM; result defined by attention_compressed(causal=True), attention.py:426-482. */
@@ -191,9 +218,24 @@ int cda_b200_dequantize_rows(const void* idx, const float* norm, const float* cb
 
 /* The paged prefill kernel hands tiles between its warps through mbarriers with bounded waits.  A wait that gives up
  * ends its CTA, leaves that CTA's output rows unwritten and sets a per-device flag that makes later prefill CTAs and
- * launches return at once.  Returns 1 if the flag is set on the current device, 0 if not, a negative status on a CUDA
- * error.  Synchronises the device.  (No counterpart in the reference: its kernels report nothing.) */
+ * launches return at once until cda_b200_prefill_clear_status() is called.  Returns 1 if the flag is set on the current
+ * device, 0 if not, a negative status on a CUDA error.  Synchronises the device.  (No counterpart in the reference: its
+ * kernels report nothing.) */
 int cda_b200_prefill_fault(void);
+
+/* What cda_b200_prefill_varlen saw in its inputs on the current device since the last clear (sticky bits; synchronises
+ * the device):  bit 0 (1) a block-table entry was outside the cache and block 0 was read instead;  bit 2 (4) a bounded
+ * wait gave up;  bit 3 (8) a sequence had more new tokens than tokens (q_len > seq_len) and its rows were left unwritten.
+ * Negative status on a CUDA error.  (No counterpart in the reference.) */
+int cda_b200_prefill_status(void);
+
+/* Clear the bits of cda_b200_prefill_status and the flag of cda_b200_prefill_fault on the current device. */
+int cda_b200_prefill_clear_status(void);
+
+/* Diagnostic knobs for the prefill launches that follow in this process: the limit of every in-kernel wait in
+ * microseconds (<= 0: the default, 50 ms) and, if withhold_first_k_arrive != 0, the producers keep back one "tile ready"
+ * signal so that the waits behind it run out -- the way the tests exercise the give-up path without faulting anything. */
+int cda_b200_prefill_debug(int wait_limit_us, int withhold_first_k_arrive);
 
 #ifdef __cplusplus
 }

@@ -6,10 +6,12 @@ back to PyTorch or CPU code.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from pathlib import Path
 
 _PKG = Path(__file__).resolve().parent
-LIB_PATH = _PKG / "libcda_b200.so"
+# $CDA_B200_LIBRARY selects another build of the same library (e.g. one compiled with different tuning constants).
+LIB_PATH = Path(os.environ["CDA_B200_LIBRARY"]) if os.environ.get("CDA_B200_LIBRARY") else _PKG / "libcda_b200.so"
 
 CDA_OK = 0
 CDA_ERR_BAD_ARG, CDA_ERR_BAD_SHAPE, CDA_ERR_BAD_ALIGN, CDA_ERR_UNSUPPORTED = -1, -2, -3, -4
@@ -30,7 +32,12 @@ PROTOTYPES = {
     "cda_b200_decode": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _sz, _i, _i, _i, _i, _i, _i, _i64, _i, _i, _i, _f, _i, _p]),
     "cda_b200_decode_partial": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _sz, _i, _i, _i, _i, _i, _i, _i64, _i,
                                      _i, _i, _f, _i, _p]),
+    "cda_b200_decode_lse": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _sz, _i, _i, _i, _i, _i, _i, _i64, _i, _i, _i, _f, _i,
+                                 _p]),
+    "cda_b200_decode_partial_packed": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _sz, _i, _i, _i, _i, _i, _i, _i64, _i, _i, _i,
+                                            _f, _i, _p]),
     "cda_b200_merge_partials": (_i, [_p, _p, _p, _i, _i64, _p, _i, _p]),
+    "cda_b200_merge_partials_packed": (_i, [_p, _i, _i64, _p, _i, _p]),
     "cda_b200_decode_static": (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i64, _i, _i, _i, _f, _i, _p]),
     "cda_b200_decode_scalar": (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i64, _i, _i, _i, _f, _p]),
     "cda_b200_cache_to_dense_rotated": (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i64, _i, _i, _i, _p]),
@@ -38,6 +45,9 @@ PROTOTYPES = {
                                      _i, _f, _p]),
     "cda_b200_varlen_fwd_hadamard": (_i, [_p, _p, _p, _p, _p, _p, _p, _i64, _i, _i, _i, _i, _i, _f, _p]),
     "cda_b200_prefill_fault": (_i, []),
+    "cda_b200_prefill_status": (_i, []),
+    "cda_b200_prefill_clear_status": (_i, []),
+    "cda_b200_prefill_debug": (_i, [_i, _i]),
     "cda_b200_dequantize_rows": (_i, [_p, _p, _p, _p, _i64, _i, _p]),
 }
 

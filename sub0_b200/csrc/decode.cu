@@ -4,9 +4,14 @@
 // and owns up to 8 KV heads of one key range of one sequence.  A warp owns ONE KV head (and the whole GQA group
 // of query heads that reads it) and walks its share of the range 16 tokens at a time:
 //
-//   HBM -> shared     16-byte cp.async.cg copies of the 16 slots into a per-warp ring of NS stages (NS-1 groups in
-//                     flight per warp; no CTA barrier in the main loop).  Destinations are permuted so that the
-//                     fragment reads below are free of bank conflicts.
+//   HBM -> shared     ONE tensor-map bulk copy (TMA, cp.async.bulk.tensor.2d) per group brings the 16 slots -- a box of
+//                     16 rows x 160 bytes of the cache seen as (slot, bytes of all heads) -- into a per-warp ring of
+//                     NS stages (NS-1 groups in flight per warp, one mbarrier per stage, no CTA barrier in the main
+//                     loop).  The copy engine writes shared memory by itself: the load/store pipe, which the table
+//                     gathers below keep busy, never sees the cache bytes on their way in.  (Issued by the load/store
+//                     pipe as 16-byte cp.async copies, the same bytes cost that pipe about 45 cycles per group on top
+//                     of the ~85 cycles of gathers and fragment reads -- a third of the kernel's time.)  Each slot
+//                     lands in a 160-byte cell, which keeps the fragment reads free of bank conflicts.
 //   codes -> fp16     one shared-memory gather per code: a byte (two 4-bit indices) or nibble (two 2-bit
 //                     indices) selects an fp16 pair from a lane-replicated table, which is exactly one 32-bit
 //                     operand register of mma.m16n8k16.  The table sits on a 64 KB boundary of the shared
@@ -29,6 +34,8 @@
 #include <cmath>
 #include <cstdlib>
 
+#include <cuda.h>   // CUtensorMap and the enums of cuTensorMapEncodeTiled (types only: the entry point is looked up at run time)
+
 #include "common.cuh"
 
 namespace cda {
@@ -45,12 +52,14 @@ struct DecodeParams {
   const float* cb_v;
   float* part_ml;      // (P, B, H_q, 2): m (log2 domain, scale folded in), l
   float* part_o;       // (P, B, H_q, 128)
-  int* status;         // device status word (bit 0: a block id was out of range, bit 1: shared window too small)
+  int* status;         // device status word (bit 0: a block id was out of range, bit 1: shared window too small,
+                       // bit 2: a wait for a cache copy ran out of time)
   int B, H_q, H_kv, group;
   int heads_per_cta;   // power of two <= 8 dividing H_kv
   int block_size, bt_stride, num_blocks;
   int gpb_shift;          // log2(block_size / 16), or -1 when block_size / 16 is not a power of two
-  int tokens_per_split;   // multiple of 16
+  int chunk_groups;       // 16-token groups per chunk of the virtual line of groups (one CTA per chunk and head group)
+  int groups_pad;         // positions of the line owned by each sequence (>= groups of the longest sequence)
   int smem_bytes;         // dynamic shared memory given to the kernel
   float scale_log2;       // softmax scale * log2(e)
 };
@@ -59,12 +68,9 @@ template <int KB, int VB>
 struct Geom {
   static constexpr int kKBytes = 16 * KB;                      // index bytes of one row
   static constexpr int kVBytes = 16 * VB;
-  static constexpr int kChunks = KB + VB + 1;                  // 16-byte pieces per slot
-  static constexpr int kSlotBytes = kChunks * 16;
-  static constexpr int kGroupChunks = 16 * kChunks;
-  static constexpr int kIssueIters = (kGroupChunks + 31) / 32;
-  // A ring stage keeps every slot whole in a 160-byte cell, cells in token order: a copy instruction then writes an
-  // almost contiguous run of shared memory (scattered 16-byte destinations cost one shared-memory cycle each).
+  static constexpr int kSlotBytes = (KB + VB + 1) * 16;
+  // A ring stage keeps every slot whole in a 160-byte cell, cells in token order (the copy box is 160 bytes wide: the
+  // slot and the first bytes of the next head's slot, or zeros past the end of the row).
   // 160 = 32 (mod 128), and accumulator row r is fed by token perm(r) = 0,2,1,3,6,4,7,5: with that pairing the K
   // reads of two rows and the V reads of four rows always fall into different banks.
   static constexpr int kCell = 160;
@@ -99,10 +105,53 @@ __device__ __forceinline__ uint32_t lds_stage4(uint32_t addr) {
   asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(addr), "n"(IMM) : "memory");
   return v;
 }
-template <int IMM>
-__device__ __forceinline__ void cp_async16_imm(uint32_t dst, const uint8_t* src) {
-  asm volatile("cp.async.cg.shared.global [%0+%2], [%1], 16;" ::"r"(dst), "l"(src), "n"(IMM) : "memory");
+
+// ---- tensor-map bulk copies and their mbarriers ------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Wait for the copy of a ring stage, for at most kCopyWaitNs (a copy takes microseconds).  False if the time ran out.
+constexpr unsigned long long kCopyWaitNs = 100ull * 1000 * 1000;
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity) {
+  unsigned long long t0;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  for (uint32_t i = 1;; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 63u) == 0u) {
+      unsigned long long t;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+      if (t - t0 > kCopyWaitNs) return false;
+    }
+  }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity);
+}
+// Box (x .. x+159 bytes of the row, rows y .. y+15) of the cache -> shared memory at dst; completion is counted in bytes
+// on the mbarrier.  x must be a multiple of 16 (it is head * slot_bytes).  No multicast: the source is this GPU's memory
+// and the destination this CTA's shared memory.
+__device__ __forceinline__ void tma_load_group(uint32_t dst, const CUtensorMap* tmap, int x, int y, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+               ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(y)
+               : "memory");
+}
+// Orders this thread's earlier ordinary shared-memory accesses before later writes of the copy engine to the same bytes.
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 // Table entry for the code in byte POS of w: the address is [base.byte3 | base.byte2 | code | base.byte0].
 template <int POS>
@@ -190,14 +239,15 @@ struct WarpCtx {
   float oacc[4][NT][4];
   float m_run[2], l_run[2];
   uint32_t base_k, base_v, sel_b0, sel_b1;
-  uint32_t dst_addr[Gm::kIssueIters];    // window address of this lane's pieces in stage 0
-  int src_off[Gm::kIssueIters];
-  bool last_valid;                        // whether the lane takes part in the last copy iteration
+  uint32_t ring;                          // window address of stage 0 of this warp's ring
+  uint32_t bar;                           // window address of the mbarrier of stage 0 (stage S: + 8 S)
+  uint32_t phases;                        // bit S: parity of the next completion of stage S's mbarrier
+  const CUtensorMap* tmap;
+  int x_bytes;                            // first byte of this warp's head inside a cache row
+  bool leader, dead;                      // lane 0 issues the copies; dead: a wait ran out of time, stop waiting
   uint32_t k_addr, v_addr, v_addr_b, n_addr;   // window addresses of this lane's fragment pieces in stage 0 (V: rows 2c, 2c+1)
-  const uint8_t* cache_head;
   const int32_t* bt_row;
-  int row_stride, block_size, num_blocks, gpb, gpb_shift;
-  uint32_t block_bytes, group_bytes;      // bytes of one cache block / of 16 consecutive slots (all heads)
+  int block_size, num_blocks, gpb, gpb_shift;
   int g_begin_sub, R, ng, t_end, r;
   int tok_r;                              // position inside the group of the token that feeds accumulator row r
   int blk_q;                              // block id of the next group to be issued
@@ -211,7 +261,8 @@ struct WarpCtx {
     blk_q = __ldg(bt_row + block_index(g_begin_sub + R * jj));
   }
 
-  // Start the copies of group j into stage S (nothing if j is past the end); always closes a cp.async group.
+  // Start the copy of group j into stage S (nothing if j is past the end).  Every lane is past its reads of the stage
+  // (the callers put a __syncwarp() between the last read and this call).
   template <int S>
   __device__ __forceinline__ void issue(int j) {
     if (j < ng) {
@@ -219,14 +270,20 @@ struct WarpCtx {
       const bool bad = blk >= static_cast<uint32_t>(num_blocks);   // reported once, when the warp is done
       bad_block |= bad;
       blk = bad ? 0u : blk;
-      const uint8_t* base = cache_head + static_cast<uint64_t>(blk) * block_bytes;
-      if (gpb > 1) base += static_cast<uint32_t>(block_rem(g_begin_sub + R * j)) * group_bytes;
-#pragma unroll
-      for (int it = 0; it < Gm::kIssueIters; ++it)
-        if (it + 1 < Gm::kIssueIters || last_valid) cp_async16_imm<S * Gm::kStageBytes>(dst_addr[it], base + src_off[it]);
+      int y = static_cast<int>(blk) * block_size;                  // first slot of the group
+      if (gpb > 1) y += block_rem(g_begin_sub + R * j) << 4;
+      if (leader) {
+        mbar_expect_tx(bar + 8 * S, Gm::kStageBytes);
+        tma_load_group(ring + S * Gm::kStageBytes, tmap, x_bytes, y, bar + 8 * S);
+      }
       load_block_id(j + 1);
     }
-    cp_async_commit();
+  }
+  // Wait until the copy into stage S has landed.
+  template <int S>
+  __device__ __forceinline__ void wait_stage() {
+    if (!dead && !mbar_wait(bar + 8 * S, (phases >> S) & 1u)) dead = true;
+    phases ^= 1u << S;
   }
 
   template <int S, bool MASKED>
@@ -334,8 +391,7 @@ struct RingSteps {
     const int j = j0 + S;
     if (STEADY || j < cx.ng) {
       cx.template issue<(S + NS - 1) % NS>(j + NS - 1);
-      cp_async_wait<NS - 1>();
-      __syncwarp();
+      cx.template wait_stage<S>();
       if (!STEADY && tail_masked && j == cx.ng - 1) cx.template consume<S, true>(j);
       else cx.template consume<S, false>(j);
       __syncwarp();
@@ -360,9 +416,21 @@ struct RingPrologue<G, KB, VB, NS, NS - 1> {
   __device__ static __forceinline__ void run(WarpCtx<G, KB, VB, NS>&) {}
 };
 
+// One piece of a CTA's chunk: groups [g_lo, g_hi) (16 tokens each) of sequence b, stored as partial `piece` of b.
+struct ChunkItem {
+  int b, g_lo, g_hi, piece;
+};
+
 // G: padded GQA group (4 or 8).  W: warps per CTA.  NS: ring stages per warp.
+//
+// Work decomposition.  Every sequence owns `groups_pad` consecutive positions of a virtual line of 16-token groups
+// (sequence b: positions [b * groups_pad, (b + 1) * groups_pad)), and the line is cut into chunks of `chunk_groups`
+// positions.  CTA (chunk, head group) walks the sequences its chunk touches, one item per sequence: with a chunk size of
+// (all positions / SM count) every SM gets the same number of tokens whatever B and N are, and a chunk that straddles
+// the end of one sequence simply continues with the next.  The partial of item (chunk, b) is row
+// piece = chunk - first chunk of b; pieces a sequence does not reach hold m = -inf.
 template <int G, int KB, int VB, int W, int NS>
-__global__ void __launch_bounds__(W * 32, 1) decode_split_kernel(const DecodeParams p) {
+__global__ void __launch_bounds__(W * 32, 1) decode_split_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap cache_map) {
   using Gm = Geom<KB, VB>;
   using Cfg = DecCfg<W, NS, KB, VB>;
   constexpr int NT = G / 4;
@@ -370,20 +438,12 @@ __global__ void __launch_bounds__(W * 32, 1) decode_split_kernel(const DecodePar
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int r = lane >> 2, c = lane & 3;
-  const int split = blockIdx.x, b = blockIdx.y, hg = blockIdx.z;
   const int hpc = p.heads_per_cta;
   const int R = W / hpc;                 // warps sharing one head (each takes every R-th group)
+  const int chunk = blockIdx.x, hg = blockIdx.y;
   const int head = hg * hpc + (warp & (hpc - 1));
   const int sub = warp / hpc;
   const int g = p.group;
-
-  const int seq_len = p.seq_lens[b];
-  const int t_begin = split * p.tokens_per_split;
-  const int t_end = min(seq_len, t_begin + p.tokens_per_split);   // tokens at or beyond this are masked
-  const int cta_groups = t_end > t_begin ? (t_end - t_begin + 15) >> 4 : 0;
-  const int ng = cta_groups > sub ? (cta_groups - sub + R - 1) / R : 0;   // groups of this warp
-
-  const int64_t prow0 = (static_cast<int64_t>(split) * p.B + b) * p.H_q + head * g;   // partial row of query 0
 
   // ---- shared window layout: warp rings fill the space before the 64 KB-aligned table, the rest follow it -----------
   const uint32_t win0 = smem_addr(smem);
@@ -391,42 +451,92 @@ __global__ void __launch_bounds__(W * 32, 1) decode_split_kernel(const DecodePar
   const int rings_before = static_cast<int>((lut_win - win0) / Cfg::kRingBytes);
   const int rings_after = W > rings_before ? W - rings_before : 0;
   const uint32_t win_end = lut_win + kLutWindow + rings_after * Cfg::kRingBytes;
-  const bool fits = win_end - win0 <= static_cast<uint32_t>(p.smem_bytes);
-  if (cta_groups == 0 || !fits) {   // nothing in range (short sequence) or no room: empty partials, no set-up
-    if (!fits && tid == 0) atomicOr(p.status, 2);
-    if (sub == 0 && lane < g) *reinterpret_cast<float2*>(p.part_ml + (prow0 + lane) * 2) = make_float2(-INFINITY, 0.f);
-    return;
-  }
+  // (the copy engine wants 128-byte aligned destinations: every ring offset is a multiple of 128, so the window must be too)
+  const bool fits = win_end - win0 <= static_cast<uint32_t>(p.smem_bytes) && (win0 & 127u) == 0u;
   const uint32_t ring = warp < rings_before ? win0 + warp * Cfg::kRingBytes
                                             : lut_win + kLutWindow + (warp - rings_before) * Cfg::kRingBytes;
   uint8_t* lut = smem + (lut_win - win0);
 
-  // ---- this warp's view of the cache; start the first copies so that their latency hides behind the set-up ------------
+  // ---- the chunk's items -------------------------------------------------------------------------------------------------
+  // The item of sequence b in this chunk, or false if the chunk ends before b.  Identical in every thread (depends on
+  // the launch parameters only); everything is recomputed from b so that only b stays live across the key loop.
+  auto item_of = [&](int b, ChunkItem& it) -> bool {
+    const int64_t pos_lo = static_cast<int64_t>(blockIdx.x) * p.chunk_groups, pos_hi = pos_lo + p.chunk_groups;
+    const int64_t base = static_cast<int64_t>(b) * p.groups_pad;
+    if (b >= p.B || base >= pos_hi) return false;
+    it.b = b;
+    it.g_lo = static_cast<int>(pos_lo > base ? pos_lo - base : 0);
+    const int64_t hi = pos_hi - base;
+    it.g_hi = hi < p.groups_pad ? static_cast<int>(hi) : p.groups_pad;
+    it.piece = static_cast<int>(blockIdx.x) - static_cast<int>(base / p.chunk_groups);
+    return true;
+  };
+  // An item without tokens (short sequence) or a CTA without room: empty partial rows for every head of the CTA.
+  auto write_empty = [&](const ChunkItem& it) {
+    const int rows = hpc * g;
+    const int64_t prow_cta = (static_cast<int64_t>(it.piece) * p.B + it.b) * p.H_q + hg * hpc * g;
+    for (int i = tid; i < rows; i += W * 32) *reinterpret_cast<float2*>(p.part_ml + (prow_cta + i) * 2) = make_float2(-INFINITY, 0.f);
+  };
+
+  __shared__ __align__(8) unsigned long long s_bar[W * NS];   // one mbarrier per warp and ring stage
   WarpCtx<G, KB, VB, NS> cx;
-  cx.row_stride = p.H_kv * Gm::kSlotBytes;
+  cx.ring = ring;
+  cx.bar = smem_addr(s_bar) + warp * (8 * NS);
+  cx.phases = 0u;
+  cx.tmap = &cache_map;
+  cx.x_bytes = head * Gm::kSlotBytes;
+  cx.leader = lane == 0;
+  cx.dead = false;
+  if (cx.leader) {                       // only this warp ever touches its barriers: lane 0 arrives, all lanes wait
 #pragma unroll
-  for (int it = 0; it < Gm::kIssueIters; ++it) {
-    int ch = it * 32 + lane;
-    if (ch >= Gm::kGroupChunks) ch = Gm::kGroupChunks - 1;
-    const int rho = ch / Gm::kChunks, piece = ch - rho * Gm::kChunks;
-    cx.src_off[it] = rho * cx.row_stride + piece * 16;
-    cx.dst_addr[it] = ring + rho * Gm::kCell + piece * 16;
+    for (int st = 0; st < NS; ++st) mbar_init(cx.bar + 8 * st, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    fence_proxy_async();
   }
-  cx.last_valid = (Gm::kIssueIters - 1) * 32 + lane < Gm::kGroupChunks;
+  __syncwarp();
   cx.k_addr = ring + stage_perm(r) * Gm::kCell + c * (4 * KB);
   cx.v_addr = ring + stage_perm(2 * c) * Gm::kCell + 16 * KB + r * (2 * VB);
   cx.v_addr_b = ring + stage_perm(2 * c + 1) * Gm::kCell + 16 * KB + r * (2 * VB);
   cx.n_addr = ring + stage_perm(r) * Gm::kCell + 16 * KB + 16 * VB;
-  cx.cache_head = p.cache + static_cast<int64_t>(head) * Gm::kSlotBytes;
-  cx.bt_row = p.block_table + static_cast<int64_t>(b) * p.bt_stride;
   cx.block_size = p.block_size; cx.num_blocks = p.num_blocks;
   cx.gpb = p.block_size >> 4; cx.gpb_shift = p.gpb_shift;
-  cx.block_bytes = static_cast<uint32_t>(p.block_size) * cx.row_stride; cx.group_bytes = 16u * cx.row_stride;
-  cx.g_begin_sub = (t_begin >> 4) + sub; cx.R = R; cx.ng = ng; cx.t_end = t_end; cx.r = r; cx.tok_r = stage_perm(r);
+  cx.R = R; cx.r = r; cx.tok_r = stage_perm(r);
   cx.bad_block = false;
-  if (ng > 0) {
-    cx.load_block_id(0);
-    RingPrologue<G, KB, VB, NS, 0>::run(cx);   // stages 0 .. NS-2; stage NS-1 is free until the first turn of the ring
+
+  // Point the warp at an item and start its first copies (stages 0 .. NS-2; stage NS-1 stays free until the first turn
+  // of the ring).  Returns the number of 16-token groups of the whole CTA in the item (0: nothing to read).
+  int t_begin = 0, t_end = 0;
+  auto begin_item = [&](const ChunkItem& it) -> int {
+    const int seq_len = p.seq_lens[it.b];
+    t_begin = it.g_lo << 4;
+    t_end = min(seq_len, it.g_hi << 4);                           // tokens at or beyond this are masked
+    const int cta_groups = t_end > t_begin ? (t_end - t_begin + 15) >> 4 : 0;
+    cx.ng = cta_groups > sub ? (cta_groups - sub + R - 1) / R : 0;   // groups of this warp
+    cx.bt_row = p.block_table + static_cast<int64_t>(it.b) * p.bt_stride;
+    cx.g_begin_sub = it.g_lo + sub; cx.t_end = t_end;
+    if (cx.ng > 0) {
+      cx.load_block_id(0);
+      RingPrologue<G, KB, VB, NS, 0>::run(cx);
+    }
+    return cta_groups;
+  };
+
+  int b_cur = static_cast<int>(static_cast<int64_t>(chunk) * p.chunk_groups / p.groups_pad);
+  int cta_groups = 0;
+  {
+    ChunkItem item;
+    bool have = item_of(b_cur, item);
+    if (!fits) {                      // no room for the table and the rings: report it, leave well-formed empty partials
+      if (tid == 0) atomicOr(p.status, 2);
+      for (; have; have = item_of(++b_cur, item)) write_empty(item);
+      return;
+    }
+    for (; have; have = item_of(++b_cur, item)) {   // leading items without tokens need no set-up at all
+      cta_groups = begin_item(item);
+      if (cta_groups > 0) break;
+      write_empty(item);
+    }
+    if (!have) return;
   }
 
   __shared__ float s_err[64];
@@ -449,35 +559,6 @@ __global__ void __launch_bounds__(W * 32, 1) decode_split_kernel(const DecodePar
       if (e < EV) lw[e * 64 + 32 + lane] = wv;
     }
   }
-
-  // ---- rotate this head's queries, stage them as fp16 rows in the last stage of this warp's ring, pick up the B fragments --
-  {
-    __half* q_rows = reinterpret_cast<__half*>(smem + (ring - win0) + (NS - 1) * Gm::kStageBytes);
-    static_assert(8 * kHeadDim * 2 <= Gm::kStageBytes, "eight fp16 query rows must fit one ring stage");
-    float qv[G][4];
-#pragma unroll
-    for (int qi = 0; qi < G; ++qi) {
-      qv[qi][0] = qv[qi][1] = qv[qi][2] = qv[qi][3] = 0.f;
-      if (qi < g) load_half4(p.q + (static_cast<int64_t>(b) * p.H_q + head * g + qi) * kHeadDim + 4 * lane, qv[qi]);
-    }
-#pragma unroll
-    for (int qi = 0; qi < G; ++qi) {
-      fht128_warp(qv[qi], lane);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) qv[qi][i] *= kRsqrtD;
-      *reinterpret_cast<uint2*>(q_rows + qi * kHeadDim + 4 * lane) = pack_half4(qv[qi]);
-    }
-    __syncwarp();
-    const int qrow = G == 4 ? (r & 3) : r;   // column r: query r, or r & 3 when the group is padded to 4
-    const uint4* src = reinterpret_cast<const uint4*>(q_rows + qrow * kHeadDim + 32 * c);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const uint4 t = src[i];
-      cx.qf[4 * i] = t.x; cx.qf[4 * i + 1] = t.y; cx.qf[4 * i + 2] = t.z; cx.qf[4 * i + 3] = t.w;
-    }
-  }
-  __syncthreads();   // tables visible to every warp; every lane is done with its query rows
-
   cx.base_k = lut_win | (lane << 2);
   cx.base_v = cx.base_k | 128u;
   {   // operand placement of the probabilities: even columns take the low half, odd columns the high half
@@ -486,143 +567,225 @@ __global__ void __launch_bounds__(W * 32, 1) decode_split_kernel(const DecodePar
     cx.sel_b1 = odd ? 0x3244u : 0x4432u;
   }
   cx.scale_log2 = p.scale_log2 * alpha_k;
-  cx.m_run[0] = cx.m_run[1] = kMinusBig;
-  cx.l_run[0] = cx.l_run[1] = 0.f;
-#pragma unroll
-  for (int u = 0; u < 4; ++u)
-#pragma unroll
-    for (int t = 0; t < NT; ++t)
-#pragma unroll
-      for (int i = 0; i < 4; ++i) cx.oacc[u][t][i] = 0.f;
 
-  if (ng > 0) {
-    const bool tail_masked = ((t_end - t_begin) & 15) != 0 && (cta_groups - 1) % R == sub;
-    int j0 = 0;
-    const int steady_end = ng - (tail_masked ? 1 : 0);
-#pragma unroll 1
-    for (; j0 + NS <= steady_end; j0 += NS) RingSteps<G, KB, VB, NS, 0, true>::run(cx, j0, false);
-#pragma unroll 1
-    for (; j0 < ng; j0 += NS) RingSteps<G, KB, VB, NS, 0, false>::run(cx, j0, tail_masked);
-    if (cx.bad_block) atomicOr(p.status, 1);
-  }
-  cp_async_wait<0>();   // also the copies a warp without groups started above
-  __syncwarp();         // every lane is done reading the ring before it is reused below
-
-  // ---- combine the partials of the warps that share a head, write one partial per (split, head) ----------------------------
-  float l0 = cx.l_run[0], l1 = cx.l_run[1];
-#pragma unroll
-  for (int mask = 4; mask < 32; mask <<= 1) {
-    l0 += __shfl_xor_sync(0xffffffffu, l0, mask);
-    l1 += __shfl_xor_sync(0xffffffffu, l1, mask);
-  }
-  const float m0 = l0 > 0.f ? cx.m_run[0] : -INFINITY, m1 = l1 > 0.f ? cx.m_run[1] : -INFINITY;
-  // every warp parks (O[q][128], m[q], l[q]) for its G query rows in its own ring: rows of 132 floats
-  constexpr int kRowFloats = kHeadDim + 4;   // 528-byte rows keep the 16-byte reads aligned
+  constexpr int kRowFloats = kHeadDim + 4;   // parked partial rows: 528 bytes keep the 16-byte reads aligned
   static_assert(G * kRowFloats * 4 <= Cfg::kRingBytes, "a warp's partial must fit its ring");
   auto ring_of = [&](int w) -> float* {
     const uint32_t a = w < rings_before ? win0 + w * Cfg::kRingBytes : lut_win + kLutWindow + (w - rings_before) * Cfg::kRingBytes;
     return reinterpret_cast<float*>(smem + (a - win0));
   };
-  {
-    float* st = ring_of(warp);
-    if (G == 4) {
-      const int parity = c >> 1, q0 = 2 * (c & 1);
+
+  for (;;) {   // one turn per item with tokens; the copies of its first groups are already in flight
+    // ---- rotate this head's queries, stage them as fp16 rows in the last stage of this warp's ring, pick up the B fragments --
+    {
+      const int b = b_cur;
+      __half* q_rows = reinterpret_cast<__half*>(smem + (ring - win0) + (NS - 1) * Gm::kStageBytes);
+      static_assert(8 * kHeadDim * 2 <= Gm::kStageBytes, "eight fp16 query rows must fit one ring stage");
+      float qv[G][4];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int d = 16 * r + 4 * u + parity;
-        st[q0 * kRowFloats + d] = cx.oacc[u][0][0] * alpha_v; st[q0 * kRowFloats + d + 2] = cx.oacc[u][0][2] * alpha_v;
-        st[(q0 + 1) * kRowFloats + d] = cx.oacc[u][0][1] * alpha_v; st[(q0 + 1) * kRowFloats + d + 2] = cx.oacc[u][0][3] * alpha_v;
+      for (int qi = 0; qi < G; ++qi) {
+        qv[qi][0] = qv[qi][1] = qv[qi][2] = qv[qi][3] = 0.f;
+        if (qi < g) load_half4(p.q + (static_cast<int64_t>(b) * p.H_q + head * g + qi) * kHeadDim + 4 * lane, qv[qi]);
       }
-      if (r == 0 && c < 2) {
-        st[q0 * kRowFloats + kHeadDim] = m0; st[q0 * kRowFloats + kHeadDim + 1] = l0;
-        st[(q0 + 1) * kRowFloats + kHeadDim] = m1; st[(q0 + 1) * kRowFloats + kHeadDim + 1] = l1;
+#pragma unroll
+      for (int qi = 0; qi < G; ++qi) {
+        fht128_warp(qv[qi], lane);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) qv[qi][i] *= kRsqrtD;
+        *reinterpret_cast<uint2*>(q_rows + qi * kHeadDim + 4 * lane) = pack_half4(qv[qi]);
       }
-    } else {
-      const int q0 = 2 * c;
+      __syncwarp();
+      const int qrow = G == 4 ? (r & 3) : r;   // column r: query r, or r & 3 when the group is padded to 4
+      const uint4* src = reinterpret_cast<const uint4*>(q_rows + qrow * kHeadDim + 32 * c);
 #pragma unroll
-      for (int u = 0; u < 4; ++u)
+      for (int i = 0; i < 4; ++i) {
+        const uint4 t = src[i];
+        cx.qf[4 * i] = t.x; cx.qf[4 * i + 1] = t.y; cx.qf[4 * i + 2] = t.z; cx.qf[4 * i + 3] = t.w;
+      }
+      fence_proxy_async();   // the stage that held the query rows is written by the copy engine next
+    }
+    __syncthreads();   // first turn: tables visible to every warp; every turn: every lane is done with its query rows
+
+    cx.m_run[0] = cx.m_run[1] = kMinusBig;
+    cx.l_run[0] = cx.l_run[1] = 0.f;
 #pragma unroll
-        for (int t = 0; t < NT; ++t) {
-          const int d = 16 * r + 4 * u + t;
-          st[q0 * kRowFloats + d] = cx.oacc[u][t][0] * alpha_v; st[q0 * kRowFloats + d + 2] = cx.oacc[u][t][2] * alpha_v;
-          st[(q0 + 1) * kRowFloats + d] = cx.oacc[u][t][1] * alpha_v; st[(q0 + 1) * kRowFloats + d + 2] = cx.oacc[u][t][3] * alpha_v;
+    for (int u = 0; u < 4; ++u)
+#pragma unroll
+      for (int t = 0; t < NT; ++t)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) cx.oacc[u][t][i] = 0.f;
+
+    const int ng = cx.ng;
+    if (ng > 0) {
+      const bool tail_masked = ((t_end - t_begin) & 15) != 0 && (cta_groups - 1) % R == sub;
+      int j0 = 0;
+      const int steady_end = ng - (tail_masked ? 1 : 0);
+#pragma unroll 1
+      for (; j0 + NS <= steady_end; j0 += NS) RingSteps<G, KB, VB, NS, 0, true>::run(cx, j0, false);
+#pragma unroll 1
+      for (; j0 < ng; j0 += NS) RingSteps<G, KB, VB, NS, 0, false>::run(cx, j0, tail_masked);
+    }
+    __syncwarp();         // every lane is done reading the ring before it is reused below (no copy is in flight: every
+                          // group that was requested has been waited for and consumed)
+
+    // ---- combine the partials of the warps that share a head, write one partial per (piece, head) ------------------------------
+    float l0 = cx.l_run[0], l1 = cx.l_run[1];
+#pragma unroll
+    for (int mask = 4; mask < 32; mask <<= 1) {
+      l0 += __shfl_xor_sync(0xffffffffu, l0, mask);
+      l1 += __shfl_xor_sync(0xffffffffu, l1, mask);
+    }
+    const float m0 = l0 > 0.f ? cx.m_run[0] : -INFINITY, m1 = l1 > 0.f ? cx.m_run[1] : -INFINITY;
+    // every warp parks (O[q][128], m[q], l[q]) for its G query rows in its own ring: rows of 132 floats
+    {
+      float* st = ring_of(warp);
+      if (G == 4) {
+        const int parity = c >> 1, q0 = 2 * (c & 1);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int d = 16 * r + 4 * u + parity;
+          st[q0 * kRowFloats + d] = cx.oacc[u][0][0] * alpha_v; st[q0 * kRowFloats + d + 2] = cx.oacc[u][0][2] * alpha_v;
+          st[(q0 + 1) * kRowFloats + d] = cx.oacc[u][0][1] * alpha_v; st[(q0 + 1) * kRowFloats + d + 2] = cx.oacc[u][0][3] * alpha_v;
         }
-      if (r == 0) {
-        st[q0 * kRowFloats + kHeadDim] = m0; st[q0 * kRowFloats + kHeadDim + 1] = l0;
-        st[(q0 + 1) * kRowFloats + kHeadDim] = m1; st[(q0 + 1) * kRowFloats + kHeadDim + 1] = l1;
+        if (r == 0 && c < 2) {
+          st[q0 * kRowFloats + kHeadDim] = m0; st[q0 * kRowFloats + kHeadDim + 1] = l0;
+          st[(q0 + 1) * kRowFloats + kHeadDim] = m1; st[(q0 + 1) * kRowFloats + kHeadDim + 1] = l1;
+        }
+      } else {
+        const int q0 = 2 * c;
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+#pragma unroll
+          for (int t = 0; t < NT; ++t) {
+            const int d = 16 * r + 4 * u + t;
+            st[q0 * kRowFloats + d] = cx.oacc[u][t][0] * alpha_v; st[q0 * kRowFloats + d + 2] = cx.oacc[u][t][2] * alpha_v;
+            st[(q0 + 1) * kRowFloats + d] = cx.oacc[u][t][1] * alpha_v; st[(q0 + 1) * kRowFloats + d + 2] = cx.oacc[u][t][3] * alpha_v;
+          }
+        if (r == 0) {
+          st[q0 * kRowFloats + kHeadDim] = m0; st[q0 * kRowFloats + kHeadDim + 1] = l0;
+          st[(q0 + 1) * kRowFloats + kHeadDim] = m1; st[(q0 + 1) * kRowFloats + kHeadDim + 1] = l1;
+        }
       }
     }
-  }
-  __syncthreads();
-  // (head, query row) pairs are dealt over all warps; lane s < R holds the (m, l) of the head's s-th warp, lane l adds
-  // up coordinates 4l .. 4l+3 of the row
-  const int items = hpc * g;
-  const int64_t prow_cta = (static_cast<int64_t>(split) * p.B + b) * p.H_q + hg * hpc * g;
-  for (int it = warp; it < items; it += W) {
-    const int hh = it & (hpc - 1), q = it / hpc;
-    float ms = -INFINITY, ls = 0.f;
-    if (lane < R) {
-      const float2 ml = *reinterpret_cast<const float2*>(ring_of(hh + lane * hpc) + q * kRowFloats + kHeadDim);
-      ms = ml.x; ls = ml.y;
-    }
-    float mt = ms;
+    __syncthreads();
+    // (head, query row) pairs are dealt over all warps; lane s < R holds the (m, l) of the head's s-th warp, lane l adds
+    // up coordinates 4l .. 4l+3 of the row
+    const int items = hpc * g;
+    ChunkItem item;
+    item_of(b_cur, item);
+    const int64_t prow_cta = (static_cast<int64_t>(item.piece) * p.B + item.b) * p.H_q + hg * hpc * g;
+    for (int it = warp; it < items; it += W) {
+      const int hh = it & (hpc - 1), q = it / hpc;
+      float ms = -INFINITY, ls = 0.f;
+      if (lane < R) {
+        const float2 ml = *reinterpret_cast<const float2*>(ring_of(hh + lane * hpc) + q * kRowFloats + kHeadDim);
+        ms = ml.x; ls = ml.y;
+      }
+      float mt = ms;
 #pragma unroll
-    for (int mask = 1; mask < 32; mask <<= 1) mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, mask));
-    const float wgt = ms == -INFINITY ? 0.f : fast_exp2(ms - mt);
-    const float lt = warp_sum(ls * wgt);
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int mask = 1; mask < 32; mask <<= 1) mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, mask));
+      const float wgt = ms == -INFINITY ? 0.f : fast_exp2(ms - mt);
+      const float lt = warp_sum(ls * wgt);
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 4
-    for (int s2 = 0; s2 < R; ++s2) {
-      const float w2 = __shfl_sync(0xffffffffu, wgt, s2);
-      const float4 o = *reinterpret_cast<const float4*>(ring_of(hh + s2 * hpc) + q * kRowFloats + 4 * lane);
-      acc.x += o.x * w2; acc.y += o.y * w2; acc.z += o.z * w2; acc.w += o.w * w2;
+      for (int s2 = 0; s2 < R; ++s2) {
+        const float w2 = __shfl_sync(0xffffffffu, wgt, s2);
+        const float4 o = *reinterpret_cast<const float4*>(ring_of(hh + s2 * hpc) + q * kRowFloats + 4 * lane);
+        acc.x += o.x * w2; acc.y += o.y * w2; acc.z += o.z * w2; acc.w += o.w * w2;
+      }
+      const int64_t prow = prow_cta + hh * g + q;
+      *reinterpret_cast<float4*>(p.part_o + prow * kHeadDim + 4 * lane) = acc;
+      if (lane == 0) *reinterpret_cast<float2*>(p.part_ml + prow * 2) = make_float2(mt, lt);
     }
-    const int64_t prow = prow_cta + hh * g + q;
-    *reinterpret_cast<float4*>(p.part_o + prow * kHeadDim + 4 * lane) = acc;
-    if (lane == 0) *reinterpret_cast<float2*>(p.part_ml + prow * 2) = make_float2(mt, lt);
+
+    // ---- next item with tokens of this chunk, if any ---------------------------------------------------------------------
+    bool have = item_of(++b_cur, item);
+    for (; have; have = item_of(++b_cur, item)) {
+      if (p.seq_lens[item.b] > (item.g_lo << 4)) break;
+      write_empty(item);
+    }
+    if (!have) break;
+    fence_proxy_async();
+    __syncthreads();   // the parked partials have been read: the rings are free again
+    cta_groups = begin_item(item);
   }
+  if (cx.bad_block) atomicOr(p.status, 1);
+  if (cx.dead && lane == 0) atomicOr(p.status, 4);
 }
 
 // ---- merge --------------------------------------------------------------------------------------------------
+// Inputs: P partial rows per output row, partial pi of row `row` at index pi * rows + row; O rows o_stride floats apart
+// (128 for the split kernel's workspace, 130 for packed partials whose columns 128 / 129 hold m / l), m and l read at
+// (index * ml_stride).  m values are multiplied by `m_to_log2` on load (1 for the split kernel's own partials, log2(e)
+// for natural-log partials supplied through the C ABI).
+// mode 0: normalise, round to fp16, optional inverse Hadamard, store fp16 (and log-sum-exp if asked).
+// mode 1: store the merged un-normalised partial as fp32: O at out_o + row * out_o_stride, m (natural log) and l at
+//         out_m / out_l + row * out_ml_stride.
+// When chunk_groups > 0 the partials come from decode_split_kernel and row r (sequence r / rows_per_seq) owns only the
+// pieces its sequence's positions touch; pieces beyond that were never written and are not read.
+struct MergeParams {
+  const float* part_o; const float* part_m; const float* part_l;
+  int ml_stride, o_stride, P;
+  int64_t rows;
+  float m_to_log2;
+  int mode, unrotate;
+  __half* out; float* out_lse;
+  float* out_o; float* out_m; float* out_l;
+  int out_o_stride, out_ml_stride;
+  int rows_per_seq, chunk_groups, groups_pad;
+};
+
+__device__ __forceinline__ int merge_valid_parts(const MergeParams& q, int64_t row) {
+  if (q.chunk_groups <= 0) return q.P;
+  const int64_t lo = (row / q.rows_per_seq) * q.groups_pad;
+  const int n = static_cast<int>((lo + q.groups_pad - 1) / q.chunk_groups - lo / q.chunk_groups + 1);
+  return n < q.P ? n : q.P;
+}
+__device__ __forceinline__ float4 merge_load4(const float* ptr, bool vec4) {
+  if (vec4) return *reinterpret_cast<const float4*>(ptr);
+  const float2 a = *reinterpret_cast<const float2*>(ptr), b = *reinterpret_cast<const float2*>(ptr + 2);
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+
 // Last step of a merge: lane l holds coordinates 4l .. 4l+3 of the summed row, every lane the row's l and maximum.
-__device__ __forceinline__ void merge_finish(const float (&ot)[4], float lt, float mt, int64_t row, int lane, int mode,
-                                             int unrotate, __half* __restrict__ out, float* __restrict__ out_o,
-                                             float* __restrict__ out_m, float* __restrict__ out_l) {
-  if (mode == 1) {
-    *reinterpret_cast<float4*>(out_o + row * kHeadDim + 4 * lane) = make_float4(ot[0], ot[1], ot[2], ot[3]);
-    if (lane == 0) { out_m[row] = mt == -INFINITY ? -INFINITY : mt * kLn2; out_l[row] = lt; }
+__device__ __forceinline__ void merge_finish(const MergeParams& q, const float (&ot)[4], float lt, float mt, int64_t row, int lane) {
+  if (q.mode == 1) {
+    float* dst = q.out_o + row * q.out_o_stride + 4 * lane;
+    if ((q.out_o_stride & 3) == 0) *reinterpret_cast<float4*>(dst) = make_float4(ot[0], ot[1], ot[2], ot[3]);
+    else { *reinterpret_cast<float2*>(dst) = make_float2(ot[0], ot[1]); *reinterpret_cast<float2*>(dst + 2) = make_float2(ot[2], ot[3]); }
+    if (lane == 0) {
+      q.out_m[row * q.out_ml_stride] = mt == -INFINITY ? -INFINITY : mt * kLn2;
+      q.out_l[row * q.out_ml_stride] = lt;
+    }
     return;
   }
   const float inv = 1.0f / fmaxf(lt, 1e-30f);   // merge_partials clamps the denominator (attention.py:271)
   float v[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) v[i] = round_to_half(ot[i] * inv);   // the oracle rounds O_rot to fp16 before un-rotating
-  if (unrotate) {
+  if (q.unrotate) {
     fht128_warp(v, lane);
 #pragma unroll
     for (int i = 0; i < 4; ++i) v[i] *= kRsqrtD;
   }
-  *reinterpret_cast<uint2*>(out + row * kHeadDim + 4 * lane) = pack_half4(v);
+  *reinterpret_cast<uint2*>(q.out + row * kHeadDim + 4 * lane) = pack_half4(v);
+  if (q.out_lse != nullptr && lane == 0) q.out_lse[row] = (mt == -INFINITY || !(lt > 0.f)) ? -INFINITY : mt * kLn2 + logf(lt);
 }
 
 // One CTA (16 warps) per output row.  A first pass over the (m) column finds the row's maximum; then warp w sums
 // partials w, w+16, ... weighted by exp2(m_p - max), four at a time so that their loads are in flight together,
-// and the sixteen warp sums are added through shared memory.  m values are multiplied by `m_to_log2` on load (1 for
-// the split kernel's own partials, log2(e) for natural-log partials supplied through the C ABI).
-// mode 0: normalise, round to fp16, optional inverse Hadamard, store fp16.
-// mode 1: store the merged un-normalised partial as fp32 (O, m in natural log, l).
+// and the sixteen warp sums are added through shared memory.
 constexpr int kMergeWarps = 16, kMergeUnroll = 4;
-__global__ void __launch_bounds__(kMergeWarps * 32) decode_merge_kernel(
-    const float* __restrict__ part_o, const float* __restrict__ part_m, const float* __restrict__ part_l, int ml_stride, int P,
-    int64_t rows, float m_to_log2, int mode, int unrotate, __half* __restrict__ out, float* __restrict__ out_o,
-    float* __restrict__ out_m, float* __restrict__ out_l) {
+__global__ void __launch_bounds__(kMergeWarps * 32) decode_merge_kernel(const MergeParams q) {
   __shared__ float s_o[kMergeWarps][kHeadDim];
   __shared__ float s_l[kMergeWarps], s_max[kMergeWarps];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int64_t row = blockIdx.x;
+  const int64_t row = blockIdx.x, rows = q.rows;
+  const int P = merge_valid_parts(q, row);
+  const bool vec4 = (q.o_stride & 3) == 0;
   float mx = -INFINITY;
   for (int pi = threadIdx.x; pi < P; pi += kMergeWarps * 32)
-    mx = fmaxf(mx, part_m[(static_cast<int64_t>(pi) * rows + row) * ml_stride]);
+    mx = fmaxf(mx, q.part_m[(static_cast<int64_t>(pi) * rows + row) * q.ml_stride]);
 #pragma unroll
   for (int mask = 16; mask > 0; mask >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, mask));
   if (lane == 0) s_max[warp] = mx;
@@ -630,7 +793,7 @@ __global__ void __launch_bounds__(kMergeWarps * 32) decode_merge_kernel(
   float mt = -INFINITY;
 #pragma unroll
   for (int w = 0; w < kMergeWarps; ++w) mt = fmaxf(mt, s_max[w]);
-  mt *= m_to_log2;                                   // the factor is positive: the maximum stays the maximum
+  mt *= q.m_to_log2;                                 // the factor is positive: the maximum stays the maximum
   const float ms = mt == -INFINITY ? 0.f : mt;
 
   float l = 0.f, o[4] = {0.f, 0.f, 0.f, 0.f};
@@ -642,14 +805,14 @@ __global__ void __launch_bounds__(kMergeWarps * 32) decode_merge_kernel(
       const int pi = base + u * kMergeWarps;
       const bool valid = pi < P;
       const int64_t pr = static_cast<int64_t>(valid ? pi : base) * rows + row;
-      mp[u] = valid ? part_m[pr * ml_stride] : -INFINITY;
-      lp[u] = part_l[pr * ml_stride];
-      op[u] = *reinterpret_cast<const float4*>(part_o + pr * kHeadDim + 4 * lane);
+      mp[u] = valid ? q.part_m[pr * q.ml_stride] : -INFINITY;
+      lp[u] = q.part_l[pr * q.ml_stride];
+      op[u] = merge_load4(q.part_o + pr * q.o_stride + 4 * lane, vec4);
     }
 #pragma unroll
     for (int u = 0; u < kMergeUnroll; ++u) {
       if (mp[u] == -INFINITY) continue;              // empty range: its O row was never written, do not touch it
-      const float bw = fast_exp2(mp[u] * m_to_log2 - ms);
+      const float bw = fast_exp2(mp[u] * q.m_to_log2 - ms);
       l += lp[u] * bw;
       o[0] += op[u].x * bw; o[1] += op[u].y * bw; o[2] += op[u].z * bw; o[3] += op[u].w * bw;
     }
@@ -665,24 +828,23 @@ __global__ void __launch_bounds__(kMergeWarps * 32) decode_merge_kernel(
     const float4 t = *reinterpret_cast<const float4*>(&s_o[w][4 * lane]);
     ot[0] += t.x; ot[1] += t.y; ot[2] += t.z; ot[3] += t.w;
   }
-  merge_finish(ot, lt, mt, row, lane, mode, unrotate, out, out_o, out_m, out_l);
+  merge_finish(q, ot, lt, mt, row, lane);
 }
 
 // Merge of at most 32 partials per row: one warp per row, no shared memory.  Lane p holds (m, l) of partial p; the O
 // rows are read eight at a time.
 constexpr int kMergeSmallRows = 4, kMergeSmallMaxP = 32;
-__global__ void __launch_bounds__(kMergeSmallRows * 32) decode_merge_small_kernel(
-    const float* __restrict__ part_o, const float* __restrict__ part_m, const float* __restrict__ part_l, int ml_stride, int P,
-    int64_t rows, float m_to_log2, int mode, int unrotate, __half* __restrict__ out, float* __restrict__ out_o,
-    float* __restrict__ out_m, float* __restrict__ out_l) {
+__global__ void __launch_bounds__(kMergeSmallRows * 32) decode_merge_small_kernel(const MergeParams q) {
   const int lane = threadIdx.x & 31;
-  const int64_t row = static_cast<int64_t>(blockIdx.x) * kMergeSmallRows + (threadIdx.x >> 5);
+  const int64_t rows = q.rows, row = static_cast<int64_t>(blockIdx.x) * kMergeSmallRows + (threadIdx.x >> 5);
   if (row >= rows) return;
+  const int P = merge_valid_parts(q, row);
+  const bool vec4 = (q.o_stride & 3) == 0;
   float mp = -INFINITY, lp = 0.f;
   if (lane < P) {
     const int64_t pr = static_cast<int64_t>(lane) * rows + row;
-    mp = part_m[pr * ml_stride] * m_to_log2;
-    lp = part_l[pr * ml_stride];
+    mp = q.part_m[pr * q.ml_stride] * q.m_to_log2;
+    lp = q.part_l[pr * q.ml_stride];
   }
   float mt = mp;
 #pragma unroll
@@ -697,7 +859,7 @@ __global__ void __launch_bounds__(kMergeSmallRows * 32) decode_merge_small_kerne
     for (int u = 0; u < 8; ++u) {
       const int pi = base + u < P ? base + u : base;
       w8[u] = base + u < P ? __shfl_sync(0xffffffffu, bw, pi) : 0.f;
-      op[u] = *reinterpret_cast<const float4*>(part_o + (static_cast<int64_t>(pi) * rows + row) * kHeadDim + 4 * lane);
+      op[u] = merge_load4(q.part_o + (static_cast<int64_t>(pi) * rows + row) * q.o_stride + 4 * lane, vec4);
     }
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
@@ -705,19 +867,16 @@ __global__ void __launch_bounds__(kMergeSmallRows * 32) decode_merge_small_kerne
       ot[0] += op[u].x * w8[u]; ot[1] += op[u].y * w8[u]; ot[2] += op[u].z * w8[u]; ot[3] += op[u].w * w8[u];
     }
   }
-  merge_finish(ot, lt, mt, row, lane, mode, unrotate, out, out_o, out_m, out_l);
+  merge_finish(q, ot, lt, mt, row, lane);
 }
 
 // Picks the merge kernel by the number of partials per row.
-static void launch_merge(const float* po, const float* pm, const float* pl_, int ml_stride, int P, int64_t rows, float m_to_log2,
-                         int mode, int unrotate, __half* out, float* out_o, float* out_m, float* out_l, cudaStream_t st) {
-  if (P <= kMergeSmallMaxP) {
-    const unsigned grid = static_cast<unsigned>((rows + kMergeSmallRows - 1) / kMergeSmallRows);
-    decode_merge_small_kernel<<<grid, kMergeSmallRows * 32, 0, st>>>(po, pm, pl_, ml_stride, P, rows, m_to_log2, mode, unrotate, out,
-                                                                     out_o, out_m, out_l);
+static void launch_merge(const MergeParams& q, cudaStream_t st) {
+  if (q.P <= kMergeSmallMaxP) {
+    const unsigned grid = static_cast<unsigned>((q.rows + kMergeSmallRows - 1) / kMergeSmallRows);
+    decode_merge_small_kernel<<<grid, kMergeSmallRows * 32, 0, st>>>(q);
   } else {
-    decode_merge_kernel<<<static_cast<unsigned>(rows), kMergeWarps * 32, 0, st>>>(po, pm, pl_, ml_stride, P, rows, m_to_log2, mode,
-                                                                                  unrotate, out, out_o, out_m, out_l);
+    decode_merge_kernel<<<static_cast<unsigned>(q.rows), kMergeWarps * 32, 0, st>>>(q);
   }
 }
 
@@ -781,54 +940,93 @@ __global__ void __launch_bounds__(32) decode_scalar_kernel(const __half* __restr
 
 // ---- host side --------------------------------------------------------------------------------------------------
 struct Plan {
-  int warps, depth, heads_per_cta, head_groups, warps_per_head, splits, tokens_per_split, parts;
+  int warps, depth, heads_per_cta, head_groups, warps_per_head;
+  int chunk_groups, groups_pad, chunks;   // work decomposition (see decode_split_kernel)
+  int parts;                              // partial rows per output row = most chunks any sequence touches
 };
 
 // Warps per CTA and ring stages per warp of the split kernel: 16 warps (four per scheduler, 128 registers each)
 // with three 2560-byte stages per warp leave room for the 64 KB table in the 227 KB of one SM.
-constexpr int kSplitWarps = 16, kSplitStages = 3;
+#ifndef CDA_SPLIT_WARPS
+#define CDA_SPLIT_WARPS 16
+#endif
+#ifndef CDA_SPLIT_STAGES
+#define CDA_SPLIT_STAGES 3
+#endif
+constexpr int kSplitWarps = CDA_SPLIT_WARPS, kSplitStages = CDA_SPLIT_STAGES;
 
-static int pick_heads_per_cta(int H_kv) {
+static int pick_heads_per_cta(int H_kv) {   // largest power of two <= 8 that divides both H_kv and the warp count
   int h = 8;
-  while (h > 1 && (h > H_kv || H_kv % h)) h >>= 1;
+  while (h > 1 && (h > H_kv || H_kv % h || kSplitWarps % h)) h >>= 1;
   return h;
 }
 
-// Choose the number of key-range splits.  One CTA occupies one SM and CTAs of one launch all carry the same work, so
-// the launch runs in ceil(CTAs / SMs) rounds, each as long as one CTA: a fixed part (launch, table and query set-up,
-// first copies, partial write and its share of the merge; measured at about the streaming time of 360 tokens when
-// the CTA's warps cover eight heads, and proportionally more tokens when they share fewer heads and so pass over a
-// token faster) plus the CTA's tokens.  Take the split count with the smallest estimate; splits never go below 128
-// tokens.
+// Chunks touched by positions [lo, lo + len) of the line when it is cut every c positions.
+static int chunks_touched(int64_t lo, int64_t len, int64_t c) { return static_cast<int>((lo + len - 1) / c - lo / c + 1); }
+
+// Choose the chunk size.  One CTA occupies one SM and every chunk carries the same number of groups, so the launch runs
+// in ceil(CTAs / SMs) rounds, each as long as one CTA: a fixed part (launch, table and query set-up, first copies,
+// partial write and its share of the merge; measured at about the streaming time of 360 tokens when the CTA's warps
+// cover eight heads, and proportionally more tokens when they share fewer heads and so pass over a token faster) plus
+// the chunk's tokens.  Candidates are the chunk sizes that give 1, 2, ... CTAs per SM; the smallest estimate wins and a
+// chunk never goes below 128 tokens.  num_splits > 0 instead cuts every sequence into that many equal key ranges of its
+// own (chunks then never straddle two sequences).
 static Plan make_plan(int B, int H_kv, int max_seq_len, int num_splits, int sms) {
-  constexpr int kFloorTokens = 128, kFixedTokens = 360, kMaxSplits = 4096;
+  constexpr int kFloorGroups = 8, kFixedTokens = 360, kMaxParts = 4096, kMaxCtasPerSm = 8;
   Plan pl;
   pl.warps = kSplitWarps; pl.depth = kSplitStages;
   pl.heads_per_cta = pick_heads_per_cta(H_kv);
   pl.head_groups = H_kv / pl.heads_per_cta;
   pl.warps_per_head = pl.warps / pl.heads_per_cta;
-  const int n = max_seq_len > 0 ? max_seq_len : 1;
-  int S = num_splits;
-  if (S <= 0) {
-    const int64_t other = static_cast<int64_t>(B > 0 ? B : 1) * pl.head_groups;
-    int s_max = (n + kFloorTokens - 1) / kFloorTokens;
-    if (s_max > kMaxSplits) s_max = kMaxSplits;
-    const int fixed = kFixedTokens * 8 / pl.heads_per_cta;
-    int64_t best = -1;
-    S = 1;
-    for (int s = 1; s <= s_max; ++s) {
-      const int tps_s = ((n + s - 1) / s + 15) / 16 * 16;
-      const int64_t ctas = static_cast<int64_t>((n + tps_s - 1) / tps_s) * other;
-      const int64_t rounds = (ctas + sms - 1) / sms;
-      const int64_t est = rounds * (fixed + tps_s);
-      if (best < 0 || est < best) { best = est; S = s; }
-      if (rounds > 16 && est > 2 * best) break;   // finer splits only add rounds from here on
-    }
+  const int64_t batch = B > 0 ? B : 1;
+  const int ng = max_seq_len > 0 ? (max_seq_len + 15) / 16 : 1;     // groups of the longest sequence
+  if (num_splits > 0) {
+    const int want = num_splits < kMaxParts ? num_splits : kMaxParts;
+    pl.chunk_groups = (ng + want - 1) / want;
+    pl.parts = (ng + pl.chunk_groups - 1) / pl.chunk_groups;
+    pl.groups_pad = pl.chunk_groups * pl.parts;
+    pl.chunks = static_cast<int>(batch * pl.parts);
+    return pl;
   }
-  int tps = ((n + S - 1) / S + 15) / 16 * 16;
-  pl.tokens_per_split = tps;
-  pl.splits = (n + tps - 1) / tps;
-  pl.parts = pl.splits;            // the warps of a head are combined inside the CTA
+  const int64_t positions = batch * ng;
+  const int fixed = kFixedTokens * 8 / pl.heads_per_cta / 16;     // per CTA, in groups
+  const int fixed_item = fixed / 2 + 1;                           // a second item in a CTA: pipeline drained and refilled
+  int64_t best = -1;
+  int best_c = kFloorGroups, best_pad = ng;
+  auto consider = [&](int64_t c, int pad, bool straddles) {
+    const int64_t ctas = (batch * pad + c - 1) / c * pl.head_groups;
+    const int64_t rounds = (ctas + sms - 1) / sms;
+    const int64_t est = rounds * (fixed + c) + (straddles ? fixed_item : 0);
+    if (best < 0 || est < best) { best = est; best_c = static_cast<int>(c); best_pad = pad; }
+  };
+  for (int k = 1; k <= kMaxCtasPerSm; ++k) {
+    int64_t target = static_cast<int64_t>(sms) * k / pl.head_groups;
+    if (target < 1) target = 1;
+    // (a) equal key ranges inside every sequence: no chunk touches two sequences
+    for (int64_t per_seq = target / batch; per_seq <= target / batch + 1; ++per_seq) {
+      if (per_seq < 1) continue;
+      int64_t c = (ng + per_seq - 1) / per_seq;
+      if (c < kFloorGroups) c = kFloorGroups;
+      const int64_t n = (ng + c - 1) / c;
+      consider(c, static_cast<int>(c * n), false);
+    }
+    // (b) the whole line cut into `target` equal chunks, whatever the sequence boundaries
+    int64_t c = (positions + target - 1) / target;
+    if (c < kFloorGroups) c = kFloorGroups;
+    consider(c, ng, ng % c != 0);
+    if (c == kFloorGroups) break;
+  }
+  pl.chunk_groups = best_c;
+  pl.groups_pad = best_pad;
+  pl.chunks = static_cast<int>((batch * best_pad + best_c - 1) / best_c);
+  int parts = 1;
+  if (best_pad % best_c == 0) parts = best_pad / best_c;
+  else if (batch <= 65536) {
+    for (int64_t b = 0; b < batch; ++b) { const int t = chunks_touched(b * best_pad, best_pad, best_c); if (t > parts) parts = t; }
+  } else {
+    parts = (best_pad - 1) / best_c + 2;
+  }
+  pl.parts = parts;
   return pl;
 }
 
@@ -864,8 +1062,45 @@ static int validate(const char* who, const DecodeCommon& a) {
 
 constexpr int kMaxDynamicSmem = 232448 - 1024;   // the opt-in shared memory of one SM (227 KB) less the kernel's static arrays
 
+// cuTensorMapEncodeTiled, looked up through the runtime so that the library does not link against libcuda.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess || qres != cudaDriverEntryPointSuccess)
+      ptr = nullptr;
+    cudaGetLastError();
+    fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// The cache as a 2-D byte tensor: row = one slot position (all heads, H_kv * slot_bytes bytes), rows = slot positions.
+// A copy box is 16 rows x 160 bytes starting at byte head * slot_bytes: one 16-token group of one head, each slot followed
+// by the first bytes of the next head's slot (or zeros where the box leaves the row), so that a slot lands in a 160-byte
+// cell of the ring stage.
+static int make_cache_map(const char* who, const DecodeCommon& a, CUtensorMap* out) {
+  const EncodeTiledFn encode = encode_tiled_fn();
+  if (encode == nullptr) return fail(CDA_ERR_LAUNCH, "%s: cuTensorMapEncodeTiled is not available from this driver", who);
+  const cuuint64_t row_bytes = static_cast<cuuint64_t>(a.H_kv) * a.slot_bytes;
+  const cuuint64_t dims[2] = {row_bytes, static_cast<cuuint64_t>(a.num_slots)};
+  const cuuint64_t strides[1] = {row_bytes};
+  const cuuint32_t box[2] = {160u, 16u};
+  const cuuint32_t elem[2] = {1u, 1u};
+  const CUresult rc = encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(a.cache), dims, strides, box, elem,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS) return fail(CDA_ERR_LAUNCH, "%s: cuTensorMapEncodeTiled failed (%d) for rows of %llu bytes x %lld slots", who,
+                                      static_cast<int>(rc), static_cast<unsigned long long>(row_bytes), static_cast<long long>(a.num_slots));
+  return CDA_OK;
+}
+
 template <int G, int KB, int VB, int W, int NS>
-static int launch_split(const DecodeParams& p0, const Plan& pl, cudaStream_t st) {
+static int launch_split(const DecodeParams& p0, const Plan& pl, const CUtensorMap& cache_map, cudaStream_t st) {
   // Wherever the dynamic window starts relative to a 64 KB boundary, the rings packed around the aligned table need
   // at most one ring of slack (or, with few warps, the gap before the table itself).
   static_assert(kLutWindow + (W + 1) * DecCfg<W, NS, KB, VB>::kRingBytes <= kMaxDynamicSmem && 2 * kLutWindow <= kMaxDynamicSmem,
@@ -881,27 +1116,26 @@ static int launch_split(const DecodeParams& p0, const Plan& pl, cudaStream_t st)
   }
   DecodeParams p = p0;
   p.smem_bytes = kMaxDynamicSmem;
-  const dim3 grid(pl.splits, p.B, pl.head_groups);
-  decode_split_kernel<G, KB, VB, W, NS><<<grid, W * 32, kMaxDynamicSmem, st>>>(p);
+  const dim3 grid(pl.chunks, pl.head_groups);
+  decode_split_kernel<G, KB, VB, W, NS><<<grid, W * 32, kMaxDynamicSmem, st>>>(p, cache_map);
   return check_launch("decode split kernel");
 }
 
 template <int G, int KB, int VB>
-static int dispatch_shape(const DecodeParams& p, const Plan& pl, cudaStream_t st) {
-  return launch_split<G, KB, VB, kSplitWarps, kSplitStages>(p, pl, st);
+static int dispatch_shape(const DecodeParams& p, const Plan& pl, const CUtensorMap& cache_map, cudaStream_t st) {
+  return launch_split<G, KB, VB, kSplitWarps, kSplitStages>(p, pl, cache_map, st);
 }
 
 template <int G>
-static int dispatch_bits(const DecodeParams& p, const Plan& pl, int kb, int vb, cudaStream_t st) {
-  if (kb == 4 && vb == 4) return dispatch_shape<G, 4, 4>(p, pl, st);
-  if (kb == 4 && vb == 2) return dispatch_shape<G, 4, 2>(p, pl, st);
-  if (kb == 2 && vb == 2) return dispatch_shape<G, 2, 2>(p, pl, st);
-  return dispatch_shape<G, 2, 4>(p, pl, st);
+static int dispatch_bits(const DecodeParams& p, const Plan& pl, const CUtensorMap& cache_map, int kb, int vb, cudaStream_t st) {
+  if (kb == 4 && vb == 4) return dispatch_shape<G, 4, 4>(p, pl, cache_map, st);
+  if (kb == 4 && vb == 2) return dispatch_shape<G, 4, 2>(p, pl, cache_map, st);
+  if (kb == 2 && vb == 2) return dispatch_shape<G, 2, 2>(p, pl, cache_map, st);
+  return dispatch_shape<G, 2, 4>(p, pl, cache_map, st);
 }
 
-static int run_split(const char* who, const DecodeCommon& a, void* workspace, size_t workspace_bytes, int num_splits,
-                     cudaStream_t st, Plan* plan_out, float** ml_out, float** o_out) {
-  const Plan pl = make_plan(a.B, a.H_kv, a.max_seq_len, num_splits, device_sm_count(-1));
+static int run_split(const char* who, const DecodeCommon& a, void* workspace, size_t workspace_bytes, const Plan& pl,
+                     cudaStream_t st, float** ml_out, float** o_out) {
   const size_t need = ws_bytes(pl, a.B, a.H_q);
   if (!workspace || workspace_bytes < need)
     return fail(CDA_ERR_WORKSPACE, "%s: workspace of %zu bytes, need %zu", who, workspace_bytes, need);
@@ -919,15 +1153,18 @@ static int run_split(const char* who, const DecodeCommon& a, void* workspace, si
   p.heads_per_cta = pl.heads_per_cta;
   p.block_size = a.block_size; p.bt_stride = a.bt_stride;
   p.num_blocks = static_cast<int>(a.num_slots / a.block_size);
-  p.tokens_per_split = pl.tokens_per_split;
+  p.chunk_groups = pl.chunk_groups; p.groups_pad = pl.groups_pad;
   p.scale_log2 = a.scale * kLog2e;
   const int gpb = a.block_size / 16;
   p.gpb_shift = -1;
   for (int sft = 0; sft < 16; ++sft) if ((1 << sft) == gpb) p.gpb_shift = sft;
   p.smem_bytes = 0;
-  const int rc = p.group <= 4 ? dispatch_bits<4>(p, pl, a.k_bits, a.v_bits, st) : dispatch_bits<8>(p, pl, a.k_bits, a.v_bits, st);
+  CUtensorMap cache_map;
+  int rc = make_cache_map(who, a, &cache_map);
   if (rc != CDA_OK) return rc;
-  *plan_out = pl; *ml_out = p.part_ml; *o_out = p.part_o;
+  rc = p.group <= 4 ? dispatch_bits<4>(p, pl, cache_map, a.k_bits, a.v_bits, st) : dispatch_bits<8>(p, pl, cache_map, a.k_bits, a.v_bits, st);
+  if (rc != CDA_OK) return rc;
+  *ml_out = p.part_ml; *o_out = p.part_o;
   return CDA_OK;
 }
 
@@ -955,18 +1192,55 @@ static int static_scratch_address(uint8_t** out) {
   return CDA_OK;
 }
 
+// Where a decode call delivers its result.  mode 0: fp16 rows (and optionally the log-sum-exp); mode 1: the merged
+// partial (O rows o_stride floats apart, m / l ml_stride floats apart).
+struct DecodeSink {
+  int mode;
+  __half* out; float* lse;
+  float* O; float* m; float* l;
+  int o_stride, ml_stride;
+};
+
+static int decode_run(const char* who, const DecodeCommon& a, const DecodeSink& sink, void* workspace, size_t workspace_bytes,
+                      const Plan& pl, cudaStream_t st) {
+  const int64_t rows = static_cast<int64_t>(a.B) * a.H_q;
+  if (rows > 0x7fffffffLL) return fail(CDA_ERR_N_TOO_LARGE, "%s: B*H_q too large", who);
+  float* ml; float* po;
+  const int rc = run_split(who, a, workspace, workspace_bytes, pl, st, &ml, &po);
+  if (rc != CDA_OK) return rc;
+  MergeParams q{};
+  q.part_o = po; q.part_m = ml; q.part_l = ml + 1; q.ml_stride = 2; q.o_stride = kHeadDim; q.P = pl.parts; q.rows = rows;
+  q.m_to_log2 = 1.0f; q.mode = sink.mode; q.unrotate = 1; q.out = sink.out; q.out_lse = sink.lse;
+  q.out_o = sink.O; q.out_m = sink.m; q.out_l = sink.l; q.out_o_stride = sink.o_stride; q.out_ml_stride = sink.ml_stride;
+  q.rows_per_seq = a.H_q; q.chunk_groups = pl.chunk_groups; q.groups_pad = pl.groups_pad;
+  launch_merge(q, st);
+  return check_launch("decode merge kernel");
+}
+
 }  // namespace cda
 
 using namespace cda;
 
 extern "C" int cda_b200_decode_plan_splits(int B, int H_kv, int max_seq_len, int device) {
   if (B <= 0 || H_kv <= 0 || max_seq_len < 0) return fail(CDA_ERR_BAD_ARG, "decode_plan_splits: bad size");
-  return make_plan(B, H_kv, max_seq_len, 0, device_sm_count(device)).splits;
+  return make_plan(B, H_kv, max_seq_len, 0, device_sm_count(device)).parts;
 }
 
 extern "C" size_t cda_b200_decode_workspace_bytes(int B, int H_q, int H_kv, int max_seq_len, int num_splits, int device) {
   if (B <= 0 || H_q <= 0 || H_kv <= 0 || max_seq_len < 0) return 256;
   return ws_bytes(make_plan(B, H_kv, max_seq_len, num_splits, device_sm_count(device)), B, H_q);
+}
+
+static int decode_fp16(const char* who, const DecodeCommon& a, void* out, float* lse, void* workspace, size_t workspace_bytes,
+                       int num_splits, void* stream) {
+  const int rc = validate(who, a);
+  if (rc != CDA_OK || a.B == 0) return rc;
+  if (!out) return fail(CDA_ERR_BAD_ARG, "%s: null output", who);
+  if (reinterpret_cast<uintptr_t>(out) & 7u) return fail(CDA_ERR_BAD_ALIGN, "%s: output must be 8-byte aligned", who);
+  if (num_splits < 0) return fail(CDA_ERR_BAD_ARG, "%s: negative num_splits", who);
+  const DecodeSink sink{0, static_cast<__half*>(out), lse, nullptr, nullptr, nullptr, 0, 0};
+  return decode_run(who, a, sink, workspace, workspace_bytes, make_plan(a.B, a.H_kv, a.max_seq_len, num_splits, device_sm_count(-1)),
+                    static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int cda_b200_decode(const void* Q, const void* kv_cache, const int32_t* block_table, const int32_t* seq_lens,
@@ -975,18 +1249,30 @@ extern "C" int cda_b200_decode(const void* Q, const void* kv_cache, const int32_
                                int slot_bytes, int k_bits, int v_bits, float scale, int num_splits, void* stream) {
   const DecodeCommon a{Q, kv_cache, block_table, seq_lens, cb_K, cb_V, B, H_q, H_kv, block_size, block_table_stride,
                        max_seq_len, num_slots, slot_bytes, k_bits, v_bits, scale};
-  int rc = validate("decode", a);
-  if (rc != CDA_OK || B == 0) return rc;
-  if (!out) return fail(CDA_ERR_BAD_ARG, "decode: null output");
-  if (reinterpret_cast<uintptr_t>(out) & 7u) return fail(CDA_ERR_BAD_ALIGN, "decode: output must be 8-byte aligned");
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  Plan pl; float* ml; float* po;
-  rc = run_split("decode", a, workspace, workspace_bytes, num_splits, st, &pl, &ml, &po);
-  if (rc != CDA_OK) return rc;
-  const int64_t rows = static_cast<int64_t>(B) * H_q;
-  if (rows > 0x7fffffffLL) return fail(CDA_ERR_N_TOO_LARGE, "decode: B*H_q too large");
-  launch_merge(po, ml, ml + 1, 2, pl.parts, rows, 1.0f, 0, 1, static_cast<__half*>(out), nullptr, nullptr, nullptr, st);
-  return check_launch("decode merge kernel");
+  return decode_fp16("decode", a, out, nullptr, workspace, workspace_bytes, num_splits, stream);
+}
+
+extern "C" int cda_b200_decode_lse(const void* Q, const void* kv_cache, const int32_t* block_table, const int32_t* seq_lens,
+                                   const float* cb_K, const float* cb_V, void* out, float* lse, void* workspace,
+                                   size_t workspace_bytes, int B, int H_q, int H_kv, int block_size, int block_table_stride,
+                                   int max_seq_len, int64_t num_slots, int slot_bytes, int k_bits, int v_bits, float scale,
+                                   int num_splits, void* stream) {
+  const DecodeCommon a{Q, kv_cache, block_table, seq_lens, cb_K, cb_V, B, H_q, H_kv, block_size, block_table_stride,
+                       max_seq_len, num_slots, slot_bytes, k_bits, v_bits, scale};
+  if (B > 0 && !lse) return fail(CDA_ERR_BAD_ARG, "decode_lse: null lse");
+  return decode_fp16("decode_lse", a, out, lse, workspace, workspace_bytes, num_splits, stream);
+}
+
+static int decode_partial_any(const char* who, const DecodeCommon& a, float* O, float* m, float* l, int o_stride, int ml_stride,
+                              void* workspace, size_t workspace_bytes, int num_splits, void* stream) {
+  const int rc = validate(who, a);
+  if (rc != CDA_OK || a.B == 0) return rc;
+  if (!O || !m || !l) return fail(CDA_ERR_BAD_ARG, "%s: null output", who);
+  if (reinterpret_cast<uintptr_t>(O) & ((o_stride & 3) ? 7u : 15u)) return fail(CDA_ERR_BAD_ALIGN, "%s: O must be 16-byte aligned (packed rows: 8)", who);
+  if (num_splits < 0) return fail(CDA_ERR_BAD_ARG, "%s: negative num_splits", who);
+  const DecodeSink sink{1, nullptr, nullptr, O, m, l, o_stride, ml_stride};
+  return decode_run(who, a, sink, workspace, workspace_bytes, make_plan(a.B, a.H_kv, a.max_seq_len, num_splits, device_sm_count(-1)),
+                    static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int cda_b200_decode_partial(const void* Q, const void* kv_cache, const int32_t* block_table, const int32_t* seq_lens,
@@ -996,30 +1282,45 @@ extern "C" int cda_b200_decode_partial(const void* Q, const void* kv_cache, cons
                                        int num_splits, void* stream) {
   const DecodeCommon a{Q, kv_cache, block_table, seq_lens, cb_K, cb_V, B, H_q, H_kv, block_size, block_table_stride,
                        max_seq_len, num_slots, slot_bytes, k_bits, v_bits, scale};
-  int rc = validate("decode_partial", a);
-  if (rc != CDA_OK || B == 0) return rc;
-  if (!O || !m || !l) return fail(CDA_ERR_BAD_ARG, "decode_partial: null output");
-  if (!aligned16(O)) return fail(CDA_ERR_BAD_ALIGN, "decode_partial: O must be 16-byte aligned");
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  Plan pl; float* ml; float* po;
-  rc = run_split("decode_partial", a, workspace, workspace_bytes, num_splits, st, &pl, &ml, &po);
-  if (rc != CDA_OK) return rc;
-  const int64_t rows = static_cast<int64_t>(B) * H_q;
-  if (rows > 0x7fffffffLL) return fail(CDA_ERR_N_TOO_LARGE, "decode_partial: B*H_q too large");
-  launch_merge(po, ml, ml + 1, 2, pl.parts, rows, 1.0f, 1, 0, nullptr, O, m, l, st);
-  return check_launch("decode partial merge kernel");
+  return decode_partial_any("decode_partial", a, O, m, l, kHeadDim, 1, workspace, workspace_bytes, num_splits, stream);
+}
+
+extern "C" int cda_b200_decode_partial_packed(const void* Q, const void* kv_cache, const int32_t* block_table,
+                                              const int32_t* seq_lens, const float* cb_K, const float* cb_V, float* packed,
+                                              void* workspace, size_t workspace_bytes, int B, int H_q, int H_kv, int block_size,
+                                              int block_table_stride, int max_seq_len, int64_t num_slots, int slot_bytes,
+                                              int k_bits, int v_bits, float scale, int num_splits, void* stream) {
+  const DecodeCommon a{Q, kv_cache, block_table, seq_lens, cb_K, cb_V, B, H_q, H_kv, block_size, block_table_stride,
+                       max_seq_len, num_slots, slot_bytes, k_bits, v_bits, scale};
+  constexpr int kPacked = kHeadDim + 2;
+  return decode_partial_any("decode_partial_packed", a, packed, packed ? packed + kHeadDim : nullptr,
+                            packed ? packed + kHeadDim + 1 : nullptr, kPacked, kPacked, workspace, workspace_bytes, num_splits, stream);
+}
+
+static int merge_any(const char* who, const float* O, const float* m, const float* l, int o_stride, int ml_stride, int S, int64_t R,
+                     void* out, int unrotate, void* stream) {
+  if (S <= 0 || R < 0) return fail(CDA_ERR_BAD_ARG, "%s: bad size", who);
+  if (R == 0) return CDA_OK;
+  if (!O || !m || !l || !out) return fail(CDA_ERR_BAD_ARG, "%s: null pointer", who);
+  if ((reinterpret_cast<uintptr_t>(O) & ((o_stride & 3) ? 7u : 15u)) || (reinterpret_cast<uintptr_t>(out) & 7u))
+    return fail(CDA_ERR_BAD_ALIGN, "%s: misaligned buffer", who);
+  if (R > 0x7fffffffLL) return fail(CDA_ERR_N_TOO_LARGE, "%s: too many rows", who);
+  MergeParams q{};
+  q.part_o = O; q.part_m = m; q.part_l = l; q.ml_stride = ml_stride; q.o_stride = o_stride; q.P = S; q.rows = R;
+  q.m_to_log2 = kLog2e; q.mode = 0; q.unrotate = unrotate ? 1 : 0; q.out = static_cast<__half*>(out);
+  launch_merge(q, static_cast<cudaStream_t>(stream));
+  return check_launch(who);
 }
 
 extern "C" int cda_b200_merge_partials(const float* O, const float* m, const float* l, int S, int64_t R, void* out,
                                        int unrotate, void* stream) {
-  if (S <= 0 || R < 0) return fail(CDA_ERR_BAD_ARG, "merge_partials: bad size");
-  if (R == 0) return CDA_OK;
-  if (!O || !m || !l || !out) return fail(CDA_ERR_BAD_ARG, "merge_partials: null pointer");
-  if (!aligned16(O) || (reinterpret_cast<uintptr_t>(out) & 7u)) return fail(CDA_ERR_BAD_ALIGN, "merge_partials: misaligned buffer");
-  if (R > 0x7fffffffLL) return fail(CDA_ERR_N_TOO_LARGE, "merge_partials: too many rows");
-  launch_merge(O, m, l, 1, S, R, kLog2e, 0, unrotate ? 1 : 0, static_cast<__half*>(out), nullptr, nullptr, nullptr,
-               static_cast<cudaStream_t>(stream));
-  return check_launch("merge_partials");
+  return merge_any("merge_partials", O, m, l, kHeadDim, 1, S, R, out, unrotate, stream);
+}
+
+extern "C" int cda_b200_merge_partials_packed(const float* packed, int S, int64_t R, void* out, int unrotate, void* stream) {
+  constexpr int kPacked = kHeadDim + 2;
+  return merge_any("merge_partials_packed", packed, packed ? packed + kHeadDim : nullptr, packed ? packed + kHeadDim + 1 : nullptr,
+                   kPacked, kPacked, S, R, out, unrotate, stream);
 }
 
 extern "C" int cda_b200_decode_scalar(const void* Q, const void* kv_cache, const int32_t* block_table, const int32_t* seq_lens,
@@ -1031,6 +1332,7 @@ extern "C" int cda_b200_decode_scalar(const void* Q, const void* kv_cache, const
   int rc = validate("decode_scalar", a);
   if (rc != CDA_OK || B == 0) return rc;
   if (!out) return fail(CDA_ERR_BAD_ARG, "decode_scalar: null output");
+  if (reinterpret_cast<uintptr_t>(out) & 7u) return fail(CDA_ERR_BAD_ALIGN, "decode_scalar: output must be 8-byte aligned");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const dim3 grid(H_q, B);
   const int nb = static_cast<int>(num_slots / block_size), grp = H_q / H_kv;
@@ -1059,14 +1361,13 @@ extern "C" int cda_b200_decode_static(const void* Q, const void* kv_cache, const
   if (!out) return fail(CDA_ERR_BAD_ARG, "decode_static: null output");
   if (reinterpret_cast<uintptr_t>(out) & 7u) return fail(CDA_ERR_BAD_ALIGN, "decode_static: output must be 8-byte aligned");
   if (num_splits < 0) return fail(CDA_ERR_BAD_ARG, "decode_static: negative num_splits");
-  const int64_t rows = static_cast<int64_t>(B) * H_q;
-  if (rows > 0x7fffffffLL) return fail(CDA_ERR_N_TOO_LARGE, "decode_static: B*H_q too large");
-  // Pick the split count: the planned (or requested) one if its partials fit in the built-in scratch, otherwise the
-  // largest count that does.  If not even one split fits, the problem is too large for this entry point.
+  // Pick the decomposition: the planned (or requested) one if its partials fit in the built-in scratch, otherwise equal
+  // key ranges per sequence with the largest count that does.  If not even one range per sequence fits, the problem is
+  // too large for this entry point.
   const int sms = device_sm_count(-1);
-  int splits = make_plan(B, H_kv, max_seq_len, num_splits, sms).splits;
-  while (splits > 1 && ws_bytes(make_plan(B, H_kv, max_seq_len, splits, sms), B, H_q) > kStaticScratchBytes) --splits;
-  const size_t need = ws_bytes(make_plan(B, H_kv, max_seq_len, splits, sms), B, H_q);
+  Plan pl = make_plan(B, H_kv, max_seq_len, num_splits, sms);
+  for (int s = pl.parts; ws_bytes(pl, B, H_q) > kStaticScratchBytes && s > 1;) pl = make_plan(B, H_kv, max_seq_len, --s, sms);
+  const size_t need = ws_bytes(pl, B, H_q);
   if (need > kStaticScratchBytes)
     return fail(CDA_ERR_WORKSPACE, "decode_static: B=%d, H_q=%d needs %zu bytes of scratch even unsplit; the built-in scratch holds %zu "
                 "(use cda_b200_decode with a caller-owned workspace)", B, H_q, need, kStaticScratchBytes);
@@ -1077,9 +1378,6 @@ extern "C" int cda_b200_decode_static(const void* Q, const void* kv_cache, const
   // The array keeps whatever the previous call left.  Only the status block has to start at zero; every (m, l) row and
   // every O row that the merge reads is rewritten by this call's split kernel first.
   if (cudaMemsetAsync(scratch, 0, 256, st) != cudaSuccess) return check_launch("decode_static: clearing the status block");
-  Plan pl; float* ml; float* po;
-  rc = run_split("decode_static", a, scratch, kStaticScratchBytes, splits, st, &pl, &ml, &po);
-  if (rc != CDA_OK) return rc;
-  launch_merge(po, ml, ml + 1, 2, pl.parts, rows, 1.0f, 0, 1, static_cast<__half*>(out), nullptr, nullptr, nullptr, st);
-  return check_launch("decode_static merge kernel");
+  const DecodeSink sink{0, static_cast<__half*>(out), nullptr, nullptr, nullptr, nullptr, 0, 0};
+  return decode_run("decode_static", a, sink, scratch, kStaticScratchBytes, pl, st);
 }

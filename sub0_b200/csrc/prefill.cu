@@ -328,6 +328,8 @@ extern "C" int cda_b200_cache_to_dense_rotated(const void* kv_cache, const int32
   const int64_t rows = static_cast<int64_t>(B) * max_seq_len * H_kv;
   if (rows == 0) return CDA_OK;
   if (!kv_cache || !block_table || !seq_lens || !cb_K || !cb_V || !k_out || !v_out) return fail(CDA_ERR_BAD_ARG, "cache_to_dense_rotated: null pointer");
+  if ((reinterpret_cast<uintptr_t>(k_out) & 7u) || (reinterpret_cast<uintptr_t>(v_out) & 7u))
+    return fail(CDA_ERR_BAD_ALIGN, "cache_to_dense_rotated: k_out and v_out must be 8-byte aligned");
   const int64_t blocks = (rows + 7) / 8;
   if (blocks > 0x7fffffffLL) return fail(CDA_ERR_N_TOO_LARGE, "cache_to_dense_rotated: too many rows");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -386,11 +388,12 @@ extern "C" int cda_b200_prefill_varlen(const void* Q, const void* kv_cache, cons
   if (static_cast<int64_t>(block_table_stride) * block_size < max_seq_len) return fail(CDA_ERR_BAD_SHAPE, "prefill_varlen: block table row shorter than max_seq_len");
   if (!kv_cache || !block_table || !seq_lens || !cb_K || !cb_V) return fail(CDA_ERR_BAD_ARG, "prefill_varlen: null pointer");
   if (!aligned16(kv_cache)) return fail(CDA_ERR_BAD_ALIGN, "prefill_varlen: cache must be 16-byte aligned");
+  if (!aligned16(Q) || !aligned16(out)) return fail(CDA_ERR_BAD_ALIGN, "prefill_varlen: Q and out must be 16-byte aligned");
   if (H_q / H_kv > 8) return fail(CDA_ERR_UNSUPPORTED, "prefill_varlen: GQA group %d > 8", H_q / H_kv);
   PrefillUmmaParams p{};
   p.q = static_cast<const __half*>(Q); p.out = static_cast<__half*>(out); p.cu_q = cu_seqlens_q;
   p.cache = static_cast<const uint8_t*>(kv_cache); p.block_table = block_table; p.seq_lens = seq_lens;
-  p.cb_k = cb_K; p.cb_v = cb_V; p.status = nullptr; p.block_size = block_size; p.bt_stride = block_table_stride;
+  p.cb_k = cb_K; p.cb_v = cb_V; p.block_size = block_size; p.bt_stride = block_table_stride;
   p.bs_shift = -1;
   for (int sft = 4; sft < 31; ++sft) if ((1 << sft) == block_size) p.bs_shift = sft;
   p.num_blocks = static_cast<int>(num_slots / block_size);

@@ -28,9 +28,19 @@
 
 namespace cda {
 
-// Set (and never cleared) when a CTA of the prefill kernel gave up on a wait: later CTAs and launches return at once
-// instead of each running into its own time-out.  Read by cda_b200_prefill_fault().
+// Set when a CTA of the prefill kernel gave up on a wait: later CTAs and launches return at once instead of each
+// running into its own time-out.  Read by cda_b200_prefill_fault(), cleared only by cda_b200_prefill_clear_status().
 __device__ int g_prefill_fault = 0;
+// Sticky per-device report of what the prefill kernel saw in its inputs (cda_b200_prefill_status()):
+//   bit 0  a block-table entry was outside the cache (block 0 was read instead)
+//   bit 2  a bounded wait gave up (same event as g_prefill_fault)
+//   bit 3  a sequence had more new tokens than tokens (q_len > seq_len): its output rows were left unwritten
+__device__ int g_prefill_status = 0;
+
+// Diagnostic knobs of the next launches (host side, set by cda_b200_prefill_debug): the wait limit, and whether the
+// producers keep back the "K tile 0 is full" arrive so that the waits behind it run out.
+static unsigned long long g_wait_limit_ns = umma::kWaitLimitNs;
+static int g_withhold_first_k = 0;
 
 namespace pfu {
 
@@ -59,7 +69,7 @@ constexpr int kSmemBytes = kOffBar + 256 + 1024;   // + slack for the 1024-byte 
 // barrier slots (8 bytes each) inside kOffBar
 constexpr int kBarKFull = 0, kBarKEmpty = 2, kBarVFull = 4, kBarVEmpty = 6, kBarSFull = 8, kBarPFull = 10, kBarPvDone = 12,
               kBarNorms = 14;   // 18 barriers
-constexpr int kOffTmemAddr = 160, kOffAbort = 164, kOffOutcome = 168;   // outcome words: 2 per waiting group (3 groups)
+constexpr int kOffTmemAddr = 160, kOffOutcome = 168, kOffAbort = 192;   // outcome words: 2 per waiting group (3 groups); WaitState (16 B)
 
 __device__ __forceinline__ uint32_t lds32(uint32_t a) {
   uint32_t v;
@@ -97,7 +107,7 @@ __device__ __forceinline__ void named_barrier(int id, int nthreads) {
 }
 struct GroupWaiter {
   volatile int* outcome;     // two words in shared memory
-  volatile int* abort_flag;
+  volatile umma::WaitState* abort_flag;
   int id, nthreads, turn;
   bool leader;               // lane 0 of the group's first warp
   __device__ __forceinline__ bool wait(uint32_t bar, uint32_t parity) {
@@ -137,14 +147,18 @@ __device__ __forceinline__ void fill_code_table(uint8_t* lut, int stride, const 
 // Expand 16 bytes of codes (one quad of a slot) of token row `nl` into fp16 chunks of a 128-row tile.
 // tile: shared address of column block 0 (block 1 is kColBlockBytes further).  quad: index of the 16 bytes in the row's codes.
 // lut_lane: table address + this lane's copy; stride: bytes per entry row.
-// scale: a half2 (norm, norm) every expanded pair is multiplied by, or 0 for none.
-__device__ __forceinline__ uint32_t hmul2(uint32_t a, uint32_t b) {
+// scale_hi / scale_lo (SCALED only): the row's norm as two fp16 terms, each duplicated into a half2 -- hi = fp16(norm),
+// lo = fp16(norm - hi).  Every expanded pair becomes pair * hi + pair * lo.  A single fp16 factor would put the SAME relative
+// rounding error of the norm (up to 2^-11) on all 128 coordinates of that key, which the inverse Hadamard transform does not
+// average out; with the second term only per-element rounding is left.
+__device__ __forceinline__ uint32_t hscale2(uint32_t a, uint32_t hi, uint32_t lo) {
   uint32_t d;
-  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  asm("{\n\t.reg .b32 t;\n\tmul.rn.f16x2 t, %1, %3;\n\tfma.rn.f16x2 %0, %1, %2, t;\n\t}" : "=r"(d) : "r"(a), "r"(hi), "r"(lo));
   return d;
 }
 template <int BITS, bool SCALED>
-__device__ __forceinline__ void expand_quad(uint32_t tile, uint32_t lut_lane, uint32_t stride, const uint4& w, int nl, int quad, uint32_t scale) {
+__device__ __forceinline__ void expand_quad(uint32_t tile, uint32_t lut_lane, uint32_t stride, const uint4& w, int nl, int quad, uint32_t scale_hi,
+                                            uint32_t scale_lo) {
   const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
   if (BITS == 4) {
 #pragma unroll
@@ -157,7 +171,7 @@ __device__ __forceinline__ void expand_quad(uint32_t tile, uint32_t lut_lane, ui
       v[3] = lds32(lut_lane + (x >> 24) * stride);
       if (SCALED) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) v[i] = hmul2(v[i], scale);
+        for (int i = 0; i < 4; ++i) v[i] = hscale2(v[i], scale_hi, scale_lo);
       }
       const int c16 = quad * 4 + wi;                       // 16-byte chunk of the row: 8 coordinates
       sts128(tile + (c16 >> 3) * kColBlockBytes + sw128(nl, c16 & 7), v[0], v[1], v[2], v[3]);
@@ -170,7 +184,10 @@ __device__ __forceinline__ void expand_quad(uint32_t tile, uint32_t lut_lane, ui
       for (int hb = 0; hb < 2; ++hb) {                     // two code bytes = 8 coordinates = one chunk
         const uint32_t b0 = (x >> (16 * hb)) & 0xffu, b1 = (x >> (16 * hb + 8)) & 0xffu;
         uint2 lo = lds64(lut_lane + b0 * stride), hi = lds64(lut_lane + b1 * stride);
-        if (SCALED) { lo.x = hmul2(lo.x, scale); lo.y = hmul2(lo.y, scale); hi.x = hmul2(hi.x, scale); hi.y = hmul2(hi.y, scale); }
+        if (SCALED) {
+          lo.x = hscale2(lo.x, scale_hi, scale_lo); lo.y = hscale2(lo.y, scale_hi, scale_lo);
+          hi.x = hscale2(hi.x, scale_hi, scale_lo); hi.y = hscale2(hi.y, scale_hi, scale_lo);
+        }
         const int c16 = quad * 8 + wi * 2 + hb;
         sts128(tile + (c16 >> 3) * kColBlockBytes + sw128(nl, c16 & 7), lo.x, lo.y, hi.x, hi.y);
       }
@@ -305,7 +322,11 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
   const int seq_len = p.seq_lens[b];
   const int n_qtiles = (q_len + kPosPerTile - 1) / kPosPerTile;
   const int qt = n_qtiles - 1 - static_cast<int>(blockIdx.z);   // longest rows first
-  if (qt < 0 || seq_len <= 0 || q_len > seq_len) return;
+  if (qt < 0 || seq_len <= 0) return;
+  if (q_len > seq_len) {   // more new tokens than tokens: not a causal chunk; report it, write nothing
+    if (threadIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) atomicOr(&g_prefill_status, 8);
+    return;
+  }
   if (*reinterpret_cast<volatile int*>(&g_prefill_fault)) return;
   const int p0 = qt * kPosPerTile;                               // first query position (within the new tokens) of this tile
   const int q_offset = seq_len - q_len;                          // bottom-right alignment
@@ -313,7 +334,7 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
   const int n_tiles = (q_offset + pos_hi) / kKeys + 1;           // key tiles that hold an unmasked key
   const int g = p.group;
 
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + kOffBar + kOffAbort);
+  volatile WaitState* abort_flag = reinterpret_cast<volatile WaitState*>(sm + kOffBar + kOffAbort);
   const uint32_t bar0 = base + kOffBar;
   auto bar = [&](int i) { return bar0 + 8u * i; };
 
@@ -351,7 +372,8 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
       mbar_init(bar(kBarSFull + i), 1); mbar_init(bar(kBarPFull + i), kSoftmaxWarpsPerBlock); mbar_init(bar(kBarPvDone + i), 1);
     }
     for (int i = 0; i < 4; ++i) mbar_init(bar(kBarNorms + i), kProducerWarps);
-    *abort_flag = 0;
+    abort_flag->abort = 0;
+    abort_flag->limit_ns = p.wait_limit_ns;
     mbar_init_fence();
   }
   if (warp == kMmaWarp) {
@@ -539,18 +561,24 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
       for (int it = 0; it < kItK; ++it) {
         const int x = pt + kProducerThreads * it, nl = x / KB, quad = x % KB;
         if (quad == 0) kn[nl] = r.n[it] * kscale;
-        expand_quad<KB, false>(tile, lutk_lane, lut_stride, r.w[it], nl, quad, 0u);
+        expand_quad<KB, false>(tile, lutk_lane, lut_stride, r.w[it], nl, quad, 0u, 0u);
       }
       fence_async_smem();
       __syncwarp();
-      if (lane == 0) { mbar_arrive(bar(kBarNorms + (j & 3))); mbar_arrive(bar(kBarKFull + (j & 1))); }
+      if (lane == 0) {
+        mbar_arrive(bar(kBarNorms + (j & 3)));
+        if (!(p.withhold_first_k && j == 0)) mbar_arrive(bar(kBarKFull + (j & 1)));
+      }
     };
     auto expand_v = [&](int j, const VRegs& r) {
 #pragma unroll
       for (int it = 0; it < kItV; ++it) {
         const int x = pt + kProducerThreads * it, nl = x / VB, quad = x % VB;
-        // the value norm goes into the tile (fp16 product), so the probabilities need no per-key factor
-        expand_quad<VB, true>(base + kOffV + (j & 1) * kTileBytes, lutv_lane, lut_stride, r.w[it], nl, quad, pack_half2(r.n[it], r.n[it]));
+        // the value norm goes into the tile (fp16 products, norm as two fp16 terms), so the probabilities need no per-key factor
+        const float n_hi = round_to_half(r.n[it]);
+        const float n_lo = r.n[it] - n_hi;
+        expand_quad<VB, true>(base + kOffV + (j & 1) * kTileBytes, lutv_lane, lut_stride, r.w[it], nl, quad, pack_half2(n_hi, n_hi),
+                              pack_half2(n_lo, n_lo));
       }
       fence_async_smem();
       __syncwarp();
@@ -571,7 +599,7 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
       expand_v(i, vr);
       load_v(i + 1, vr);
     }
-    if (bad_block && p.status) atomicOr(p.status, 1);
+    if (bad_block) atomicOr(&g_prefill_status, 1);
   } else {
     // ================= MMA issuer ==================================================================================================
     if (lane == 0) {
@@ -634,9 +662,9 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
 
   // ---- end: a CTA in which a wait gave up raises the device-wide flag; tensor memory is released either way ---------------
   __syncthreads();
-  if (*abort_flag != 0 && tid == 0) {
+  if (abort_flag->abort != 0 && tid == 0) {
     atomicOr(&g_prefill_fault, 1);
-    if (p.status) atomicOr(p.status, 4);
+    atomicOr(&g_prefill_status, 4);
   }
   if (warp == kMmaWarp) {
     tc_fence_after_sync();
@@ -658,7 +686,10 @@ static int launch_prefill_umma(const PrefillUmmaParams& p, int max_query_len, in
   const int q_tiles = (max_query_len + per_tile - 1) / per_tile;
   if (q_tiles > 65535 || p.H_kv > 65535) return fail(CDA_ERR_N_TOO_LARGE, "prefill: max_query_len %d or H_kv %d exceeds the grid limits", max_query_len, p.H_kv);
   const dim3 grid(B, p.H_kv, q_tiles);
-  prefill_umma_kernel<G, KB, VB><<<grid, pfu::kThreads, pfu::kSmemBytes, st>>>(p);
+  PrefillUmmaParams pp = p;
+  pp.wait_limit_ns = g_wait_limit_ns;
+  pp.withhold_first_k = g_withhold_first_k;
+  prefill_umma_kernel<G, KB, VB><<<grid, pfu::kThreads, pfu::kSmemBytes, st>>>(pp);
   return check_launch("prefill kernel");
 }
 
@@ -676,9 +707,33 @@ int dispatch_prefill_umma(const PrefillUmmaParams& p, int k_bits, int v_bits, in
 
 }  // namespace cda
 
-// 1 if a prefill CTA on the current device ever gave up on a wait (synchronises the device), 0 if not, < 0 on error.
+// 1 if a prefill CTA on the current device gave up on a wait since the last clear (synchronises the device), 0 if not,
+// < 0 on error.
 extern "C" int cda_b200_prefill_fault(void) {
   int v = 0;
   if (cudaMemcpyFromSymbol(&v, cda::g_prefill_fault, sizeof(int)) != cudaSuccess) return cda::check_launch("prefill_fault");
   return v != 0 ? 1 : 0;
+}
+
+// Status bits the prefill kernel raised on the current device since the last clear (synchronises the device).
+extern "C" int cda_b200_prefill_status(void) {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, cda::g_prefill_status, sizeof(int)) != cudaSuccess) return cda::check_launch("prefill_status");
+  return v & 0x7fffffff;
+}
+
+// Clears the status bits and the fault flag of the current device (synchronises the device).
+extern "C" int cda_b200_prefill_clear_status(void) {
+  const int zero = 0;
+  if (cudaMemcpyToSymbol(cda::g_prefill_status, &zero, sizeof(int)) != cudaSuccess ||
+      cudaMemcpyToSymbol(cda::g_prefill_fault, &zero, sizeof(int)) != cudaSuccess)
+    return cda::check_launch("prefill_clear_status");
+  return CDA_OK;
+}
+
+// Diagnostic knobs for the launches that follow on this process: wait_limit_us <= 0 restores the default limit.
+extern "C" int cda_b200_prefill_debug(int wait_limit_us, int withhold_first_k_arrive) {
+  cda::g_wait_limit_ns = wait_limit_us > 0 ? static_cast<unsigned long long>(wait_limit_us) * 1000ull : cda::umma::kWaitLimitNs;
+  cda::g_withhold_first_k = withhold_first_k_arrive ? 1 : 0;
+  return CDA_OK;
 }

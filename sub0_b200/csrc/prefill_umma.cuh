@@ -15,7 +15,8 @@ struct PrefillUmmaParams {
   const int32_t* seq_lens;
   const float* cb_k;
   const float* cb_v;
-  int* status;          // device status word or null (bit 0: bad block id, bit 2: a bounded wait gave up)
+  unsigned long long wait_limit_ns;   // limit of every mbarrier wait (set by the launcher)
+  int withhold_first_k;               // diagnostic: the producers keep back the first "K tile full" arrive
   int block_size, bs_shift, bt_stride, num_blocks;   // bs_shift: log2(block_size), or -1 if it is not a power of two
   int H_q, H_kv, group;
   float scale_log2;

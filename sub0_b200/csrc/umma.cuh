@@ -2,7 +2,7 @@
 // descriptors and the accumulator in tensor memory (TMEM), tcgen05.ld / st, TMEM allocation, mbarriers and the proxy
 // fences between ordinary shared-memory stores and the tensor core's reads.
 //
-// Every wait in this file is bounded: mbar_wait() gives up after a fixed number of polls and reports it, so a protocol
+// Every wait in this file is bounded: mbar_wait() gives up after a time limit and reports it, so a protocol
 // error ends the kernel with a status bit instead of a hang.
 #pragma once
 #include <cstdint>
@@ -37,18 +37,24 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
-// Wait for the phase with the given parity, for at most kWaitLimitNs (legitimate waits last microseconds).
-// `abort_flag` is a shared-memory word any role sets when it gave up; a waiter that sees it, or that runs out of
-// time, sets it and returns false.
+// Wait for the phase with the given parity, for at most `limit_ns` of the CTA's WaitState (legitimate waits last
+// microseconds; the default limit is kWaitLimitNs).  `abort` is set by any role that gave up; a waiter that sees it,
+// or that runs out of time, sets it and returns false.  The state lives in shared memory and is initialised by one
+// thread before the first wait.
 constexpr unsigned long long kWaitLimitNs = 50ull * 1000 * 1000;
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+struct WaitState {
+  int abort;
+  int pad;
+  unsigned long long limit_ns;
+};
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile WaitState* ws) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = global_timer_ns();
   for (uint32_t i = 1;; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 15u) == 0u && (*abort_flag || global_timer_ns() - t0 > kWaitLimitNs)) break;
+    if ((i & 15u) == 0u && (ws->abort || global_timer_ns() - t0 > ws->limit_ns)) break;
   }
-  *abort_flag = 1;
+  ws->abort = 1;
   return false;
 }
 

@@ -3,9 +3,10 @@
 * :func:`decode_hmma_v1`          -- wrappers.py:79-124
 * :func:`paged_encode_fused_cuda` -- wrappers.py:127-156
 
-Differences a caller can observe: the split-KV scratch is a caller-visible, grow-only workspace (optional
-``workspace=``) instead of an allocation inside the kernel call, so the call is CUDA-graph safe once warmed up; 2-bit
-codebooks (4 levels) select the low-bit slot layouts; GQA groups of 1..8 are accepted.
+Differences a caller can observe: the split-KV scratch is a caller-visible workspace (optional ``workspace=``, else a
+per-device cache that only grows and refuses to grow during a stream capture -- see ``sub0_b200.ops``) instead of an
+allocation inside the kernel call; 2-bit codebooks (4 levels) select the low-bit slot layouts; GQA groups of 1..8 are
+accepted.
 """
 from __future__ import annotations
 
@@ -20,9 +21,10 @@ from .hmma_loader import load_decode_hmma, load_paged_encode_fused
 
 
 def _choose_splits(max_seq_len: int, *, B: int = 1, H_kv: int = 8, device_idx: int = 0) -> int:
-    """Counterpart of ``_choose_tile_n`` (wrappers.py:41-76): the number of key-range splits the decode kernel will
-    use -- enough CTAs (one per SM, all KV heads of a key range each) for up to 8 full waves while every split keeps
-    >= 512 tokens.  There is no 256-split cap."""
+    """Counterpart of ``_choose_tile_n`` (wrappers.py:41-76): the number of partial results per output row the decode
+    kernel will produce.  The kernel cuts the concatenation of all sequences' keys into equal chunks, one CTA (all KV
+    heads of the chunk) per SM, never below 128 tokens per chunk; a sequence is merged from as many partials as chunks
+    it touches.  There is no 256-split cap."""
     return ops.plan_splits(B, H_kv, max_seq_len, device_idx)
 
 

@@ -2,7 +2,10 @@
 grow-only decode workspace, and calls ``libcda_b200.so``.  PyTorch is used for device memory and streams only.
 
 All functions enqueue on ``torch.cuda.current_stream()`` and never synchronise, so they may be captured in a CUDA
-graph (allocate the workspace beforehand by running once, or pass ``workspace=``).
+graph.  The split-KV workspace is either passed in (``workspace=``) or taken from a per-device cache that only grows;
+growing it frees the old buffer, so the cache refuses to grow while a stream capture is in progress (size it first with
+:func:`reserve_workspace` or by one eager call at the largest shape) -- a graph captured earlier keeps the pointer it
+was captured with.  The cache assumes one stream per device: calls on different streams that share it would race.
 """
 from __future__ import annotations
 
@@ -153,9 +156,19 @@ def _workspace(need: int, dev: torch.device, given: Optional[Tensor]) -> Tensor:
     key = (dev.type, dev.index if dev.index is not None else torch.cuda.current_device())
     ws = _WORKSPACES.get(key)
     if ws is None or ws.numel() < need:
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError(f"the cached decode workspace must grow to {need} bytes during a stream capture; call "
+                               "ops.reserve_workspace() (or run the largest shape once) before capturing, or pass workspace=")
         ws = new_workspace(need, dev)
         _WORKSPACES[key] = ws
     return ws
+
+
+def reserve_workspace(nbytes: int, device: Optional[torch.device] = None) -> Tensor:
+    """Grow the cached per-device workspace to at least ``nbytes`` now (e.g. for the largest batch and context a server
+    will see), so that later calls -- including captured ones -- never reallocate it."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    return _workspace(int(nbytes), dev, None)
 
 
 def workspace_status(workspace: Optional[Tensor] = None, device: Optional[torch.device] = None) -> int:
@@ -195,45 +208,54 @@ def _decode_args(Q, kv_cache, block_table, seq_lens, cb_K, cb_V, block_size, sca
 
 def decode(Q: Tensor, kv_cache: Tensor, block_table: Tensor, seq_lens: Tensor, output: Tensor, *, cb_K: Tensor,
            cb_V: Tensor, block_size: int, scale: Optional[float] = None, max_seq_len: Optional[int] = None,
-           num_splits: int = 0, workspace: Optional[Tensor] = None) -> None:
+           num_splits: int = 0, workspace: Optional[Tensor] = None, lse: Optional[Tensor] = None) -> None:
+    """``lse``: optional (B, H_q) fp32 buffer that receives the natural-log log-sum-exp of the scaled scores."""
     a = _decode_args(Q, kv_cache, block_table, seq_lens, cb_K, cb_V, block_size, scale, max_seq_len)
     if output.dtype != torch.float16:
         raise ValueError("decode requires an fp16 output buffer")
     if not output.is_cuda or output.shape != Q.shape or not output.is_contiguous():
         raise ValueError("output must be a contiguous CUDA tensor shaped like Q")
+    if lse is not None and (lse.dtype != torch.float32 or not lse.is_cuda or not lse.is_contiguous()
+                            or lse.numel() != a.B * a.Hq):
+        raise ValueError("lse must be a contiguous fp32 CUDA tensor of B * H_q elements")
     if a.B == 0:
         return
     need = decode_workspace_bytes(a.B, a.Hq, a.Hkv, a.max_len, num_splits)
     ws = _workspace(need, Q.device, workspace)
-    check(lib.cda_b200_decode(a.Q.data_ptr(), a.cache.data_ptr(), a.bt.data_ptr(), a.sl.data_ptr(), a.cbk.data_ptr(),
-                              a.cbv.data_ptr(), output.data_ptr(), ws.data_ptr(), ws.numel(), a.B, a.Hq, a.Hkv, a.bs,
-                              a.bt.shape[1], a.max_len, a.cache.shape[0], a.cache.shape[2], a.kb, a.vb, a.scale,
-                              num_splits, _stream(Q.device)))
+    if lse is None:
+        check(lib.cda_b200_decode(a.Q.data_ptr(), a.cache.data_ptr(), a.bt.data_ptr(), a.sl.data_ptr(), a.cbk.data_ptr(),
+                                  a.cbv.data_ptr(), output.data_ptr(), ws.data_ptr(), ws.numel(), a.B, a.Hq, a.Hkv, a.bs,
+                                  a.bt.shape[1], a.max_len, a.cache.shape[0], a.cache.shape[2], a.kb, a.vb, a.scale,
+                                  num_splits, _stream(Q.device)))
+    else:
+        check(lib.cda_b200_decode_lse(a.Q.data_ptr(), a.cache.data_ptr(), a.bt.data_ptr(), a.sl.data_ptr(),
+                                      a.cbk.data_ptr(), a.cbv.data_ptr(), output.data_ptr(), lse.data_ptr(), ws.data_ptr(),
+                                      ws.numel(), a.B, a.Hq, a.Hkv, a.bs, a.bt.shape[1], a.max_len, a.cache.shape[0],
+                                      a.cache.shape[2], a.kb, a.vb, a.scale, num_splits, _stream(Q.device)))
 
 
 def decode_partial(Q: Tensor, kv_cache: Tensor, block_table: Tensor, seq_lens: Tensor, *, cb_K: Tensor, cb_V: Tensor,
                    block_size: int, scale: Optional[float] = None, max_seq_len: Optional[int] = None,
                    num_splits: int = 0, workspace: Optional[Tensor] = None, out: Optional[Tensor] = None) -> Tensor:
     """Rotated-frame partial of the keys held in this cache, packed as (B, H_q, 130) fp32: 128 un-normalised O values,
-    then m (natural-log domain), then l.  One tensor so that a sequence-sharded rank sends a single message."""
+    then m (natural-log domain), then l.  One tensor so that a sequence-sharded rank sends a single message; the merge
+    kernel writes the packed rows directly (two launches in all)."""
     a = _decode_args(Q, kv_cache, block_table, seq_lens, cb_K, cb_V, block_size, scale, max_seq_len)
     need = decode_workspace_bytes(a.B, a.Hq, a.Hkv, a.max_len, num_splits)
-    rows = a.B * a.Hq
-    extra = rows * (HEAD_DIM + 2) * 4 + 256
-    ws = _workspace(need + extra, Q.device, workspace)
-    base = (need + 255) // 256 * 256
-    O = ws[base:base + rows * HEAD_DIM * 4].view(torch.float32).view(a.B, a.Hq, HEAD_DIM)
-    ml = ws[base + rows * HEAD_DIM * 4:base + rows * (HEAD_DIM + 2) * 4].view(torch.float32).view(2, a.B, a.Hq)
+    ws = _workspace(need, Q.device, workspace)
+    if out is None:
+        packed = torch.empty(a.B, a.Hq, HEAD_DIM + 2, dtype=torch.float32, device=Q.device)
+    else:
+        packed = out
+        if (packed.dtype != torch.float32 or not packed.is_cuda or not packed.is_contiguous()
+                or packed.numel() != a.B * a.Hq * (HEAD_DIM + 2)):
+            raise ValueError("out must be a contiguous fp32 CUDA tensor of B * H_q * 130 elements")
     if a.B:
-        check(lib.cda_b200_decode_partial(a.Q.data_ptr(), a.cache.data_ptr(), a.bt.data_ptr(), a.sl.data_ptr(),
-                                          a.cbk.data_ptr(), a.cbv.data_ptr(), O.data_ptr(), ml[0].data_ptr(),
-                                          ml[1].data_ptr(), ws.data_ptr(), need, a.B, a.Hq, a.Hkv, a.bs, a.bt.shape[1],
-                                          a.max_len, a.cache.shape[0], a.cache.shape[2], a.kb, a.vb, a.scale, num_splits,
-                                          _stream(Q.device)))
-    packed = torch.empty(a.B, a.Hq, HEAD_DIM + 2, dtype=torch.float32, device=Q.device) if out is None else out
-    packed[..., :HEAD_DIM].copy_(O)
-    packed[..., HEAD_DIM].copy_(ml[0])
-    packed[..., HEAD_DIM + 1].copy_(ml[1])
+        check(lib.cda_b200_decode_partial_packed(a.Q.data_ptr(), a.cache.data_ptr(), a.bt.data_ptr(), a.sl.data_ptr(),
+                                                 a.cbk.data_ptr(), a.cbv.data_ptr(), packed.data_ptr(), ws.data_ptr(),
+                                                 ws.numel(), a.B, a.Hq, a.Hkv, a.bs, a.bt.shape[1], a.max_len,
+                                                 a.cache.shape[0], a.cache.shape[2], a.kb, a.vb, a.scale, num_splits,
+                                                 _stream(Q.device)))
     return packed
 
 
@@ -248,12 +270,9 @@ def merge_partials(packed: Tensor, output: Tensor, *, unrotate: bool = True) -> 
     R = packed[0].numel() // (HEAD_DIM + 2)
     if output.numel() != R * HEAD_DIM:
         raise ValueError("output does not match the number of partial rows")
-    flat = packed.reshape(S, R, HEAD_DIM + 2)
-    O = flat[..., :HEAD_DIM].contiguous()
-    m = flat[..., HEAD_DIM].contiguous()
-    l = flat[..., HEAD_DIM + 1].contiguous()
-    check(lib.cda_b200_merge_partials(O.data_ptr(), m.data_ptr(), l.data_ptr(), S, R, output.data_ptr(),
-                                      1 if unrotate else 0, _stream(packed.device)))
+    flat = packed.contiguous()
+    check(lib.cda_b200_merge_partials_packed(flat.data_ptr(), S, R, output.data_ptr(), 1 if unrotate else 0,
+                                             _stream(packed.device)))
 
 
 def decode_scalar(Q: Tensor, kv_cache: Tensor, block_table: Tensor, seq_lens: Tensor, output: Tensor, *, cb_K: Tensor,
@@ -311,12 +330,34 @@ def prefill_varlen(Q: Tensor, kv_cache: Tensor, block_table: Tensor, cu_seqlens_
 
 
 def prefill_fault() -> bool:
-    """True if a CTA of the paged prefill kernel ever gave up on one of its bounded waits on the current device (its
-    rows of the output were then left unwritten, and later prefill launches return at once).  Synchronises the device."""
+    """True if a CTA of the paged prefill kernel gave up on one of its bounded waits on the current device since the
+    last :func:`prefill_clear_status` (its rows of the output were then left unwritten, and later prefill launches
+    return at once).  Synchronises the device."""
     rc = lib.cda_b200_prefill_fault()
     if rc < 0:
         check(rc)
     return rc != 0
+
+
+PREFILL_BAD_BLOCK, PREFILL_WAIT_GAVE_UP, PREFILL_QLEN_EXCEEDS_SEQLEN = 1, 4, 8
+
+
+def prefill_status() -> int:
+    """Sticky status bits of the paged prefill kernel on the current device (``PREFILL_*``).  Synchronises the device."""
+    rc = lib.cda_b200_prefill_status()
+    if rc < 0:
+        check(rc)
+    return rc
+
+
+def prefill_clear_status() -> None:
+    check(lib.cda_b200_prefill_clear_status())
+
+
+def prefill_debug(wait_limit_us: int = 0, withhold_first_k_arrive: bool = False) -> None:
+    """Diagnostic knobs of the following prefill launches (see ``cda_b200_prefill_debug``); call with no arguments to
+    restore the defaults."""
+    check(lib.cda_b200_prefill_debug(int(wait_limit_us), 1 if withhold_first_k_arrive else 0))
 
 
 def varlen_fwd_hadamard(Q: Tensor, k_rot: Tensor, v_rot: Tensor, output: Tensor, cu_seqlens_q: Tensor,

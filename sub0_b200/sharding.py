@@ -61,9 +61,53 @@ def decode_sequence_sharded(Q: Tensor, local_cache: Tensor, local_block_table: T
                             output: Tensor, *, cb_K: Tensor, cb_V: Tensor, block_size: int, local_max_seq_len: int,
                             scale: Optional[float] = None, group: Optional[dist.ProcessGroup] = None,
                             workspace: Optional[Tensor] = None) -> None:
-    """Decode one step when every rank holds a different key range of the same sequences.  ``Q`` (full, identical on
-    every rank) and ``output`` are (B, H_q, 128) fp16; ``local_*`` describe this rank's keys only."""
+    """Decode one step when every rank holds a different key range of the same sequences.  ``Q`` and ``output`` are
+    (B, H_q, 128) fp16; ``local_*`` describe this rank's keys only.
+
+    Precondition: ``Q`` is the SAME tensor on every rank of ``group`` (all query heads, replicated) -- the partial rows
+    of different ranks are merged row by row.  When the ranks hold different query heads (tensor parallelism inside the
+    group) use :func:`decode_context_parallel`, which exchanges the queries first."""
     from . import ops
     packed = ops.decode_partial(Q, local_cache, local_block_table, local_seq_lens, cb_K=cb_K, cb_V=cb_V,
                                 block_size=block_size, scale=scale, max_seq_len=local_max_seq_len, workspace=workspace)
     ops.merge_partials(gather_partials(packed, group), output)
+
+
+def gather_heads(q_local: Tensor, H_kv: int, group: Optional[dist.ProcessGroup] = None) -> Tensor:
+    """All-gather query heads over ``group``: every rank holds (n, H_kv * g_local, 128) -- its own g_local query heads of
+    each of the H_kv KV heads the group shares -- and receives (n, H_kv * world * g_local, 128) ordered
+    (KV head, rank, local head), i.e. KV head h again owns a contiguous run of world * g_local query heads."""
+    world = dist.get_world_size(group)
+    n, h_local, d = q_local.shape
+    g_local = h_local // H_kv
+    buf = torch.empty((world, n, h_local, d), dtype=q_local.dtype, device=q_local.device)
+    dist.all_gather_into_tensor(buf.view(-1), q_local.contiguous().view(-1), group=group)
+    return buf.view(world, n, H_kv, g_local, d).permute(1, 2, 0, 3, 4).reshape(n, H_kv * world * g_local, d).contiguous()
+
+
+def decode_context_parallel(q_local: Tensor, local_cache: Tensor, local_block_table: Tensor, local_seq_lens: Tensor,
+                            output_local: Tensor, *, cb_K: Tensor, cb_V: Tensor, block_size: int, local_max_seq_len: int,
+                            scale: Optional[float] = None, group: Optional[dist.ProcessGroup] = None,
+                            workspace: Optional[Tensor] = None) -> None:
+    """Decode step of a context-parallel group that sits inside a tensor-parallel group: the ranks share the same KV
+    heads, each holds its own slice of the query heads of those KV heads and its own part of every sequence's keys.
+
+    1. all-gather the queries along the head axis, so that every rank attends ALL of the group's query heads over its
+       own keys (the GQA group seen by the kernel becomes world * g_local, which must stay <= 8);
+    2. partial (O, m, l) rows of those heads over the local keys;
+    3. one all-gather of the packed partials, local log-sum-exp merge (cda/algorithm/attention.py:239-272);
+    4. keep this rank's query heads.
+    ``q_local`` / ``output_local``: (n, H_kv * g_local, 128) fp16."""
+    from . import ops
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    H_kv = local_cache.shape[-2]
+    n, h_local, d = q_local.shape
+    g_local = h_local // H_kv
+    if g_local * H_kv != h_local or g_local * world > 8:
+        raise NotImplementedError(f"context-parallel decode needs world * local GQA group <= 8 (got {world} x {g_local})")
+    q_all = gather_heads(q_local, H_kv, group)
+    packed = ops.decode_partial(q_all, local_cache, local_block_table, local_seq_lens, cb_K=cb_K, cb_V=cb_V,
+                                block_size=block_size, scale=scale, max_seq_len=local_max_seq_len, workspace=workspace)
+    out_all = torch.empty_like(q_all)
+    ops.merge_partials(gather_partials(packed, group), out_all)
+    output_local.copy_(out_all.view(n, H_kv, world, g_local, d)[:, :, rank].reshape(n, h_local, d))

@@ -83,6 +83,64 @@ def split_counts_from_query_start(query_start_loc, num_reqs: int, num_actual_tok
     return num_decodes, num_reqs - num_decodes, num_decode_tokens, num_actual_tokens - num_decode_tokens
 
 
+# ---- optional per-call timing (CDA_V2_TIME_STEPS=1) -----------------------------------------------------------------------
+# Same switch and output location as the reference's ``_time_call`` (``:115-296``): with CDA_V2_TIME_STEPS=1 every
+# backend call (cache update, decode, prefill, DCP decode) is bracketed by a host timer and -- outside stream capture -- a
+# pair of CUDA events; ``step_timing_summary()`` resolves the events, and the summary is written as JSON to
+# ``$CDA_V2_TIME_STEPS_OUT`` (default /tmp/cda_v2_step_timings) + ``.<pid>.json`` when the process exits.
+_STEP_TIMINGS: dict = {}
+
+
+def _time_steps_enabled() -> bool:
+    import os
+    return os.environ.get("CDA_V2_TIME_STEPS") == "1"
+
+
+def _time_call(label: str, fn):
+    """Run ``fn()``; when step timing is on, record its host time and (if the stream is not capturing) device time."""
+    if not _time_steps_enabled():
+        return fn()
+    import time
+    events = None
+    if torch.cuda.is_available() and not torch.cuda.is_current_stream_capturing():
+        events = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+        events[0].record()
+    t0 = time.perf_counter()
+    try:
+        return fn()
+    finally:
+        cpu_ms = (time.perf_counter() - t0) * 1e3
+        if events is not None:
+            events[1].record()
+        if not _STEP_TIMINGS:
+            import atexit
+            atexit.register(_dump_step_timings)
+        _STEP_TIMINGS.setdefault(label, []).append((cpu_ms, events))
+
+
+def step_timing_summary() -> dict:
+    """``{label: {calls, cpu_ms_mean, gpu_ms_mean, gpu_calls}}`` of the calls timed so far (synchronises the device)."""
+    if torch.cuda.is_available() and any(ev is not None for recs in _STEP_TIMINGS.values() for _, ev in recs):
+        torch.cuda.synchronize()
+    out = {}
+    for label, recs in _STEP_TIMINGS.items():
+        gpu = [ev[0].elapsed_time(ev[1]) for _, ev in recs if ev is not None]
+        out[label] = {"calls": len(recs), "cpu_ms_mean": sum(c for c, _ in recs) / len(recs),
+                      "gpu_ms_mean": (sum(gpu) / len(gpu)) if gpu else None, "gpu_calls": len(gpu)}
+    return out
+
+
+def _dump_step_timings() -> None:
+    import json
+    import os
+    try:
+        path = os.environ.get("CDA_V2_TIME_STEPS_OUT", "/tmp/cda_v2_step_timings") + f".{os.getpid()}.json"
+        with open(path, "w") as f:
+            json.dump({"pid": os.getpid(), "summary": step_timing_summary()}, f, indent=2)
+    except Exception:
+        pass
+
+
 _CODEBOOKS: dict = {}
 
 
@@ -265,7 +323,9 @@ def _build_backend_classes():
                 kv_cache[src_to_dists[:, 1]] = kv_cache[src_to_dists[:, 0]]
 
     class CDAv2AttentionImpl(AttentionImpl[CDAv2AttentionMetadata]):
-        can_return_lse_for_decode: bool = False
+        # The reference leaves this False (``:621``): its decode kernel cannot hand out the log-sum-exp.  Here the merge
+        # kernel writes it on request (``forward_decode_with_lse``), and the DCP path exchanges (O, m, l) itself.
+        can_return_lse_for_decode: bool = True
 
         def __init__(self, num_heads: int, head_size: int, scale: float, num_kv_heads: Optional[int] = None,
                      alibi_slopes: Optional[list] = None, sliding_window: Optional[int] = None, kv_cache_dtype: str = "auto",
@@ -299,7 +359,8 @@ def _build_backend_classes():
             nb, bs, hkv, w = cache.shape
             cb_K, cb_V = get_codebooks(cache.device)
             n = slot_mapping.shape[0]
-            paged_encode_fused_cuda(key[:n], value[:n], slot_mapping, cache.view(nb * bs, hkv, w), cb_K=cb_K, cb_V=cb_V)
+            _time_call("do_kv_cache_update", lambda: paged_encode_fused_cuda(
+                key[:n], value[:n], slot_mapping, cache.view(nb * bs, hkv, w), cb_K=cb_K, cb_V=cb_V))
 
         # -- attention ---------------------------------------------------------------------------------------------
         def forward(self, layer, query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, kv_cache: torch.Tensor,
@@ -319,22 +380,24 @@ def _build_backend_classes():
             if md.dcp_world_size > 1:
                 if md.max_query_len > 1:
                     raise NotImplementedError("CDA decode context parallelism covers decode steps only.")
-                self._forward_decode_dcp(q, cache, out, md)
+                _time_call("forward_decode_dcp", lambda: self._forward_decode_dcp(q, cache, out, md))
                 return output
             if md.max_query_len <= 1:
-                self._forward_decode(q, cache, out, md.block_table, md.seq_lens, md.max_seq_len)
+                _time_call("forward_decode", lambda: self._forward_decode(q, cache, out, md.block_table, md.seq_lens, md.max_seq_len))
                 return output
             nd, npf, nd_tok, np_tok = md.num_decodes, md.num_prefills, md.num_decode_tokens, md.num_prefill_tokens
             if nd + npf != md.num_reqs or nd_tok + np_tok != n:      # metadata built elsewhere: recount
                 nd, npf, nd_tok, np_tok = split_counts_from_query_start(md.query_start_loc, md.num_reqs, n, md.max_query_len)
             if nd_tok > 0:                                   # decodes come first in the batch
-                self._forward_decode(q[:nd_tok], cache, out[:nd_tok], md.block_table[:nd], md.seq_lens[:nd], md.max_seq_len)
+                _time_call("forward_decode", lambda: self._forward_decode(q[:nd_tok], cache, out[:nd_tok], md.block_table[:nd],
+                                                                          md.seq_lens[:nd], md.max_seq_len))
             if np_tok > 0:
                 cu = md.query_start_loc[nd: nd + npf + 1]
                 if nd_tok:
                     cu = cu - nd_tok
-                self._forward_prefill(q[nd_tok: nd_tok + np_tok], cache, out[nd_tok: nd_tok + np_tok], md.block_table[nd: nd + npf],
-                                      cu, md.seq_lens[nd: nd + npf], md.max_query_len, md.max_seq_len)
+                _time_call("forward_prefill", lambda: self._forward_prefill(
+                    q[nd_tok: nd_tok + np_tok], cache, out[nd_tok: nd_tok + np_tok], md.block_table[nd: nd + npf], cu,
+                    md.seq_lens[nd: nd + npf], md.max_query_len, md.max_seq_len))
             return output
 
         def _flat(self, cache: torch.Tensor):
@@ -352,6 +415,24 @@ def _build_backend_classes():
             if dst is not out:
                 out.copy_(dst)
 
+        def forward_decode_with_lse(self, query: torch.Tensor, kv_cache: torch.Tensor, attn_metadata):
+            """Decode step that also returns the log-sum-exp of the scaled scores: ``(out (n, H, 128) fp16, lse (n, H) fp32,
+            natural log)`` -- what ``can_return_lse_for_decode`` promises a caller that corrects the output across ranks
+            itself."""
+            from .. import ops
+
+            md = attn_metadata
+            cache = as_uint8_cache(kv_cache)
+            n = md.num_actual_tokens
+            q = query[:n].view(n, self.num_heads, HEAD_DIM).contiguous()
+            flat, bs = self._flat(cache)
+            cb_K, cb_V = get_codebooks(cache.device)
+            out = torch.empty_like(q)
+            lse = torch.empty(n, self.num_heads, dtype=torch.float32, device=q.device)
+            ops.decode(q, flat, md.block_table, md.seq_lens, out, cb_K=cb_K, cb_V=cb_V, block_size=bs, scale=self.scale,
+                       max_seq_len=int(md.max_seq_len), lse=lse)
+            return out, lse
+
         def _forward_prefill(self, q, cache, out, block_table, cu_seqlens_q, seq_lens, max_query_len, max_seq_len) -> None:
             from ..kernels_cuda.fa2_cda import fa2_cda_prefill_varlen_v1
 
@@ -366,16 +447,15 @@ def _build_backend_classes():
                 out.copy_(dst)
 
         def _forward_decode_dcp(self, q, cache, out, md) -> None:
-            """Decode with the keys of every sequence sharded over the DCP group: this rank's ``(O, m, l)`` rows over
-            its own shard, one all-gather, local merge (the split-KV contract of ``attention_partial_reference`` /
-            ``merge_partials``, cda/algorithm/attention.py:190-272)."""
-            from .. import ops
-            from ..sharding import gather_partials
+            """Decode with the keys of every sequence sharded over the DCP group.  The group lies inside the
+            tensor-parallel group: its ranks share this rank's KV heads but hold different query heads, so the queries are
+            all-gathered along the head axis first; then this rank's ``(O, m, l)`` rows over its own key shard, one
+            all-gather, local merge (the split-KV contract of ``attention_partial_reference`` / ``merge_partials``,
+            cda/algorithm/attention.py:190-272), and this rank keeps its own heads."""
+            from ..sharding import decode_context_parallel
 
             flat, bs = self._flat(cache)
             cb_K, cb_V = get_codebooks(cache.device)
-            packed = ops.decode_partial(q.contiguous(), flat, md.block_table, md.seq_lens, cb_K=cb_K, cb_V=cb_V, block_size=bs,
-                                        scale=self.scale, max_seq_len=int(md.max_seq_len))
             group = None
             try:
                 from vllm.distributed.parallel_state import get_dcp_group
@@ -383,9 +463,9 @@ def _build_backend_classes():
                 group = get_dcp_group().device_group
             except Exception:
                 group = None                                 # plain torch.distributed default group (tests)
-            gathered = gather_partials(packed, group=group)
             dst = out if out.is_contiguous() else torch.empty_like(q)
-            ops.merge_partials(gathered, dst)
+            decode_context_parallel(q.contiguous(), flat, md.block_table, md.seq_lens, dst, cb_K=cb_K, cb_V=cb_V,
+                                    block_size=bs, local_max_seq_len=int(md.max_seq_len), scale=self.scale, group=group)
             if dst is not out:
                 out.copy_(dst)
 

@@ -64,22 +64,48 @@ def oracle_decode(case):
                           k_bits=case["k_bits"], v_bits=case["v_bits"])
 
 
-def close(got: torch.Tensor, want: torch.Tensor, rtol=2e-3, atol=1e-3, strict_rows=None):
-    """(ok, worst violation ratio, cosine) of fp16 attention outputs (..., 128) against the oracle.
+RTOL, ATOL = 2e-3, 1e-3          # the tolerance stated for this path: |got - want| <= 1e-3 + 2e-3 |want| on fp16 outputs
 
-    Three conditions, all with the tolerance stated for this path (atol 1e-3, rtol 2e-3):
+STATS = []                         # one record per comparison of this session (written out by conftest on request)
+
+
+def violations(got: torch.Tensor, want: torch.Tensor, rtol=RTOL, atol=ATOL):
+    """(number of elements outside |got - want| <= atol + rtol |want|, worst |err| / bound, number of elements)."""
+    g, w = got.float().cpu(), want.float().cpu()
+    if g.numel() == 0:
+        return 0, 0.0, 0
+    ratio = (g - w).abs() / (atol + rtol * w.abs())
+    return int((ratio > 1.0).sum()), float(ratio.max()), g.numel()
+
+
+def strict(got: torch.Tensor, want: torch.Tensor, what: str = ""):
+    """The stated tolerance, element-wise, no exceptions: returns (ok, count of violating elements, worst ratio, cosine)."""
+    g, w = got.float().cpu(), want.float().cpu()
+    bad, worst, n = violations(g, w)
+    cos = float(torch.nn.functional.cosine_similarity(g.flatten(), w.flatten(), dim=0)) if n else 1.0
+    STATS.append({"what": what, "form": "strict", "elements": n, "violations": bad, "worst_ratio": worst, "cosine": cos})
+    return bad == 0, bad, worst, cos
+
+
+def close(got: torch.Tensor, want: torch.Tensor, rtol=RTOL, atol=ATOL, strict_rows=None, max_bad_frac=1e-2, what: str = ""):
+    """(ok, worst violation ratio, cosine) of fp16 attention outputs (..., 128) against the oracle -- the ROW-MAX form,
+    used only where the element-wise bound cannot hold for reasons outside the kernel (see below); every case with
+    N >= 4096 and every benchmark shape is checked with :func:`strict` instead.
+
+    Three conditions, with the tolerance stated for this path (atol 1e-3, rtol 2e-3):
       1. every element:              |got - want| <= atol + rtol * max|want_row| + ulp16(max|want_row|)
          (outputs are fp16: one unit in the last place of the row's largest value is the storage granularity)
-      2. at least 99 % of elements:   |got - want| <= atol + rtol * |want|            (element-wise)
-      3. rows whose largest |want| is below 0.25, and rows selected by ``strict_rows``: condition 2 for EVERY element.
+      2. at most ``max_bad_frac`` of the elements break the element-wise bound |got - want| <= atol + rtol * |want|
+      3. rows whose largest |want| is below 0.25, and rows selected by ``strict_rows``: the element-wise bound for EVERY
+         element.
 
-    Why not condition 2 everywhere: the reference algorithm rounds the rotated-frame output to fp16 and then applies
-    the inverse Hadamard transform, which spreads the rounding noise of the largest coordinates evenly over all 128
-    outputs of the row.  When the softmax is peaked (few keys, or the x8 outlier channels of the benchmark recipe) the
-    row holds values of magnitude ~1, one fp16 ulp is ~1e-3, and that noise alone reaches 1.5e-3 on elements that happen
-    to be near zero: two correct implementations -- e.g. the oracle itself evaluated in a different summation order --
-    then differ by more than atol on a few elements.  Where the row is small (< 0.25, i.e. fp16 ulp <= 1.2e-4) the
-    element-wise bound is enforced without exception."""
+    Why the element-wise bound is not demanded everywhere: the reference algorithm rounds the rotated-frame output to
+    fp16 and then applies the inverse Hadamard transform, which spreads the rounding noise of the largest coordinates
+    evenly over all 128 outputs of the row.  When the softmax is peaked (a handful of keys, or the x8 outlier channels of
+    the benchmark recipe at short context) the row holds values of magnitude ~1, one fp16 ulp is ~1e-3, and that noise
+    uses up most of the 1e-3 budget on elements that happen to be near zero; the kernel's own rounding (fp16 table
+    entries, fp16 P * norm_V) then tips a few of them over.  Where the row is small (< 0.25, i.e. fp16 ulp <= 1.2e-4)
+    the element-wise bound is enforced without exception.  The number of violating elements is recorded in ``STATS``."""
     g, w = got.float().cpu(), want.float().cpu()
     if g.numel() == 0:
         return True, 0.0, 1.0
@@ -88,8 +114,9 @@ def close(got: torch.Tensor, want: torch.Tensor, rtol=2e-3, atol=1e-3, strict_ro
     ulp16 = torch.exp2(torch.floor(torch.log2(rowmax.clamp_min(2.0 ** -14))) - 10)
     ratio = float((err / (atol + rtol * rowmax + ulp16)).max())              # condition 1
     elem = err / (atol + rtol * w.abs())
-    frac_bad = float((elem > 1.0).float().mean())
-    if frac_bad > 1e-2:                                                       # condition 2
+    n_bad = int((elem > 1.0).sum())
+    frac_bad = n_bad / g.numel()
+    if frac_bad > max_bad_frac:                                               # condition 2
         ratio = max(ratio, 1.0 + frac_bad)
     mask = (rowmax.squeeze(-1) < 0.25)
     if strict_rows is not None:
@@ -97,4 +124,6 @@ def close(got: torch.Tensor, want: torch.Tensor, rtol=2e-3, atol=1e-3, strict_ro
     if bool(mask.any()):
         ratio = max(ratio, float(elem[mask].max()))                          # condition 3
     cos = float(torch.nn.functional.cosine_similarity(g.flatten(), w.flatten(), dim=0))
+    STATS.append({"what": what, "form": "row-max", "elements": g.numel(), "violations": n_bad,
+                  "worst_ratio": float(elem.max()), "row_ratio": ratio, "cosine": cos})
     return ratio <= 1.0, ratio, cos

@@ -23,3 +23,20 @@ def golden():
         with np.load(GOLDEN / f"{name}.npz") as z:
             return {k: z[k] for k in z.files}
     return load
+
+
+def pytest_sessionfinish(session, exitstatus):
+    """With CDA_PARITY_STATS=<file> every output comparison of the session (elements, elements outside the stated
+    tolerance, worst error / bound, cosine) is written to that file as JSON lines."""
+    import json
+    import os
+    path = os.environ.get("CDA_PARITY_STATS")
+    if not path:
+        return
+    try:
+        from tests import _cases
+    except Exception:
+        return
+    with open(path, "w") as f:
+        for rec in _cases.STATS:
+            f.write(json.dumps(rec) + "\n")

@@ -1,5 +1,10 @@
 """GPU parity of the decode path against the CPU oracle, through the reference-shaped wrappers and the C ABI.
-Tolerance: |got - want| <= 1e-3 + 2e-3 |want| on fp16 outputs, and cosine >= 0.9999 (the reference's stated bar)."""
+
+Tolerance: |got - want| <= 1e-3 + 2e-3 |want| on every fp16 output element (``tests/_cases.strict``: zero violations
+allowed) for every sequence of at least 4096 tokens -- the benchmark shapes -- and cosine >= 0.9999 (the reference's
+stated bar) everywhere.  Shorter sequences, where a peaked softmax makes the reference's own fp16 rounding of the
+rotated output eat the absolute budget, are held to the row-max form of the same bound (``tests/_cases.close``) with the
+share of elements outside the element-wise bound capped at a measured figure."""
 import pytest
 import torch
 
@@ -36,11 +41,23 @@ def run_scalar(case):
     return out.cpu()
 
 
+STRICT_FROM = 4096        # sequences at least this long must meet the stated tolerance on every element
+MAX_BAD_FRAC = 5e-3       # short sequences: cap on the share of elements outside the element-wise bound
+
+
 def assert_close(got, want, what="", seq_lens=None):
-    """Tolerance: see ``tests/_cases.close``.  ``seq_lens`` is accepted for readability of the call sites only."""
-    ok, ratio, cos = Cs.close(got, want)
+    """Rows of sequences with >= STRICT_FROM tokens: ``Cs.strict`` (no element may break 1e-3 + 2e-3 |want|); the other
+    rows: ``Cs.close`` (row-max form).  Without ``seq_lens`` every row takes the row-max form."""
     assert not bool(got.isnan().any()), f"{what}: NaN in output"
-    assert ok and cos >= 0.9999, f"{what}: worst error/tolerance {ratio:.3f}, cosine {cos:.6f}"
+    long_rows = [b for b, n in enumerate(seq_lens or []) if n >= STRICT_FROM]
+    short_rows = [b for b in range(got.shape[0]) if b not in long_rows] if seq_lens is not None else None
+    if long_rows:
+        ok, bad, worst, cos = Cs.strict(got[long_rows], want[long_rows], what)
+        assert ok and cos >= 0.9999, f"{what}: {bad} elements outside 1e-3 + 2e-3|want| (worst x{worst:.2f}), cosine {cos:.6f}"
+    rest_g, rest_w = (got, want) if short_rows is None else (got[short_rows], want[short_rows])
+    if rest_g.numel():
+        ok, ratio, cos = Cs.close(rest_g, rest_w, max_bad_frac=MAX_BAD_FRAC, what=what)
+        assert ok and cos >= 0.9999, f"{what}: worst error/tolerance {ratio:.3f}, cosine {cos:.6f}"
 
 
 @pytest.mark.parametrize("n", [1, 15, 16, 17, 31, 257])
@@ -98,7 +115,7 @@ def test_decode_golden_fixture(golden):
         case = dict(Q=T(g["Q"])[:, :, 0].contiguous(), cache=cache, block_table=bt,
                     seq_lens=torch.full((B,), N, dtype=torch.int32), cb_K=T(g["cb_K"]), cb_V=T(g["cb_V"]), group=grp,
                     block_size=bs)
-        assert_close(run_decode(case), T(g["out"])[:, :, 0], name)
+        assert_close(run_decode(case), T(g["out"])[:, :, 0], name, [N] * B)
 
 
 def test_decode_partial_and_merge(golden):
@@ -212,6 +229,7 @@ def test_decode_cuda_graph_replay():
     assert_close(out.cpu(), want, "graph replay", [2048, 2048])
 
 
+
 def test_decode_full_size_properties():
     """At the benchmark's context length (N = 65536, all 8 KV heads, GQA 4) the CPU oracle is too slow for a full compare;
     check size-independent properties instead: (1) the result does not depend on the split count, (2) it agrees with the
@@ -239,12 +257,62 @@ def test_decode_full_size_properties():
     merged = torch.full_like(wl.Q, float("nan"))
     ops.merge_partials(torch.stack(halves), merged)
     torch.cuda.synchronize()
-    assert_close(forced.cpu(), planned.cpu(), "split count")
-    assert_close(planned.cpu(), scalar.cpu(), "scalar kernel")
-    assert_close(merged.cpu(), planned.cpu(), "merge of two key ranges")
+    assert_close(forced.cpu(), planned.cpu(), "split count", [N] * B)
+    assert_close(planned.cpu(), scalar.cpu(), "scalar kernel", [N] * B)
+    assert_close(merged.cpu(), planned.cpu(), "merge of two key ranges", [N] * B)
     b = 1
     rows = wl.block_table[b].long()
     slot_ids = (rows[:, None] * 16 + torch.arange(16, device=DEV)[None, :]).flatten()
     want = O.paged_decode(wl.Q[b:b + 1].cpu(), wl.cache[slot_ids].cpu(), torch.arange(N // 16, dtype=torch.int32)[None],
                           torch.tensor([N], dtype=torch.int32), cb_K=wl.cb_K.cpu(), cb_V=wl.cb_V.cpu(), group=4, block_size=16)
-    assert_close(planned[b:b + 1].cpu(), want, "one sequence vs the oracle")
+    assert_close(planned[b:b + 1].cpu(), want, "one sequence vs the oracle", [N])
+
+
+@pytest.mark.parametrize("kb,vb", [(4, 4), (4, 2), (2, 2)])
+@pytest.mark.parametrize("B,N", [(1, 4096), (4, 4096), (1, 16384), (4, 16384)])
+def test_decode_low_bit_grid_vs_oracle(kb, vb, B, N):
+    """The parity cells of the decode sweep (Mistral-7B geometry: 32 query heads, 8 KV heads): every output element of
+    k4v4, k4v2 and k2v2 within 1e-3 + 2e-3 |want| of the oracle (cda/algorithm/attention.py:426-482)."""
+    case = Cs.paged_case([N] * B, H_kv=8, group=4, k_bits=kb, v_bits=vb, seed=1000 + kb * 10 + vb + B + N)
+    assert_close(run_decode(case), Cs.oracle_decode(case), f"k{kb}v{vb} B={B} N={N}", [N] * B)
+
+
+def test_decode_llama70b_geometry_vs_oracle():
+    """64 query heads / 8 KV heads (GQA 8), one KV head per rank as under 8-way head sharding, and all eight together."""
+    case = Cs.paged_case([4096, 5000], H_kv=8, group=8, seed=77)
+    assert_close(run_decode(case), Cs.oracle_decode(case), "g8 H_kv=8", [4096, 5000])
+    one = Cs.paged_case([8192, 4096, 4100], H_kv=1, group=8, seed=78)
+    assert_close(run_decode(one), Cs.oracle_decode(one), "g8 H_kv=1", [8192, 4096, 4100])
+
+
+def test_decode_chunks_straddle_sequences():
+    """Many sequences of very different lengths: the planned chunks of the key line start and end in the middle of
+    sequences, skip empty ones and cover several short ones at once."""
+    lens = [5, 4096, 0, 33, 700, 16, 4500, 1, 0, 2047, 129, 64]
+    case = Cs.paged_case(lens, H_kv=8, group=4, seed=79)
+    want = Cs.oracle_decode(case)
+    got = run_decode(case)
+    assert_close(got, want, "ragged batch of 12", lens)
+    assert bool((got[2] == 0).all()) and bool((got[8] == 0).all())
+    for splits in (1, 3, 300):
+        assert_close(run_decode(case, num_splits=splits), want, f"ragged batch, {splits} ranges per sequence", lens)
+
+
+def test_decode_returns_lse():
+    """Log-sum-exp of the scaled scores (natural log) next to the output: against the oracle's partial (m + log l)."""
+    from sub0_b200 import ops
+    case = Cs.paged_case([1000, 0, 4096], H_kv=4, group=4, seed=80)
+    d = to_dev(case)
+    out = torch.empty_like(d["Q"])
+    lse = torch.full((3, 16), float("nan"), device=DEV)
+    ops.decode(d["Q"], d["cache"], d["block_table"], d["seq_lens"], out, cb_K=d["cb_K"], cb_V=d["cb_V"], block_size=16,
+               max_seq_len=4096, lse=lse)
+    torch.cuda.synchronize()
+    assert_close(out.cpu(), Cs.oracle_decode(case), "decode with lse", [1000, 0, 4096])
+    H = O.sylvester_hadamard()
+    for b, n in ((0, 1000), (2, 4096)):
+        Ks, Vs = O.gather_sequence(case["cache"], case["block_table"][b], n, 16)
+        Qr = O.rotate(case["Q"][b][None, :, None, :], H)
+        _, m, l = O.cda_partial_rotated(Qr, Ks, Vs, cb_K=case["cb_K"], cb_V=case["cb_V"], group=4)
+        torch.testing.assert_close(lse[b].cpu(), (m + l.log())[0, :, 0], rtol=1e-4, atol=2e-3)
+    assert bool((lse[1] == float("-inf")).all())

@@ -61,21 +61,33 @@ def _rank_main(rank, world, port, q):
                                 local_max_seq_len=max(local_max, 1))
         torch.cuda.synchronize()
         ok, ratio, cos = Cs.close(out.cpu(), want)
-        # --- the same shards through the vLLM backend's decode-context-parallel path (gathers over the default group)
+        # --- the vLLM backend's decode-context-parallel path (gathers over the default group).  The DCP group lies inside
+        # the tensor-parallel group: both ranks share the two KV heads, each holds FOUR of the eight query heads of every
+        # KV head (distinct queries per rank) and its own key range of every sequence.
         from sub0_b200.vllm_integration.cda_attn_v2 import get_backend_classes
         _, Impl, _, Metadata = get_backend_classes()
-        impl = Impl(16, 128, 128 ** -0.5, num_kv_heads=4)
-        slots, hkv, w = case["cache"].shape
-        kv = case["cache"].view(slots // 16, 16, hkv, w).contiguous().to(dev).view(torch.float16)
+        case2 = Cs.paged_case([1000, 333], H_kv=2, group=8, seed=6, shuffle=False, extra_blocks=0)
+        want2 = Cs.oracle_decode(case2).view(2, 2, world, 4, 128)[:, :, rank].reshape(2, 8, 128)
+        q_local = case2["Q"].view(2, 2, world, 4, 128)[:, :, rank].reshape(2, 8 * 128).contiguous()
+        bt_rows = []
+        for b, n in enumerate([1000, 333]):
+            t0, t1 = sequence_shard(rank, world, n, 16)
+            bt_rows.append(case2["block_table"][b, t0 // 16:-(-t1 // 16)] if t1 > t0 else case2["block_table"][b, :0])
+        bt2 = torch.zeros(2, width, dtype=torch.int32)
+        for b, r in enumerate(bt_rows):
+            bt2[b, :len(r)] = r
+        impl = Impl(8, 128, 128 ** -0.5, num_kv_heads=2)
+        slots, hkv, w = case2["cache"].shape
+        kv = case2["cache"].view(slots // 16, 16, hkv, w).contiguous().to(dev).view(torch.float16)
         md = Metadata(num_actual_tokens=2, num_reqs=2, max_query_len=1, max_seq_len=max(local_max, 1),
                       query_start_loc=torch.tensor([0, 1, 2], dtype=torch.int32, device=dev),
-                      seq_lens=torch.tensor(lens, dtype=torch.int32, device=dev), block_table=bt.to(dev),
+                      seq_lens=torch.tensor(lens, dtype=torch.int32, device=dev), block_table=bt2.to(dev),
                       slot_mapping=torch.zeros(2, dtype=torch.int64, device=dev), dcp_world_size=world, dcp_rank=rank,
                       num_decodes=2, num_decode_tokens=2)
-        out2 = torch.empty(2, 16 * 128, dtype=torch.float16, device=dev)
-        impl.forward(None, case["Q"].to(dev).view(2, -1), None, None, kv, md, output=out2)
+        out2 = torch.empty(2, 8 * 128, dtype=torch.float16, device=dev)
+        impl.forward(None, q_local.to(dev), None, None, kv, md, output=out2)
         torch.cuda.synchronize()
-        ok2, ratio2, _ = Cs.close(out2.view(2, 16, 128).cpu(), want)
+        ok2, ratio2, _ = Cs.close(out2.view(2, 8, 128).cpu(), want2)
         q.put((rank, same, ok and ok2, max(ratio, ratio2)))
     except Exception as exc:
         q.put((rank, False, False, repr(exc)))

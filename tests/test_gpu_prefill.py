@@ -1,4 +1,8 @@
-"""GPU parity of the prefill path (dense loader, fused causal varlen attention) against the CPU oracle."""
+"""GPU parity of the prefill path (dense loader, fused causal varlen attention) against the CPU oracle.
+
+Tolerance: query rows that see at least 4096 keys must meet |got - want| <= 1e-3 + 2e-3 |want| on every element
+(``tests/_cases.strict``); rows with fewer visible keys -- the first tokens of a prompt, where the softmax is peaked --
+take the row-max form of the same bound (``tests/_cases.close``).  Cosine >= 0.9999 everywhere."""
 import pytest
 import torch
 
@@ -18,11 +22,21 @@ def visible_keys(q_lens, seq_lens):
     return torch.cat([torch.arange(q) + (n - q) + 1 for q, n in zip(q_lens, seq_lens)])
 
 
+STRICT_FROM = 4096
+MAX_BAD_FRAC = 5e-3
+
+
 def assert_close(got, want, what="", keys=None):
-    """Tolerance: see ``tests/_cases.close``."""
-    ok, ratio, cos = Cs.close(got, want)
+    """``keys``: number of keys each query row sees; rows with >= STRICT_FROM keys are checked element-wise with no
+    exception, the others in the row-max form (see the module docstring)."""
     assert not bool(got.isnan().any()), f"{what}: NaN in output"
-    assert ok and cos >= 0.9999, f"{what}: worst error/tolerance {ratio:.3f}, cosine {cos:.6f}"
+    long_rows = keys >= STRICT_FROM if keys is not None else torch.zeros(got.shape[0], dtype=torch.bool)
+    if bool(long_rows.any()):
+        ok, bad, worst, cos = Cs.strict(got[long_rows], want[long_rows], what)
+        assert ok and cos >= 0.9999, f"{what}: {bad} elements outside 1e-3 + 2e-3|want| (worst x{worst:.2f}), cosine {cos:.6f}"
+    if bool((~long_rows).any()):
+        ok, ratio, cos = Cs.close(got[~long_rows], want[~long_rows], max_bad_frac=MAX_BAD_FRAC, what=what)
+        assert ok and cos >= 0.9999, f"{what}: worst error/tolerance {ratio:.3f}, cosine {cos:.6f}"
 
 
 def prefill_inputs(case, q_lens, seed):
@@ -203,10 +217,86 @@ def test_large_ragged_prefill_matches_the_dense_route(group, H_kv):
     fa2_cda.fa2_cda_prefill_varlen_v1(Q2.to(DEV), cache, bt, cu2.to(DEV), sl, out2, cb_K=cb, cb_V=cb, group_size=group, block_size=16,
                                       max_query_len=max(q2), max_seq_len=max(lens), fuse_fa2_epilogue=True)
     torch.cuda.synchronize()
-    assert_close(out2.cpu(), want, f"long past g{group}")
+    assert_close(out2.cpu(), want, f"long past g{group}", visible_keys(q2, lens))
+
+
+def run_prefill(case, Q, cu, q_lens, **kw):
+    from sub0_b200.kernels_cuda.fa2_cda import fa2_cda_prefill_varlen_v1
+    d = to_dev(case)
+    out = torch.full_like(Q, float("nan"), device=DEV)
+    fa2_cda_prefill_varlen_v1(Q.to(DEV), d["cache"], d["block_table"], cu.to(DEV), d["seq_lens"], out, cb_K=d["cb_K"],
+                              cb_V=d["cb_V"], group_size=case["group"], block_size=case["block_size"],
+                              max_query_len=max(q_lens), max_seq_len=int(case["seq_lens"].max()), fuse_fa2_epilogue=True, **kw)
+    torch.cuda.synchronize()
+    return out.cpu()
+
+
+def test_whole_long_prompt_vs_oracle():
+    """One prompt of the length the prefill benchmark draws (512 .. 8192 tokens; here 6200, not a multiple of the tile
+    sizes) for one KV head and its four query heads, every row against the oracle
+    (attention_compressed(causal=True), cda/algorithm/attention.py:426-482)."""
+    lens = [6200]
+    case = Cs.paged_case(lens, H_kv=1, group=4, seed=2718)
+    Q, cu = prefill_inputs(case, lens, 9)
+    want = O.paged_prefill(Q, case["cache"], case["block_table"], cu, case["seq_lens"], cb_K=case["cb_K"], cb_V=case["cb_V"],
+                           group=4, block_size=16)
+    assert_close(run_prefill(case, Q, cu, lens), want, "whole 6200-token prompt", visible_keys(lens, lens))
+
+
+def test_prefill_input_errors_set_status_not_fault():
+    """A block id outside the cache is replaced by block 0 and reported; a sequence with more new tokens than tokens is
+    skipped and reported.  Neither forms a bad address."""
+    from sub0_b200 import ops
+    ops.prefill_clear_status()
+    lens = [200]
+    case = Cs.paged_case(lens, H_kv=2, group=4, seed=161)
+    Q, cu = prefill_inputs(case, lens, 3)
+    bad = dict(case)
+    bad["block_table"] = case["block_table"].clone()
+    bad["block_table"][0, 3] = 9_999_999
+    out = run_prefill(bad, Q, cu, lens)
+    assert ops.prefill_status() & ops.PREFILL_BAD_BLOCK
+    assert not bool(out.isnan().any())
+    ops.prefill_clear_status()
+    assert ops.prefill_status() == 0
+    short = dict(case)
+    short["seq_lens"] = torch.tensor([150], dtype=torch.int32)          # 200 new tokens in a sequence of 150
+    out = run_prefill(short, Q, cu, lens)
+    assert ops.prefill_status() & ops.PREFILL_QLEN_EXCEEDS_SEQLEN
+    assert bool(out.isnan().all())                                       # rows left as they were
+    ops.prefill_clear_status()
+    want = O.paged_prefill(Q, case["cache"], case["block_table"], cu, case["seq_lens"], cb_K=case["cb_K"], cb_V=case["cb_V"],
+                           group=4, block_size=16)
+    assert_close(run_prefill(case, Q, cu, lens), want, "after the status was cleared")
+    assert ops.prefill_status() == 0
 
 
 def test_zz_no_wait_gave_up():
-    """Collected after the prefill tests of this file: none of the kernel's bounded waits may have run out."""
+    """Collected after the parity tests of this file: none of the kernel's bounded waits may have run out."""
     from sub0_b200 import ops
     assert ops.prefill_fault() is False
+
+
+def test_zz_wait_that_runs_out_ends_the_kernel_cleanly():
+    """The give-up path of the bounded waits, exercised without faulting anything: with the wait limit cut to 300 us and
+    one "K tile ready" signal held back, the MMA and softmax roles of a one-CTA launch run out of time, the CTA ends,
+    releases its tensor memory and raises the fault flag.  After the flag is cleared the next launch works."""
+    from sub0_b200 import ops
+    lens = [100]
+    case = Cs.paged_case(lens, H_kv=1, group=4, seed=162)
+    Q, cu = prefill_inputs(case, lens, 4)
+    want = O.paged_prefill(Q, case["cache"], case["block_table"], cu, case["seq_lens"], cb_K=case["cb_K"], cb_V=case["cb_V"],
+                           group=4, block_size=16)
+    ops.prefill_clear_status()
+    try:
+        ops.prefill_debug(wait_limit_us=300, withhold_first_k_arrive=True)
+        run_prefill(case, Q, cu, lens)                                   # returns: every wait is bounded
+        assert ops.prefill_fault() is True
+        assert ops.prefill_status() & ops.PREFILL_WAIT_GAVE_UP
+        flagged = run_prefill(case, Q, cu, lens)                         # flag still up: launches return at once
+        assert bool(flagged.isnan().all())
+    finally:
+        ops.prefill_debug()
+        ops.prefill_clear_status()
+    assert ops.prefill_fault() is False
+    assert_close(run_prefill(case, Q, cu, lens), want, "launch after a wait gave up")   # TMEM was released: this CTA allocates all 512 columns

@@ -84,6 +84,28 @@ def test_status_codes_without_gpu(lib):
                                      None) == lib.CDA_ERR_BAD_SHAPE
     assert L.cda_b200_cache_to_dense_rotated(al, al, al, al, al, al, al, 1, 8, 16, 4, 64, 64, 100, 4, 4,
                                              None) == lib.CDA_ERR_BAD_SHAPE
+    # alignment contracts: the tcgen05 prefill kernel moves Q / out in 16-byte pieces, the scalar decode and the dense
+    # loader store 8 bytes at a time -- a misaligned pointer is refused before any launch
+    pf = lambda q, o: L.cda_b200_prefill_varlen(q, al, al, al, al, al, al, o, 8, 1, 32, 8, 16, 4, 8, 64, 64, 144, 4, 4, 0.1, None)
+    assert pf(al + 8, al) == lib.CDA_ERR_BAD_ALIGN
+    assert pf(al, al + 8) == lib.CDA_ERR_BAD_ALIGN
+    assert "16-byte" in lib.last_error()
+    assert L.cda_b200_decode_scalar(al, al, al, al, al, al, al + 4, 1, 32, 8, 16, 4, 64, 144, 4, 4, 0.1,
+                                    None) == lib.CDA_ERR_BAD_ALIGN
+    assert L.cda_b200_cache_to_dense_rotated(al, al, al, al, al, al + 4, al, 1, 8, 16, 4, 64, 64, 144, 4, 4,
+                                             None) == lib.CDA_ERR_BAD_ALIGN
+    assert L.cda_b200_cache_to_dense_rotated(al, al, al, al, al, al, al + 4, 1, 8, 16, 4, 64, 64, 144, 4, 4,
+                                             None) == lib.CDA_ERR_BAD_ALIGN
+    # packed partials and log-sum-exp variants share the decode validation
+    assert L.cda_b200_decode_partial_packed(al, al, al, al, al, al, al + 4, al, 1 << 20, 1, 32, 8, 16, 4, 64, 64, 144, 4, 4,
+                                            0.1, 0, None) == lib.CDA_ERR_BAD_ALIGN
+    assert L.cda_b200_decode_partial_packed(al, al, al, al, al, al, None, al, 1 << 20, 1, 32, 8, 16, 4, 64, 64, 144, 4, 4,
+                                            0.1, 0, None) == lib.CDA_ERR_BAD_ARG
+    assert L.cda_b200_decode_lse(al, al, al, al, al, al, al, None, al, 1 << 20, 1, 32, 8, 16, 4, 64, 64, 144, 4, 4, 0.1, 0,
+                                 None) == lib.CDA_ERR_BAD_ARG
+    assert L.cda_b200_merge_partials_packed(al, 0, 4, al, 1, None) == lib.CDA_ERR_BAD_ARG
+    assert L.cda_b200_merge_partials_packed(al + 4, 2, 4, al, 1, None) == lib.CDA_ERR_BAD_ALIGN
+    assert L.cda_b200_prefill_debug(0, 0) == lib.CDA_OK
 
 
 def test_split_planning_properties(lib):
@@ -95,10 +117,12 @@ def test_split_planning_properties(lib):
         ws = L.cda_b200_decode_workspace_bytes(B, Hkv * 4, Hkv, n, 0, -1)
         assert ws == 256 + s * B * Hkv * 4 * 130 * 4       # one partial row of 128 + 2 floats per split and query head
         assert L.cda_b200_decode_workspace_bytes(B, Hkv * 4, Hkv, n, 3, -1) <= 256 + 3 * B * Hkv * 4 * 520
-    assert L.cda_b200_decode_plan_splits(32, 8, 65536, -1) == 9       # 288 CTAs: two rounds of 148 SMs, 97 % full
-    assert L.cda_b200_decode_plan_splits(4, 8, 65536, -1) == 37       # 148 CTAs: exactly one round
-    assert L.cda_b200_decode_plan_splits(32, 8, 4096, -1) == 4        # one round; a second would double the fixed cost
-    assert L.cda_b200_decode_plan_splits(1, 8, 4096, -1) == 32        # never below 128 tokens per split
+    # the line of all sequences' 16-token groups is cut into 148 equal chunks (one per SM): 32 x 4096 groups -> chunks of
+    # 886 groups, and a sequence of 4096 groups touches at most 6 of them
+    assert L.cda_b200_decode_plan_splits(32, 8, 65536, -1) == 6
+    assert L.cda_b200_decode_plan_splits(4, 8, 65536, -1) == 37       # 148 = 4 x 37: equal ranges inside each sequence
+    assert L.cda_b200_decode_plan_splits(32, 8, 4096, -1) == 4        # 128 ranges of 64 groups beat 148 straddling chunks
+    assert L.cda_b200_decode_plan_splits(1, 8, 4096, -1) == 32        # never below 128 tokens per chunk
     assert L.cda_b200_decode_plan_splits(0, 8, 16, -1) == lib.CDA_ERR_BAD_ARG
 
 

@@ -52,6 +52,11 @@ def _rank_main(rank, world, port, q):
         parts = [(allp[r, :, :, None, :128], allp[r, :, :, None, 128], allp[r, :, :, None, 129]) for r in range(world)]
         merged = O.unrotate(O.merge_partials(parts), O.sylvester_hadamard())[:, :, 0]
         ok, ratio, cos = Cs.close(merged, want)
+        # query all-gather of the context-parallel path: rank r holds heads (kv j, r, i) of a (kv, rank, local) grid
+        from sub0_b200.sharding import gather_heads
+        grid = torch.arange(3 * 2 * world * 2 * 128, dtype=torch.float32).view(3, 2, world, 2, 128)   # (n, kv, rank, local, d)
+        mine = grid[:, :, rank].reshape(3, 4, 128).contiguous()
+        ok = ok and bool(torch.equal(gather_heads(mine, 2), grid.reshape(3, 2 * world * 2, 128)))
         q.put((rank, ok, ratio, bool(torch.equal(allp[rank], packed))))
     except Exception as exc:                      # report instead of leaving the parent waiting
         q.put((rank, False, float("inf"), repr(exc)))

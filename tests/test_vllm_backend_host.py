@@ -40,7 +40,7 @@ def test_class_surface():
     with pytest.raises(ValueError):
         Backend.get_kv_cache_shape(10, 16, 8, 64)
     assert Builder.reorder_batch_threshold == 1
-    assert Impl.can_return_lse_for_decode is False
+    assert Impl.can_return_lse_for_decode is True          # the reference leaves it False (cda_attn_v2.py:621)
     impl = Impl(32, 128, 0.088, num_kv_heads=8)
     assert impl.group_size == 4
     for bad in (dict(alibi_slopes=[1.0]), dict(sliding_window=128), dict(attn_type="encoder"), dict(num_kv_heads=16)):
@@ -88,3 +88,21 @@ def test_memory_saving_patch_and_registration():
 
     vllm_plugin.register_cda_v2()
     assert AttentionBackendEnum.CUSTOM.get_class().__name__ == "CDAv2AttentionBackend"
+
+
+def test_step_timing_hooks(monkeypatch, tmp_path):
+    """CDA_V2_TIME_STEPS=1 brackets backend calls (reference ``_time_call``, cda_attn_v2.py:264-292); off by default."""
+    from sub0_b200.vllm_integration import cda_attn_v2 as M
+    M._STEP_TIMINGS.clear()
+    assert M._time_call("x", lambda: 7) == 7 and not M._STEP_TIMINGS
+    monkeypatch.setenv("CDA_V2_TIME_STEPS", "1")
+    monkeypatch.setenv("CDA_V2_TIME_STEPS_OUT", str(tmp_path / "t"))
+    assert M._time_call("forward_decode", lambda: 8) == 8
+    M._time_call("forward_decode", lambda: None)
+    summ = M.step_timing_summary()
+    assert summ["forward_decode"]["calls"] == 2 and summ["forward_decode"]["cpu_ms_mean"] >= 0
+    M._dump_step_timings()
+    import json, os
+    data = json.loads((tmp_path / f"t.{os.getpid()}.json").read_text())
+    assert data["summary"]["forward_decode"]["calls"] == 2
+    M._STEP_TIMINGS.clear()

@@ -51,8 +51,8 @@ def both_entry_points(case, num_splits):
 
 
 def test_static_scratch_matches_workspace_entry_point_twice():
-    # first call: many partials (4 splits x 2 warps per head); second call: a different, smaller problem with other
-    # bit widths, so every byte it reads from the scratch was either rewritten by it or is skipped
+    # first call: four partials per output row; second call: a different, smaller problem with other bit widths, so
+    # every byte it reads from the scratch was either rewritten by it or is skipped
     first = Cs.paged_case([3000, 777, 2048], H_kv=8, group=4, seed=901)
     second = Cs.paged_case([130, 0, 1], H_kv=2, group=8, k_bits=4, v_bits=2, seed=902)
     for case, splits in ((first, 4), (second, 0), (first, 0)):
@@ -69,7 +69,7 @@ def test_static_scratch_matches_workspace_entry_point_twice():
 def test_static_scratch_refuses_what_does_not_fit():
     from sub0_b200 import _lib
     L = _lib.lib
-    # B * H_q * 520 B * 2 partial sets > 8 MiB even without splitting: must be refused before any launch
+    # B * H_q * 520 B > 8 MiB even with a single partial per output row: must be refused before any launch
     B, Hq, Hkv = 4096, 32, 8
     Q = torch.zeros(16, dtype=torch.uint8, device=DEV)          # never dereferenced: the size check comes first
     p = Q.data_ptr()
