@@ -40,7 +40,16 @@
 
 namespace cda {
 
-constexpr int kLutWindow = 65536;   // the table occupies one 64 KB-aligned block of the shared window
+constexpr int kLutWindow = 65536;   // a table window is one 64 KB-aligned block of the shared window
+// Tables.  4-bit codes: entry = code byte -> fp16 pair, 4 bytes per lane, 128 bytes per row; when both sides are 4-bit the K
+// and V tables share one window (K in the low, V in the high half of the 256-byte rows).  2-bit codes: entry = code byte
+// (four codes) -> four fp16, 8 bytes per lane, 256 bytes per row: one 64-bit gather yields two operand registers.  A 2-bit
+// side therefore fills a window of its own, and any kernel with a 2-bit side uses two windows.
+template <int KB, int VB>
+struct LutCfg {
+  static constexpr int kWindows = (KB == 4 && VB == 4) ? 1 : 2;
+  static constexpr int kBytes = kWindows * kLutWindow;
+};
 constexpr float kMinusBig = -1.0e30f;   // "no score yet": finite, so differences never produce NaN
 
 struct DecodeParams {
@@ -158,10 +167,13 @@ template <int POS>
 __device__ __forceinline__ uint32_t lut_byte(uint32_t w, uint32_t base) {
   return lds_u32(__byte_perm(w, base, 0x7604 | (POS << 4)));
 }
-// Table entry for a 4-bit code (two 2-bit indices) at bit offset SH of w.
-template <int SH>
-__device__ __forceinline__ uint32_t lut_nibble(uint32_t w, uint32_t base) {
-  return lds_u32(base + (((w >> SH) & 0xfu) << 8));
+// Table entry (four fp16 = two operand registers) for the four 2-bit codes in byte POS of w; same address trick, the
+// lane's slot inside the 256-byte row is 8 bytes wide.
+template <int POS>
+__device__ __forceinline__ uint2 lut_byte4(uint32_t w, uint32_t base) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(__byte_perm(w, base, 0x7604 | (POS << 4))));
+  return v;
 }
 
 // One 16-token group as the lane holds it: K index pieces of rows r and r+8, V index pieces of rows
@@ -184,11 +196,10 @@ struct QkGather {
       a[S][1] = lut_byte<(2 * S) & 3>(k[1][(2 * S) >> 2], base);
       a[S][2] = lut_byte<(2 * S + 1) & 3>(k[0][(2 * S + 1) >> 2], base);
       a[S][3] = lut_byte<(2 * S + 1) & 3>(k[1][(2 * S + 1) >> 2], base);
-    } else {                // byte S of the lane's 8: high nibble = coordinates 4S, 4S+1, low nibble = 4S+2, 4S+3
-      a[S][0] = lut_nibble<8 * (S & 3) + 4>(k[0][S >> 2], base);
-      a[S][1] = lut_nibble<8 * (S & 3) + 4>(k[1][S >> 2], base);
-      a[S][2] = lut_nibble<8 * (S & 3)>(k[0][S >> 2], base);
-      a[S][3] = lut_nibble<8 * (S & 3)>(k[1][S >> 2], base);
+    } else {                // byte S of the lane's 8: coordinates 4S, 4S+1 (first register) and 4S+2, 4S+3 (second)
+      const uint2 e0 = lut_byte4<S & 3>(k[0][S >> 2], base), e1 = lut_byte4<S & 3>(k[1][S >> 2], base);
+      a[S][0] = e0.x; a[S][2] = e0.y;
+      a[S][1] = e1.x; a[S][3] = e1.y;
     }
     QkGather<KB, S + 1>::run(a, k, base);
   }
@@ -209,10 +220,9 @@ struct PvGather {
       a[U][2] = lut_byte<(2 * U) & 3>(vb[(2 * U) >> 2], base);
       a[U][3] = lut_byte<(2 * U + 1) & 3>(vb[(2 * U + 1) >> 2], base);
     } else {
-      a[U][0] = lut_nibble<8 * U + 4>(va[0], base);
-      a[U][1] = lut_nibble<8 * U>(va[0], base);
-      a[U][2] = lut_nibble<8 * U + 4>(vb[0], base);
-      a[U][3] = lut_nibble<8 * U>(vb[0], base);
+      const uint2 ea = lut_byte4<U>(va[0], base), eb = lut_byte4<U>(vb[0], base);
+      a[U][0] = ea.x; a[U][1] = ea.y;
+      a[U][2] = eb.x; a[U][3] = eb.y;
     }
     PvGather<VB, U + 1>::run(a, va, vb, base);
   }
@@ -450,11 +460,12 @@ __global__ void __launch_bounds__(W * 32, 1) decode_split_kernel(const DecodePar
   const uint32_t lut_win = (win0 + kLutWindow - 1) & ~static_cast<uint32_t>(kLutWindow - 1);
   const int rings_before = static_cast<int>((lut_win - win0) / Cfg::kRingBytes);
   const int rings_after = W > rings_before ? W - rings_before : 0;
-  const uint32_t win_end = lut_win + kLutWindow + rings_after * Cfg::kRingBytes;
+  constexpr uint32_t kLutBytes = LutCfg<KB, VB>::kBytes;
+  const uint32_t win_end = lut_win + kLutBytes + rings_after * Cfg::kRingBytes;
   // (the copy engine wants 128-byte aligned destinations: every ring offset is a multiple of 128, so the window must be too)
   const bool fits = win_end - win0 <= static_cast<uint32_t>(p.smem_bytes) && (win0 & 127u) == 0u;
   const uint32_t ring = warp < rings_before ? win0 + warp * Cfg::kRingBytes
-                                            : lut_win + kLutWindow + (warp - rings_before) * Cfg::kRingBytes;
+                                            : lut_win + kLutBytes + (warp - rings_before) * Cfg::kRingBytes;
   uint8_t* lut = smem + (lut_win - win0);
 
   // ---- the chunk's items -------------------------------------------------------------------------------------------------
@@ -543,24 +554,33 @@ __global__ void __launch_bounds__(W * 32, 1) decode_split_kernel(const DecodePar
   __shared__ int s_idx[64];
   float alpha_k, alpha_v;
   find_table_scales<(KB == 4 ? 16 : 4), (VB == 4 ? 16 : 4)>(p.cb_k, p.cb_v, s_err, s_idx, alpha_k, alpha_v);
-  {   // build both tables: code e, lane l -> K pair at e*256 + 4l, V pair at e*256 + 128 + 4l (levels divided by alpha)
-    constexpr int EK = KB == 4 ? 256 : 16, EV = VB == 4 ? 256 : 16, LK = KB == 4 ? 16 : 4, LV = VB == 4 ? 16 : 4;
-    // lane i keeps level i & (L - 1) of either codebook; entries are put together by shuffles
+  {   // build the tables (levels divided by alpha); lane i keeps level i & (L - 1) of either codebook and the entries are
+      // put together by shuffles.  Row e (one code byte) of a window is 256 bytes.
+    constexpr int LK = KB == 4 ? 16 : 4, LV = VB == 4 ? 16 : 4;
     const float lev_k = __ldg(p.cb_k + (lane & (LK - 1))) * (1.0f / alpha_k);
     const float lev_v = __ldg(p.cb_v + (lane & (LV - 1))) * (1.0f / alpha_v);
-    uint32_t* lw = reinterpret_cast<uint32_t*>(lut);
+    uint32_t* lw_k = reinterpret_cast<uint32_t*>(lut);
+    uint32_t* lw_v = reinterpret_cast<uint32_t*>(lut + (LutCfg<KB, VB>::kWindows == 1 ? 128 : kLutWindow));
 #pragma unroll 4
-    for (int e = warp; e < (EK > EV ? EK : EV); e += W) {
-      const int fk = KB == 4 ? (e >> 4) & 15 : (e >> 2) & 3, sk = KB == 4 ? (e & 15) : (e & 3);
-      const int fv = VB == 4 ? (e >> 4) & 15 : (e >> 2) & 3, sv = VB == 4 ? (e & 15) : (e & 3);
-      const uint32_t wk = pack_half2(__shfl_sync(0xffffffffu, lev_k, fk), __shfl_sync(0xffffffffu, lev_k, sk));
-      const uint32_t wv = pack_half2(__shfl_sync(0xffffffffu, lev_v, fv), __shfl_sync(0xffffffffu, lev_v, sv));
-      if (e < EK) lw[e * 64 + lane] = wk;
-      if (e < EV) lw[e * 64 + 32 + lane] = wv;
+    for (int e = warp; e < 256; e += W) {
+      if (KB == 4) {
+        lw_k[e * 64 + lane] = pack_half2(__shfl_sync(0xffffffffu, lev_k, (e >> 4) & 15), __shfl_sync(0xffffffffu, lev_k, e & 15));
+      } else {
+        const uint32_t lo = pack_half2(__shfl_sync(0xffffffffu, lev_k, (e >> 6) & 3), __shfl_sync(0xffffffffu, lev_k, (e >> 4) & 3));
+        const uint32_t hi = pack_half2(__shfl_sync(0xffffffffu, lev_k, (e >> 2) & 3), __shfl_sync(0xffffffffu, lev_k, e & 3));
+        *reinterpret_cast<uint2*>(lw_k + e * 64 + 2 * lane) = make_uint2(lo, hi);
+      }
+      if (VB == 4) {
+        lw_v[e * 64 + lane] = pack_half2(__shfl_sync(0xffffffffu, lev_v, (e >> 4) & 15), __shfl_sync(0xffffffffu, lev_v, e & 15));
+      } else {
+        const uint32_t lo = pack_half2(__shfl_sync(0xffffffffu, lev_v, (e >> 6) & 3), __shfl_sync(0xffffffffu, lev_v, (e >> 4) & 3));
+        const uint32_t hi = pack_half2(__shfl_sync(0xffffffffu, lev_v, (e >> 2) & 3), __shfl_sync(0xffffffffu, lev_v, e & 3));
+        *reinterpret_cast<uint2*>(lw_v + e * 64 + 2 * lane) = make_uint2(lo, hi);
+      }
     }
   }
-  cx.base_k = lut_win | (lane << 2);
-  cx.base_v = cx.base_k | 128u;
+  cx.base_k = lut_win | (lane << (KB == 4 ? 2 : 3));
+  cx.base_v = LutCfg<KB, VB>::kWindows == 1 ? (cx.base_k | 128u) : ((lut_win + kLutWindow) | (lane << (VB == 4 ? 2 : 3)));
   {   // operand placement of the probabilities: even columns take the low half, odd columns the high half
     const bool odd = G == 4 && (r >> 2) != 0;
     cx.sel_b0 = odd ? 0x1044u : 0x4410u;
@@ -571,7 +591,7 @@ __global__ void __launch_bounds__(W * 32, 1) decode_split_kernel(const DecodePar
   constexpr int kRowFloats = kHeadDim + 4;   // parked partial rows: 528 bytes keep the 16-byte reads aligned
   static_assert(G * kRowFloats * 4 <= Cfg::kRingBytes, "a warp's partial must fit its ring");
   auto ring_of = [&](int w) -> float* {
-    const uint32_t a = w < rings_before ? win0 + w * Cfg::kRingBytes : lut_win + kLutWindow + (w - rings_before) * Cfg::kRingBytes;
+    const uint32_t a = w < rings_before ? win0 + w * Cfg::kRingBytes : lut_win + kLutBytes + (w - rings_before) * Cfg::kRingBytes;
     return reinterpret_cast<float*>(smem + (a - win0));
   };
 
@@ -1103,7 +1123,8 @@ template <int G, int KB, int VB, int W, int NS>
 static int launch_split(const DecodeParams& p0, const Plan& pl, const CUtensorMap& cache_map, cudaStream_t st) {
   // Wherever the dynamic window starts relative to a 64 KB boundary, the rings packed around the aligned table need
   // at most one ring of slack (or, with few warps, the gap before the table itself).
-  static_assert(kLutWindow + (W + 1) * DecCfg<W, NS, KB, VB>::kRingBytes <= kMaxDynamicSmem && 2 * kLutWindow <= kMaxDynamicSmem,
+  static_assert(LutCfg<KB, VB>::kBytes + (W + 1) * DecCfg<W, NS, KB, VB>::kRingBytes <= kMaxDynamicSmem &&
+                    LutCfg<KB, VB>::kBytes + kLutWindow <= kMaxDynamicSmem,
                 "warp rings and the lookup table do not fit the shared memory of one SM");
   static bool configured[64];
   int dev = 0;
@@ -1121,9 +1142,12 @@ static int launch_split(const DecodeParams& p0, const Plan& pl, const CUtensorMa
   return check_launch("decode split kernel");
 }
 
+// Ring depth: three stages next to one table window, two next to two (both fit the 227 KB of an SM; the third stage
+// buys nothing measurable -- the copy engine keeps two groups per warp in flight either way).
 template <int G, int KB, int VB>
 static int dispatch_shape(const DecodeParams& p, const Plan& pl, const CUtensorMap& cache_map, cudaStream_t st) {
-  return launch_split<G, KB, VB, kSplitWarps, kSplitStages>(p, pl, cache_map, st);
+  constexpr int NS = LutCfg<KB, VB>::kWindows == 1 ? kSplitStages : 2;
+  return launch_split<G, KB, VB, kSplitWarps, NS>(p, pl, cache_map, st);
 }
 
 template <int G>
