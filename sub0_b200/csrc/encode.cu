@@ -71,10 +71,47 @@ __device__ __forceinline__ uint32_t count_thresholds_x4(float x, const float* T)
   return lo;
 }
 
+// ---- one-look-up form of the same count -----------------------------------------------------------------------------------------
+// [-1, 1] is cut into 128 cells of width 1/64.  For a cell the table holds how many thresholds lie in lower cells and the
+// one threshold inside it (+inf if none): index(x) = below[cell(x)] + (x > inside[cell(x)]) -- one 64-bit load, one
+// comparison, one add instead of four dependent load/compare steps.  cell() is monotone in x, so thresholds in lower
+// cells are below x and thresholds in higher cells are not: the count is the rule's, bit for bit.  A codebook with two
+// thresholds in one cell cannot use the table; the CTA then keeps the four-step search (build_cells reports it).
+constexpr int kCells = 129;                       // x = +1 lands in cell 128
+constexpr float kCellMagic = 1048576.0f + 64.0f;  // 2^20 + 64: the sum below has a unit in the last place of 1/8
+// Byte offset (cell * 8) of x's table entry; x in [-1, 1].  One FMA (rounded once, hence monotone) and one mask.
+__device__ __forceinline__ uint32_t cell_offset(float x) { return __float_as_uint(__fmaf_rn(x, 64.0f, kCellMagic)) & 0xff8u; }
+struct CellEntry {
+  float inside;      // the threshold in this cell, +inf if there is none
+  uint32_t below;    // thresholds in lower cells
+};
+// Threads `t` = 0 .. kCells-1 of the calling group fill one cell each from the L-1 thresholds in T (ascending).  Returns
+// true (to that thread) if its cell holds more than one threshold.
+template <int L>
+__device__ __forceinline__ bool build_cell(const float* T, CellEntry* cells, int t) {
+  if (t < 0 || t >= kCells) return false;
+  uint32_t below = 0;
+  int inside = 0;
+  float thr = INFINITY;
+#pragma unroll
+  for (int i = 0; i < L - 1; ++i) {
+    const int c = static_cast<int>(cell_offset(fminf(fmaxf(T[i], -1.0f), 1.0f)) >> 3);
+    below += c < t ? 1u : 0u;
+    if (c == t) { ++inside; thr = T[i]; }
+  }
+  cells[t].inside = thr;
+  cells[t].below = below;
+  return inside > 1;
+}
+__device__ __forceinline__ uint32_t count_by_cell(float x, const CellEntry* cells) {
+  const uint2 e = *reinterpret_cast<const uint2*>(reinterpret_cast<const char*>(cells) + cell_offset(x));
+  return e.y + (x > __uint_as_float(e.x) ? 1u : 0u);
+}
+
 // v: this lane's four rotated fp32 coordinates.  Writes the packed indices of the row to `idx_dst`
 // (16*BITS bytes per row) and returns the row norm (identical in every lane).  T: thresholds of the codebook.
-template <int BITS>
-__device__ __forceinline__ float quantize_row(const float (&v)[4], const float* T, uint8_t* idx_dst, int lane) {
+template <int BITS, bool FAST>
+__device__ __forceinline__ float quantize_row(const float (&v)[4], const float* T, const CellEntry* cells, uint8_t* idx_dst, int lane) {
   constexpr int L = BITS == 4 ? 16 : 4;
   float ss = v[0] * v[0];
   ss = fmaf(v[1], v[1], ss);
@@ -87,7 +124,7 @@ __device__ __forceinline__ float quantize_row(const float (&v)[4], const float* 
   for (int i = 0; i < 4; ++i) {
     float u = __fdiv_rn(v[i], norm);
     u = fminf(fmaxf(u, -1.0f), 1.0f);
-    idx[i] = count_thresholds<L>(u, T);
+    idx[i] = FAST ? static_cast<int>(count_by_cell(u, cells)) : count_thresholds<L>(u, T);
   }
   if (BITS == 4) {
     const uint16_t two = static_cast<uint16_t>(((idx[0] << 4) | idx[1]) | (((idx[2] << 4) | idx[3]) << 8));
@@ -153,9 +190,10 @@ __device__ __forceinline__ void scale_and_pack(const float (&y)[8][2][4], uint32
 // 2^24; with y = RN(1/norm), q = RN(x y) and r = x - q norm (exact in one FMA: no intermediate leaves the normal
 // range), RN(q + r y) is the correctly rounded quotient (Markstein's division step), i.e. the value of x / norm; only
 // a zero loses its sign (-0 comes out as +0), which no comparison below can see.
-template <int BITS>
-__device__ __forceinline__ float2 quantize_pair(const uint32_t (&hp)[8][2][2], const float* T, uint8_t* dst_lo, uint8_t* dst_hi,
-                                                int c, bool ok_lo, bool ok_hi) {
+// FAST: take the indices from the cell table; otherwise from the four-step search.
+template <int BITS, bool FAST>
+__device__ __forceinline__ float2 quantize_pair(const uint32_t (&hp)[8][2][2], const float* T, const CellEntry* cells,
+                                                uint8_t* dst_lo, uint8_t* dst_hi, int c, bool ok_lo, bool ok_hi) {
   constexpr int L = BITS == 4 ? 16 : 4;
   float ss[2] = {0.f, 0.f};
 #pragma unroll
@@ -188,18 +226,18 @@ __device__ __forceinline__ float2 quantize_pair(const uint32_t (&hp)[8][2][2], c
 #pragma unroll
         for (int t = 0; t < 2; ++t) {
           const float2 v2 = __half22float2(*reinterpret_cast<const __half2*>(&hp[2 * w + g0][t][h]));
-          uint32_t i4[2];                                            // four times the indices of coordinates e = 0, 1
+          uint32_t ix[2];                                            // the indices of coordinates e = 0, 1
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
             const float v = e ? v2.y : v2.x;
             const float q0 = __fmul_rn(v, rcp[h]);
             const float rem = __fmaf_rn(-q0, norm[h], v);
             const float u = __fmaf_rn(rem, rcp[h], q0);
-            i4[e] = count_thresholds_x4<L>(u, T);
+            ix[e] = FAST ? count_by_cell(u, cells) : (count_thresholds_x4<L>(u, T) >> 2);
           }
           const int pair = 2 * g0 + t;                               // which two of this lane's eight coordinates
-          if (BITS == 4) word += ((i4[0] << 2) + (i4[1] >> 2)) << (8 * pair);               // one byte, first code on top
-          else word += (i4[0] + (i4[1] >> 2)) << (8 * g0 + 4 - 4 * t);                      // half a byte, first code on top
+          if (BITS == 4) word += ((ix[0] << 4) + ix[1]) << (8 * pair);                      // one byte, first code on top
+          else word += ((ix[0] << 2) + ix[1]) << (8 * g0 + 4 - 4 * t);                      // half a byte, first code on top
         }
       if (ok) {
         if (BITS == 4) *reinterpret_cast<uint32_t*>(dst + 16 * w + 4 * c) = word;
@@ -210,22 +248,13 @@ __device__ __forceinline__ float2 quantize_pair(const uint32_t (&hp)[8][2][2], c
   return make_float2(norm[0], norm[1]);
 }
 
-// One warp per 16 rows (row = token * H_kv + head); lane 4r + c works on rows r and r + 8 of the tile.
-template <int KB, int VB>
-__global__ void __launch_bounds__(256, 2) paged_encode_kernel(const __half* __restrict__ K, const __half* __restrict__ V,
-                                                              const int32_t* __restrict__ slot_mapping,
-                                                              uint8_t* __restrict__ cache, const float* __restrict__ cb_K,
-                                                              const float* __restrict__ cb_V, int64_t rows, int H_kv,
-                                                              int64_t num_slots, int slot_bytes) {
-  __shared__ float s_cb[2][16], s_thr[2][16];
-  if (threadIdx.x < 16) {
-    s_cb[0][threadIdx.x] = threadIdx.x < (KB == 4 ? 16 : 4) ? cb_K[threadIdx.x] : 0.f;
-    s_cb[1][threadIdx.x] = threadIdx.x < (VB == 4 ? 16 : 4) ? cb_V[threadIdx.x] : 0.f;
-  }
-  __syncthreads();
-  build_thresholds<(KB == 4 ? 16 : 4)>(s_cb[0], s_thr[0], threadIdx.x);
-  build_thresholds<(VB == 4 ? 16 : 4)>(s_cb[1], s_thr[1], static_cast<int>(threadIdx.x) - 32);
-  __syncthreads();
+// The tile loop of the paged encoder: one warp per 16 rows (row = token * H_kv + head); lane 4r + c works on rows r and
+// r + 8 of the tile.  FAST: index selection by the cell tables, else by the four-step search.
+template <int KB, int VB, bool FAST>
+__device__ __forceinline__ void encode_tiles(const __half* __restrict__ K, const __half* __restrict__ V,
+                                             const int32_t* __restrict__ slot_mapping, uint8_t* __restrict__ cache, int64_t rows,
+                                             int H_kv, int64_t num_slots, int slot_bytes, const float (*thr)[16],
+                                             const CellEntry (*cells)[kCells + 1]) {
   const int lane = threadIdx.x & 31, r = lane >> 2, c = lane & 3;
   constexpr int kKBytes = 16 * KB, kVBytes = 16 * VB;
   const RotFrag frag = make_rot_frag(lane);
@@ -258,22 +287,25 @@ __global__ void __launch_bounds__(256, 2) paged_encode_kernel(const __half* __re
     }
     // K fragments were requested a turn ago; V's are requested before K is quantised, the next tile's K before V is
     if (first) { load_row_frags(K, row[0], row[1], c, fr); first = false; }
-    float y[8][2][4];
-    uint32_t hp[8][2][2];
-    rotate16(fr, frag, y);
-    load_row_frags(V, row[0], row[1], c, fr);
-    scale_and_pack(y, hp);
-    const float2 nk = quantize_pair<KB>(hp, s_thr[0], dst[0], dst[1], c, ok[0], ok[1]);
-    rotate16(fr, frag, y);
+    float2 nk, nv;
     {
-      const int64_t next = tile + tile_step;
-      if (next < tiles) {
-        const int64_t n_lo = next * 16 + r, n_hi = n_lo + 8;
-        load_row_frags(K, n_lo < rows ? n_lo : rows - 1, n_hi < rows ? n_hi : rows - 1, c, fr);
+      float y[8][2][4];
+      uint32_t hp[8][2][2];
+      rotate16(fr, frag, y);
+      load_row_frags(V, row[0], row[1], c, fr);
+      scale_and_pack(y, hp);
+      nk = quantize_pair<KB, FAST>(hp, thr[0], cells[0], dst[0], dst[1], c, ok[0], ok[1]);
+      rotate16(fr, frag, y);
+      {
+        const int64_t next = tile + tile_step;
+        if (next < tiles) {
+          const int64_t n_lo = next * 16 + r, n_hi = n_lo + 8;
+          load_row_frags(K, n_lo < rows ? n_lo : rows - 1, n_hi < rows ? n_hi : rows - 1, c, fr);
+        }
       }
+      scale_and_pack(y, hp);
+      nv = quantize_pair<VB, FAST>(hp, thr[1], cells[1], dst[0] + kKBytes, dst[1] + kKBytes, c, ok[0], ok[1]);
     }
-    scale_and_pack(y, hp);
-    const float2 nv = quantize_pair<VB>(hp, s_thr[1], dst[0] + kKBytes, dst[1] + kKBytes, c, ok[0], ok[1]);
     if (c == 0) {
       if (ok[0]) *reinterpret_cast<float2*>(dst[0] + kKBytes + kVBytes) = make_float2(nk.x, nv.x);
       if (ok[1]) *reinterpret_cast<float2*>(dst[1] + kKBytes + kVBytes) = make_float2(nk.y, nv.y);
@@ -281,20 +313,50 @@ __global__ void __launch_bounds__(256, 2) paged_encode_kernel(const __half* __re
   }
 }
 
+// One warp per 16 rows (row = token * H_kv + head); lane 4r + c works on rows r and r + 8 of the tile.
+template <int KB, int VB>
+__global__ void __launch_bounds__(256, 2) paged_encode_kernel(const __half* __restrict__ K, const __half* __restrict__ V,
+                                                              const int32_t* __restrict__ slot_mapping,
+                                                              uint8_t* __restrict__ cache, const float* __restrict__ cb_K,
+                                                              const float* __restrict__ cb_V, int64_t rows, int H_kv,
+                                                              int64_t num_slots, int slot_bytes) {
+  __shared__ float s_cb[2][16], s_thr[2][16];
+  __shared__ __align__(8) CellEntry s_cell[2][kCells + 1];
+  if (threadIdx.x < 16) {
+    s_cb[0][threadIdx.x] = threadIdx.x < (KB == 4 ? 16 : 4) ? cb_K[threadIdx.x] : 0.f;
+    s_cb[1][threadIdx.x] = threadIdx.x < (VB == 4 ? 16 : 4) ? cb_V[threadIdx.x] : 0.f;
+  }
+  __syncthreads();
+  build_thresholds<(KB == 4 ? 16 : 4)>(s_cb[0], s_thr[0], threadIdx.x);
+  build_thresholds<(VB == 4 ? 16 : 4)>(s_cb[1], s_thr[1], static_cast<int>(threadIdx.x) - 32);
+  __syncthreads();
+  bool crowded = build_cell<(KB == 4 ? 16 : 4)>(s_thr[0], s_cell[0], threadIdx.x);
+  crowded |= build_cell<(VB == 4 ? 16 : 4)>(s_thr[1], s_cell[1], static_cast<int>(threadIdx.x) - 127);   // threads 127 .. 255: cells 0 .. 128
+  // a codebook with two thresholds in one cell keeps the four-step search (the same choice in every CTA)
+  if (__syncthreads_or(crowded ? 1 : 0))
+    encode_tiles<KB, VB, false>(K, V, slot_mapping, cache, rows, H_kv, num_slots, slot_bytes, s_thr, s_cell);
+  else
+    encode_tiles<KB, VB, true>(K, V, slot_mapping, cache, rows, H_kv, num_slots, slot_bytes, s_thr, s_cell);
+}
+
 template <int BITS>
 __global__ void __launch_bounds__(256) quantize_rotated_kernel(const float* __restrict__ x, int64_t rows,
                                                                const float* __restrict__ cb, uint8_t* __restrict__ idx_out,
                                                                float* __restrict__ norm_out) {
   __shared__ float s_cb[16], s_thr[16];
+  __shared__ __align__(8) CellEntry s_cell[kCells + 1];
   if (threadIdx.x < 16) s_cb[threadIdx.x] = threadIdx.x < (BITS == 4 ? 16 : 4) ? cb[threadIdx.x] : 0.f;
   __syncthreads();
   build_thresholds<(BITS == 4 ? 16 : 4)>(s_cb, s_thr, threadIdx.x);
   __syncthreads();
+  // the same choice as the paged encoder makes: cell tables unless two thresholds share a cell
+  const bool fast = !__syncthreads_or(build_cell<(BITS == 4 ? 16 : 4)>(s_thr, s_cell, threadIdx.x) ? 1 : 0);
   const int lane = threadIdx.x & 31;
   for (int64_t row = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5); row < rows; row += static_cast<int64_t>(gridDim.x) * 8) {
     const float4 raw = *reinterpret_cast<const float4*>(x + row * kHeadDim + 4 * lane);
     const float v[4] = {raw.x, raw.y, raw.z, raw.w};
-    const float n = quantize_row<BITS>(v, s_thr, idx_out + row * (16 * BITS), lane);
+    const float n = fast ? quantize_row<BITS, true>(v, s_thr, s_cell, idx_out + row * (16 * BITS), lane)
+                         : quantize_row<BITS, false>(v, s_thr, s_cell, idx_out + row * (16 * BITS), lane);
     if (lane == 0) norm_out[row] = n;
   }
 }

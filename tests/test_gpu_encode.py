@@ -42,6 +42,23 @@ def test_quantize_rotated_bit_exact(ops, rows, bits):
     assert float(flips) <= 1e-5
 
 
+@pytest.mark.parametrize("table", ["default16", "default4", "uniform16", "crowded16", "crowded4"])
+def test_quantize_rotated_many_rows_every_table_kind(ops, table):
+    """12.8 million values per table, identical fp32 inputs and the kernel's own norms: zero index mismatches.  The
+    kernels pick the index with one table look-up per value (cells of width 1/64 holding at most one decision
+    threshold); the crowded tables put several thresholds into one cell, which makes them fall back to the step-by-step
+    search -- both forms must reproduce Compressor.quantize_unit (compression.py:298-313) exactly."""
+    cb = {"default16": Cs.cb_for(4), "default4": Cs.cb_for(2), "uniform16": O.uniform_levels(16),
+          "crowded16": torch.linspace(-0.04, 0.05, 16), "crowded4": torch.tensor([-0.011, -0.002, 0.001, 0.3])}[table]
+    bits = 4 if cb.numel() == 16 else 2
+    gen = torch.Generator().manual_seed(len(table))
+    x_rot = torch.randn(100_000, 128, generator=gen) * torch.rand(100_000, 1, generator=gen).mul(4).exp()
+    x_rot[::7, 5] *= 30.0                                               # some rows with one dominant coordinate: |u| near 1
+    idx, norm = ops.quantize_rotated(x_rot.to(DEV), cb)
+    want = O.quantize_rotated(x_rot, cb, norm=norm.cpu())
+    assert torch.equal(idx.cpu(), want.idx)
+
+
 def test_quantize_rotated_boundaries(ops, golden):
     """Midpoints, exact levels and +-1 from the reference's own quantiser (golden vector)."""
     g = golden("quantize")
