@@ -1,4 +1,13 @@
-"""Seeded synthetic cases shared by the CPU and GPU tests: paged caches built with the CPU oracle's encoder."""
+"""Seeded synthetic cases shared by the CPU and GPU tests: paged caches built with the CPU oracle's encoder, and the
+output comparisons.
+
+Stated tolerance of the path: fp16 outputs within |got - want| <= 1e-3 + 2e-3 |want| of the oracle.  ``strict`` counts the
+elements outside it; ``close`` is the row-max form used for short sequences.  The reference rounds the rotated-frame output
+to fp16 and then applies the inverse Hadamard transform, which spreads each coordinate's rounding over all 128 outputs: a
+kernel whose value before that rounding differs from the oracle's by one fp16 rounding of a probability (relative ~3e-4,
+coherent over the 128 coordinates of a key) flips enough of those roundings that a few near-zero outputs per million land
+past 1e-3.  Comparisons of up to tens of thousands of outputs at contexts >= 4096 are therefore asserted with zero
+violations, comparisons of millions with a measured cap."""
 from __future__ import annotations
 
 import torch
