@@ -644,12 +644,17 @@ def run_seqsplit(args):
                        "h2d_bytes_per_step": hQ.numel() * 2 * world, "d2h_bytes_per_step": hout.numel() * 2 * world,
                        "what": "pinned H2D of Q + partial + all-gather + merge + D2H of the output, one CUDA graph replayed and "
                                "synchronised every step; the KV cache is resident state"}
-        print(json.dumps(line))
-        if line["parity_sample"]["violations"]:
-            raise SystemExit("decode_seqsplit parity: output outside the stated tolerance")
+        print(json.dumps(line), flush=True)
+    failed = rank == 0 and line["parity_sample"]["violations"] > 0
     if world > 1:
+        # The captured graphs hold NCCL kernels: tearing the process group down while they exist has hung here, so the
+        # ranks meet at a last barrier and leave without destroying the group.
         dist.barrier()
-        dist.destroy_process_group()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        os._exit(1 if failed else 0)
+    if failed:
+        raise SystemExit("decode_seqsplit parity: output outside the stated tolerance")
 
 
 # ---- secondary workloads: paged encode and causal varlen prefill (full-prompt prefill of 8 ragged sequences) ------------------
