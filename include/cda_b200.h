@@ -200,14 +200,22 @@ int cda_b200_prefill_varlen(const void* Q, const void* kv_cache, const int32_t* 
                             int block_table_stride, int max_query_len, int max_seq_len, int64_t num_slots,
                             int slot_bytes, int k_bits, int v_bits, float scale, void* stream);
 
-/* The same attention kernel on dense rotated-frame fp16 K/V (row b*... given by cu_seqlens_k, valid length
- * seqused_k[b]); Q un-rotated in, out un-rotated.
+/* The same tcgen05 attention kernel on dense rotated-frame fp16 K/V (sequence b's rows start at cu_seqlens_k[b], valid
+ * length seqused_k[b]; K/V 16-byte aligned); Q un-rotated in, out un-rotated.  q_len_b <= seqused_k[b].
  * Replaces cda_fa2_varlen_fwd_hadamard(Q, k_rot, v_rot, out, cu_q, cu_k, seqused_k, max_q, max_k, scale),
  * cda/kernels_cuda/fa2_cda.py:170-181. */
 int cda_b200_varlen_fwd_hadamard(const void* Q, const void* k_rot, const void* v_rot, void* out,
                                  const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
                                  const int32_t* seqused_k, int64_t T, int B, int H_q, int H_kv,
                                  int max_query_len, int max_seq_len, float scale, void* stream);
+
+/* cda_b200_varlen_fwd_hadamard on the FlashAttention-2-style mma.sync kernel instead of the tcgen05 one: same arguments,
+ * same result within the path's tolerance.  An independent implementation kept as a cross-check (the main entry point
+ * also falls back to it when Q or out is only 8-byte aligned).  Contract as above, cda/kernels_cuda/fa2_cda.py:170-181. */
+int cda_b200_varlen_fwd_hadamard_mma(const void* Q, const void* k_rot, const void* v_rot, void* out,
+                                     const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                                     const int32_t* seqused_k, int64_t T, int B, int H_q, int H_kv,
+                                     int max_query_len, int max_seq_len, float scale, void* stream);
 
 /* Decode `rows` rows of packed indices (16*bits bytes each) and fp32 norms into fp16 rows of 128: out = fp16(cb[idx] * norm),
  * the rotated-frame K or V the "dequantise, then dense attention" baseline attends over.

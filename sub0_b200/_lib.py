@@ -44,6 +44,7 @@ PROTOTYPES = {
     "cda_b200_prefill_varlen": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _i, _i, _i, _i, _i, _i, _i, _i64, _i, _i,
                                      _i, _f, _p]),
     "cda_b200_varlen_fwd_hadamard": (_i, [_p, _p, _p, _p, _p, _p, _p, _i64, _i, _i, _i, _i, _i, _f, _p]),
+    "cda_b200_varlen_fwd_hadamard_mma": (_i, [_p, _p, _p, _p, _p, _p, _p, _i64, _i, _i, _i, _i, _i, _f, _p]),
     "cda_b200_prefill_fault": (_i, []),
     "cda_b200_prefill_status": (_i, []),
     "cda_b200_prefill_clear_status": (_i, []),

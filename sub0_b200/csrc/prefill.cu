@@ -401,6 +401,17 @@ extern "C" int cda_b200_prefill_varlen(const void* Q, const void* kv_cache, cons
   return dispatch_prefill_umma(p, k_bits, v_bits, max_query_len, B, static_cast<cudaStream_t>(stream));
 }
 
+static int dense_mma_sync(const void* Q, const void* k_rot, const void* v_rot, void* out, const int32_t* cu_seqlens_q,
+                          const int32_t* cu_seqlens_k, const int32_t* seqused_k, int B, int H_q, int H_kv, int max_query_len, float scale,
+                          void* stream) {
+  PrefillParams p{};
+  p.q = static_cast<const __half*>(Q); p.out = static_cast<__half*>(out); p.cu_q = cu_seqlens_q;
+  p.k_rot = static_cast<const __half*>(k_rot); p.v_rot = static_cast<const __half*>(v_rot);
+  p.cu_k = cu_seqlens_k; p.seqused_k = seqused_k;
+  p.H_q = H_q; p.H_kv = H_kv; p.group = H_q / H_kv; p.scale_log2 = scale * kLog2e;
+  return launch_dense_prefill(p, max_query_len, B, static_cast<cudaStream_t>(stream));
+}
+
 extern "C" int cda_b200_varlen_fwd_hadamard(const void* Q, const void* k_rot, const void* v_rot, void* out, const int32_t* cu_seqlens_q,
                                             const int32_t* cu_seqlens_k, const int32_t* seqused_k, int64_t T, int B, int H_q, int H_kv,
                                             int max_query_len, int max_seq_len, float scale, void* stream) {
@@ -410,10 +421,30 @@ extern "C" int cda_b200_varlen_fwd_hadamard(const void* Q, const void* k_rot, co
   if (rc != CDA_OK) return rc;
   if (!k_rot || !v_rot || !cu_seqlens_k || !seqused_k) return fail(CDA_ERR_BAD_ARG, "varlen_fwd_hadamard: null pointer");
   if (!aligned16(k_rot) || !aligned16(v_rot)) return fail(CDA_ERR_BAD_ALIGN, "varlen_fwd_hadamard: K/V must be 16-byte aligned");
-  PrefillParams p{};
+  // The tcgen05 kernel with dense-source producers; it moves Q and the output in 16-byte pieces and serves GQA groups up to
+  // 8.  Anything else (8-byte aligned Q / out, wider groups) goes to the mma.sync kernel.
+  if (!aligned16(Q) || !aligned16(out) || H_q / H_kv > 8)
+    return dense_mma_sync(Q, k_rot, v_rot, out, cu_seqlens_q, cu_seqlens_k, seqused_k, B, H_q, H_kv, max_query_len, scale, stream);
+  PrefillUmmaParams p{};
   p.q = static_cast<const __half*>(Q); p.out = static_cast<__half*>(out); p.cu_q = cu_seqlens_q;
-  p.k_rot = static_cast<const __half*>(k_rot); p.v_rot = static_cast<const __half*>(v_rot);
-  p.cu_k = cu_seqlens_k; p.seqused_k = seqused_k;
+  p.seq_lens = seqused_k; p.cu_k = cu_seqlens_k;
+  p.k_dense = static_cast<const __half*>(k_rot); p.v_dense = static_cast<const __half*>(v_rot);
+  p.block_size = 16; p.bs_shift = 4;
   p.H_q = H_q; p.H_kv = H_kv; p.group = H_q / H_kv; p.scale_log2 = scale * kLog2e;
-  return launch_dense_prefill(p, max_query_len, B, static_cast<cudaStream_t>(stream));
+  return dispatch_prefill_umma(p, 16, 16, max_query_len, B, static_cast<cudaStream_t>(stream));
+}
+
+// The same contract on the FlashAttention-2-style mma.sync kernel: an independent implementation kept as a cross-check
+// of the tcgen05 path (and used by it for inputs that are only 8-byte aligned).
+extern "C" int cda_b200_varlen_fwd_hadamard_mma(const void* Q, const void* k_rot, const void* v_rot, void* out,
+                                                const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k, const int32_t* seqused_k,
+                                                int64_t T, int B, int H_q, int H_kv, int max_query_len, int max_seq_len, float scale,
+                                                void* stream) {
+  (void)max_seq_len;
+  int rc = prefill_common_checks("varlen_fwd_hadamard_mma", Q, out, cu_seqlens_q, T, B, H_q, H_kv, max_query_len);
+  if (rc == 1) return CDA_OK;
+  if (rc != CDA_OK) return rc;
+  if (!k_rot || !v_rot || !cu_seqlens_k || !seqused_k) return fail(CDA_ERR_BAD_ARG, "varlen_fwd_hadamard_mma: null pointer");
+  if (!aligned16(k_rot) || !aligned16(v_rot)) return fail(CDA_ERR_BAD_ALIGN, "varlen_fwd_hadamard_mma: K/V must be 16-byte aligned");
+  return dense_mma_sync(Q, k_rot, v_rot, out, cu_seqlens_q, cu_seqlens_k, seqused_k, B, H_q, H_kv, max_query_len, scale, stream);
 }

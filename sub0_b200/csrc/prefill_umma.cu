@@ -300,10 +300,14 @@ __device__ __forceinline__ void rotate_staged_rows(uint32_t area, int tile, int 
 
 }  // namespace pfu
 
+// KB == VB == 16 selects the dense source: keys and values are fp16 rows in the rotated frame (`k_dense`, `v_dense`,
+// sequence b's rows start at cu_k[b]) instead of codes in the paged cache; the producers then copy rows into the tiles.
 template <int G, int KB, int VB>
 __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const PrefillUmmaParams p) {
   using namespace pfu;
   using namespace umma;
+  constexpr bool kDense = KB == 16;
+  static_assert(!kDense || VB == 16, "dense source: both sides");
   constexpr int kPosPerTile = kBlocks * kRows / G;
   constexpr int kSlotBytes = 16 * KB + 16 * VB + 16;
   constexpr int kProducerThreads = kProducerWarps * 32;
@@ -353,11 +357,11 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
 
   __shared__ float s_err[64];
   __shared__ int s_idx[64];
-  float alpha_k, alpha_v;
-  find_table_scales<kLevK, kLevV>(p.cb_k, p.cb_v, s_err, s_idx, alpha_k, alpha_v);
+  float alpha_k = 1.0f, alpha_v = 1.0f;
+  if constexpr (!kDense) find_table_scales<kLevK, kLevV>(p.cb_k, p.cb_v, s_err, s_idx, alpha_k, alpha_v);
   // One table serves both sides when the codebooks are the same (then their scales are the same too).
   bool same_cb = KB == VB;
-  if (KB == VB) {
+  if (KB == VB && !kDense) {
 #pragma unroll
     for (int i = 0; i < kLevK; ++i) same_cb = same_cb && __ldg(p.cb_k + i) == __ldg(p.cb_v + i);
   }
@@ -380,8 +384,10 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
     tmem_alloc(base + kOffBar + kOffTmemAddr, kTmemCols);
     tmem_relinquish();
   }
-  fill_code_table<KB>(sm + kOffLut, lut_stride, p.cb_k, 1.0f / alpha_k, tid, kThreads);
-  if (!same_cb) fill_code_table<VB>(sm + kOffLut + lutv_off, lut_stride, p.cb_v, 1.0f / alpha_v, tid, kThreads);
+  if constexpr (!kDense) {
+    fill_code_table<KB>(sm + kOffLut, lut_stride, p.cb_k, 1.0f / alpha_k, tid, kThreads);
+    if (!same_cb) fill_code_table<VB>(sm + kOffLut + lutv_off, lut_stride, p.cb_v, 1.0f / alpha_v, tid, kThreads);
+  }
   // Q: park the raw rows; then warps 0..15 rotate 16 rows each and store them as the A operand of Q K^T (K-major,
   // 128-byte swizzle)
 #pragma unroll
@@ -503,6 +509,47 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
   } else if (warp < kSoftmaxWarps + kProducerWarps) {
     // ================= producers: slots -> unit-level fp16 tiles ============================================================
     const int pt = tid - kSoftmaxWarps * 32;                 // 0..255
+   if constexpr (kDense) {
+    // Dense source: a tile is 128 rows of 256 bytes = 2048 16-byte chunks, eight per producer thread, copied with cp.async
+    // straight into the swizzled tile; the copies of a tile start as soon as its stage is free (while the previous tile is
+    // being consumed), and the thread publishes the tile when its own copies have landed.
+    GroupWaiter gw{reinterpret_cast<volatile int*>(sm + kOffBar + kOffOutcome + 16), abort_flag, kBarIdProducer, kProducerThreads, 0, pt == 0};
+    const int64_t row_halfs = static_cast<int64_t>(p.H_kv) * kHeadDim;
+    const __half* k_src = p.k_dense + (static_cast<int64_t>(p.cu_k[b]) * p.H_kv + kvh) * kHeadDim;
+    const __half* v_src = p.v_dense + (static_cast<int64_t>(p.cu_k[b]) * p.H_kv + kvh) * kHeadDim;
+    {   // every key's norm factor is the softmax scale
+      float* kn = reinterpret_cast<float*>(sm + kOffKn);
+      for (int i = pt; i < 4 * kKeys; i += kProducerThreads) kn[i] = p.scale_log2;
+    }
+    auto copy_tile = [&](const __half* src, uint32_t tile, int j) {
+#pragma unroll
+      for (int it = 0; it < 8; ++it) {
+        const int x = pt + kProducerThreads * it, nl = x >> 4, c16 = x & 15;
+        const int n = min(j * kKeys + nl, seq_len - 1);      // keys past the end are masked later; copy a valid row
+        cp_async16(tile + (c16 >> 3) * kColBlockBytes + sw128(nl, c16 & 7), src + n * row_halfs + c16 * 8);
+      }
+      cp_async_commit();
+    };
+#pragma unroll 1
+    for (int i = 0; i < n_tiles; ++i) {
+      if (i >= 2 && !gw.wait(bar(kBarKEmpty + (i & 1)), ((i - 2) >> 1) & 1)) break;
+      copy_tile(k_src, base + kOffK + (i & 1) * kTileBytes, i);
+      if (i >= 2 && !gw.wait(bar(kBarVEmpty + (i & 1)), ((i - 2) >> 1) & 1)) break;
+      copy_tile(v_src, base + kOffV + (i & 1) * kTileBytes, i);
+      cp_async_wait<1>();
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(bar(kBarNorms + (i & 3)));
+        if (!(p.withhold_first_k && i == 0)) mbar_arrive(bar(kBarKFull + (i & 1)));
+      }
+      cp_async_wait<0>();
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(kBarVFull + (i & 1)));
+    }
+    cp_async_wait<0>();
+   } else {
     const uint32_t k_copies = lut_stride / (KB == 4 ? 4u : 8u), v_copies = lut_stride / (VB == 4 ? 4u : 8u);
     const uint32_t lutk_lane = base + kOffLut + (lane & (k_copies - 1)) * (KB == 4 ? 4u : 8u);
     const uint32_t lutv_lane = base + kOffLut + lutv_off + (lane & (v_copies - 1)) * (VB == 4 ? 4u : 8u);
@@ -600,6 +647,7 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
       load_v(i + 1, vr);
     }
     if (bad_block) atomicOr(&g_prefill_status, 1);
+   }
   } else {
     // ================= MMA issuer ==================================================================================================
     if (lane == 0) {
@@ -699,6 +747,7 @@ static int dispatch_prefill_umma_group(const PrefillUmmaParams& p, int max_query
 }
 
 int dispatch_prefill_umma(const PrefillUmmaParams& p, int k_bits, int v_bits, int max_query_len, int B, cudaStream_t st) {
+  if (k_bits == 16 && v_bits == 16) return dispatch_prefill_umma_group<16, 16>(p, max_query_len, B, st);
   if (k_bits == 4 && v_bits == 4) return dispatch_prefill_umma_group<4, 4>(p, max_query_len, B, st);
   if (k_bits == 4 && v_bits == 2) return dispatch_prefill_umma_group<4, 2>(p, max_query_len, B, st);
   if (k_bits == 2 && v_bits == 2) return dispatch_prefill_umma_group<2, 2>(p, max_query_len, B, st);

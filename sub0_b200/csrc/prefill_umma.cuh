@@ -15,6 +15,9 @@ struct PrefillUmmaParams {
   const int32_t* seq_lens;
   const float* cb_k;
   const float* cb_v;
+  const __half* k_dense;   // dense source (k_bits == v_bits == 16): rotated-frame fp16 rows (row, H_kv, 128); seq_lens then
+  const __half* v_dense;   // holds the number of valid keys per sequence and cu_k the first row of each sequence
+  const int32_t* cu_k;
   unsigned long long wait_limit_ns;   // limit of every mbarrier wait (set by the launcher)
   int withhold_first_k;               // diagnostic: the producers keep back the first "K tile full" arrive
   int block_size, bs_shift, bt_stride, num_blocks;   // bs_shift: log2(block_size), or -1 if it is not a power of two
@@ -22,7 +25,7 @@ struct PrefillUmmaParams {
   float scale_log2;
 };
 
-// Launch the causal varlen prefill over the paged cache.  Grid: (query tiles of 128 / G positions, KV heads, sequences).
+// Launch the causal varlen prefill over the paged cache (k_bits, v_bits in {2, 4}) or over dense rotated rows (16, 16).
 int dispatch_prefill_umma(const PrefillUmmaParams& p, int k_bits, int v_bits, int max_query_len, int B, cudaStream_t st);
 
 }  // namespace cda

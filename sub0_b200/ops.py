@@ -362,7 +362,9 @@ def prefill_debug(wait_limit_us: int = 0, withhold_first_k_arrive: bool = False)
 
 def varlen_fwd_hadamard(Q: Tensor, k_rot: Tensor, v_rot: Tensor, output: Tensor, cu_seqlens_q: Tensor,
                         cu_seqlens_k: Tensor, seqused_k: Tensor, max_query_len: int, max_seq_len: int,
-                        scale: float) -> None:
+                        scale: float, *, mma_sync: bool = False) -> None:
+    """Causal varlen attention over dense rotated-frame K/V on the tcgen05 kernel; ``mma_sync=True`` runs the independent
+    mma.sync implementation instead (a cross-check)."""
     _cuda(Q, "Q", torch.float16), _cuda(k_rot, "k_rot", torch.float16), _cuda(v_rot, "v_rot", torch.float16)
     if Q.dim() != 3 or Q.shape[-1] != HEAD_DIM or k_rot.dim() != 3 or k_rot.shape != v_rot.shape:
         raise ValueError("Q must be (T, H_q, 128); k_rot, v_rot (rows, H_kv, 128)")
@@ -370,7 +372,7 @@ def varlen_fwd_hadamard(Q: Tensor, k_rot: Tensor, v_rot: Tensor, output: Tensor,
         raise ValueError("output must be contiguous fp16 shaped like Q")
     Qc, kc, vc = Q.contiguous(), k_rot.contiguous(), v_rot.contiguous()
     cq, ck, su = (_i32(t).contiguous() for t in (cu_seqlens_q, cu_seqlens_k, seqused_k))
-    check(lib.cda_b200_varlen_fwd_hadamard(Qc.data_ptr(), kc.data_ptr(), vc.data_ptr(), output.data_ptr(), cq.data_ptr(),
-                                           ck.data_ptr(), su.data_ptr(), Q.shape[0], cq.numel() - 1, Q.shape[1],
-                                           k_rot.shape[1], int(max_query_len), int(max_seq_len), float(scale),
-                                           _stream(Q.device)))
+    fn = lib.cda_b200_varlen_fwd_hadamard_mma if mma_sync else lib.cda_b200_varlen_fwd_hadamard
+    check(fn(Qc.data_ptr(), kc.data_ptr(), vc.data_ptr(), output.data_ptr(), cq.data_ptr(), ck.data_ptr(), su.data_ptr(),
+             Q.shape[0], cq.numel() - 1, Q.shape[1], k_rot.shape[1], int(max_query_len), int(max_seq_len), float(scale),
+             _stream(Q.device)))

@@ -158,6 +158,12 @@ def test_dense_source_and_raw_kv_paths():
                                                             100, max_len, 1.0 / 128 ** 0.5)
     torch.cuda.synchronize()
     assert_close(out.cpu(), want, "dense source")
+    # the independent mma.sync implementation of the same call, and the fall-back to it for an 8-byte aligned output
+    from sub0_b200 import ops
+    out_m = torch.full_like(Q, float("nan"), device=DEV)
+    ops.varlen_fwd_hadamard(Q.to(DEV), k_rot, v_rot, out_m, cu.to(DEV), cu_k, d["seq_lens"], 100, max_len, 1.0 / 128 ** 0.5, mma_sync=True)
+    torch.cuda.synchronize()
+    assert_close(out_m.cpu(), want, "dense source, mma.sync")
     # raw (uncompressed) K/V: the rotation cancels, so the result is plain causal attention on the raw rows
     K = torch.cat([kv[0] for kv in case["raw"]]).to(DEV)
     V = torch.cat([kv[1] for kv in case["raw"]]).to(DEV)
@@ -208,8 +214,15 @@ def test_large_ragged_prefill_matches_the_dense_route(group, H_kv):
     k_rot, v_rot = fa2_cda.paged_cache_to_dense_rotated(cache, bt, sl, cb_K=cb, cb_V=cb, block_size=16, max_seq_len=max_len)
     ref = torch.full_like(Q, float("nan"))
     cu_k = torch.arange(len(lens) + 1, dtype=torch.int32, device=DEV) * max_len
-    load_fa2_cda_varlen_fused().cda_fa2_varlen_fwd_hadamard(Q, k_rot, v_rot, ref, cu, cu_k, sl, max(q_lens), max_len, 1.0 / 128 ** 0.5)
+    from sub0_b200 import ops
+    ops.varlen_fwd_hadamard(Q, k_rot, v_rot, ref, cu, cu_k, sl, max(q_lens), max_len, 1.0 / 128 ** 0.5, mma_sync=True)
+    # and the tcgen05 kernel fed from the same dense rows (dense-source producers)
+    dense = torch.full_like(Q, float("nan"))
+    load_fa2_cda_varlen_fused().cda_fa2_varlen_fwd_hadamard(Q, k_rot, v_rot, dense, cu, cu_k, sl, max(q_lens), max_len, 1.0 / 128 ** 0.5)
     torch.cuda.synchronize()
+    assert not bool(dense.isnan().any())
+    _, ratio_d, cos_d = Cs.close(dense.cpu(), ref.cpu())
+    assert ratio_d <= 2.0 and cos_d >= 0.9999, f"large ragged g{group}, dense source: distance/tolerance {ratio_d:.3f}, cosine {cos_d:.6f}"
     # two independent fp16 pipelines, each within the path's tolerance of the oracle: their distance may reach twice that
     assert not bool(out.isnan().any()) and not bool(ref.isnan().any())
     _, ratio, cos = Cs.close(out.cpu(), ref.cpu())
