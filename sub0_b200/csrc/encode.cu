@@ -88,8 +88,7 @@ struct CellEntry {
 // Threads `t` = 0 .. kCells-1 of the calling group fill one cell each from the L-1 thresholds in T (ascending).  Returns
 // true (to that thread) if its cell holds more than one threshold.
 template <int L>
-__device__ __forceinline__ bool build_cell(const float* T, CellEntry* cells, int t) {
-  if (t < 0 || t >= kCells) return false;
+__device__ __forceinline__ bool cell_of(const float* T, int t, CellEntry& e) {
   uint32_t below = 0;
   int inside = 0;
   float thr = INFINITY;
@@ -99,9 +98,37 @@ __device__ __forceinline__ bool build_cell(const float* T, CellEntry* cells, int
     below += c < t ? 1u : 0u;
     if (c == t) { ++inside; thr = T[i]; }
   }
-  cells[t].inside = thr;
-  cells[t].below = below;
+  e.inside = thr;
+  e.below = below;
   return inside > 1;
+}
+template <int L>
+__device__ __forceinline__ bool build_cell(const float* T, CellEntry* cells, int t) {
+  if (t < 0 || t >= kCells) return false;
+  CellEntry e;
+  const bool crowded = cell_of<L>(T, t, e);
+  cells[t] = e;
+  return crowded;
+}
+// Where the code of this lane's coordinate p = 4 g0 + 2 t + e sits in the piece of the index field that the lane writes
+// (32 bits of 4-bit codes, 16 bits of 2-bit codes): the first code of a byte on top.
+template <int BITS>
+__host__ __device__ constexpr int code_shift(int p) {
+  return BITS == 4 ? 8 * (p >> 1) + 4 * (1 - (p & 1)) : 8 * (p >> 2) + 4 - 4 * ((p >> 1) & 1) + 2 * (1 - (p & 1));
+}
+// Eight copies of the cell table, one per coordinate position of a lane, with `below` already shifted to the place of
+// that position's code: a lane's piece of the index field is then a plain sum of table words and compare results.
+template <int BITS>
+__device__ __forceinline__ bool build_cells_by_position(const float* T, CellEntry (*cells)[kCells + 1], int t) {
+  if (t < 0 || t >= kCells) return false;
+  CellEntry e;
+  const bool crowded = cell_of<(BITS == 4 ? 16 : 4)>(T, t, e);
+#pragma unroll
+  for (int p = 0; p < 8; ++p) {
+    cells[p][t].inside = e.inside;
+    cells[p][t].below = e.below << code_shift<BITS>(p);
+  }
+  return crowded;
 }
 __device__ __forceinline__ uint32_t count_by_cell(float x, const CellEntry* cells) {
   const uint2 e = *reinterpret_cast<const uint2*>(reinterpret_cast<const char*>(cells) + cell_offset(x));
@@ -154,10 +181,8 @@ __device__ __forceinline__ void rotate16(const RowFrags& a, const RotFrag& f, fl
   for (int j = 0; j < 4; ++j)
 #pragma unroll
     for (int t = 0; t < 2; ++t) {
-#pragma unroll
-      for (int i = 0; i < 4; ++i) y[2 * j][t][i] = y[2 * j + 1][t][i] = 0.f;
-      mma_16816(y[2 * j][t], a.lo[j].x, a.hi[j].x, a.lo[j].y, a.hi[j].y, f.b0[t], f.b1[t]);
-      mma_16816(y[2 * j + 1][t], a.lo[j].z, a.hi[j].z, a.lo[j].w, a.hi[j].w, f.b0[t], f.b1[t]);
+      mma_16816_zero(y[2 * j][t], a.lo[j].x, a.hi[j].x, a.lo[j].y, a.hi[j].y, f.b0[t], f.b1[t]);
+      mma_16816_zero(y[2 * j + 1][t], a.lo[j].z, a.hi[j].z, a.lo[j].w, a.hi[j].w, f.b0[t], f.b1[t]);
     }
 #pragma unroll
   for (int bit = 1; bit < 8; bit <<= 1)
@@ -167,10 +192,10 @@ __device__ __forceinline__ void rotate16(const RowFrags& a, const RotFrag& f, fl
 #pragma unroll
         for (int t = 0; t < 2; ++t)
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const float a = y[g][t][i], b = y[g | bit][t][i];
-            y[g][t][i] = a + b;
-            y[g | bit][t][i] = a - b;
+          for (int i = 0; i < 4; i += 2) {                 // two coordinates per instruction
+            const uint64_t a = f2_pack(y[g][t][i], y[g][t][i + 1]), b = f2_pack(y[g | bit][t][i], y[g | bit][t][i + 1]);
+            f2_unpack(f2_add(a, b), y[g][t][i], y[g][t][i + 1]);
+            f2_unpack(f2_sub(a, b), y[g | bit][t][i], y[g | bit][t][i + 1]);
           }
       }
 }
@@ -182,7 +207,11 @@ __device__ __forceinline__ void scale_and_pack(const float (&y)[8][2][4], uint32
 #pragma unroll
     for (int t = 0; t < 2; ++t)
 #pragma unroll
-      for (int h = 0; h < 2; ++h) hp[g][t][h] = pack_half2(y[g][t][2 * h] * kRsqrtD, y[g][t][2 * h + 1] * kRsqrtD);
+      for (int h = 0; h < 2; ++h) {
+        float s0, s1;
+        f2_unpack(f2_mul(f2_pack(y[g][t][2 * h], y[g][t][2 * h + 1]), f2_pack(kRsqrtD, kRsqrtD)), s0, s1);
+        hp[g][t][h] = pack_half2(s0, s1);
+      }
 }
 // Quantises the two rows held in hp and writes this lane's pieces of their index fields.  Returns the two norms (the same in the four lanes of a quad).
 //
@@ -195,22 +224,34 @@ template <int BITS, bool FAST>
 __device__ __forceinline__ float2 quantize_pair(const uint32_t (&hp)[8][2][2], const float* T, const CellEntry* cells,
                                                 uint8_t* dst_lo, uint8_t* dst_hi, int c, bool ok_lo, bool ok_hi) {
   constexpr int L = BITS == 4 ? 16 : 4;
-  float ss[2] = {0.f, 0.f};
+  float ss[2];
+  {
+    uint64_t acc[2] = {f2_pack(0.f, 0.f), f2_pack(0.f, 0.f)};      // even and odd coordinates summed side by side
 #pragma unroll
-  for (int g = 0; g < 8; ++g)
+    for (int g = 0; g < 8; ++g)
 #pragma unroll
-    for (int t = 0; t < 2; ++t)
+      for (int t = 0; t < 2; ++t)
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const float2 v = __half22float2(*reinterpret_cast<const __half2*>(&hp[g][t][h]));
-        ss[h] = fmaf(v.x, v.x, ss[h]);
-        ss[h] = fmaf(v.y, v.y, ss[h]);
-      }
-  float norm[2], rcp[2];
+        for (int h = 0; h < 2; ++h) {
+          const float2 v = __half22float2(*reinterpret_cast<const __half2*>(&hp[g][t][h]));
+          const uint64_t vv = f2_pack(v.x, v.y);
+          acc[h] = f2_fma(vv, vv, acc[h]);
+        }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      float even, odd;
+      f2_unpack(acc[h], even, odd);
+      ss[h] = even + odd;
+    }
+  }
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     ss[h] += __shfl_xor_sync(0xffffffffu, ss[h], 1);
     ss[h] += __shfl_xor_sync(0xffffffffu, ss[h], 2);
+  }
+  float norm[2], rcp[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
     norm[h] = fmaxf(sqrtf(ss[h]), kNormFloor);
     rcp[h] = __frcp_rn(norm[h]);
   }
@@ -227,17 +268,31 @@ __device__ __forceinline__ float2 quantize_pair(const uint32_t (&hp)[8][2][2], c
         for (int t = 0; t < 2; ++t) {
           const float2 v2 = __half22float2(*reinterpret_cast<const __half2*>(&hp[2 * w + g0][t][h]));
           uint32_t ix[2];                                            // the indices of coordinates e = 0, 1
+          // the division step and the cell index on both coordinates at once (each lane rounded as the scalar form;
+          // q * (-norm) is the same product as (-q) * norm)
+          float u2[2], cf2[2];
+          {
+            const uint64_t vv = f2_pack(v2.x, v2.y), rr = f2_pack(rcp[h], rcp[h]);
+            const uint64_t q0 = f2_mul(vv, rr);
+            const uint64_t rem = f2_fma(q0, f2_pack(-norm[h], -norm[h]), vv);
+            const uint64_t uu = f2_fma(rem, rr, q0);
+            f2_unpack(uu, u2[0], u2[1]);
+            f2_unpack(f2_fma(uu, f2_pack(64.0f, 64.0f), f2_pack(kCellMagic, kCellMagic)), cf2[0], cf2[1]);
+          }
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
-            const float v = e ? v2.y : v2.x;
-            const float q0 = __fmul_rn(v, rcp[h]);
-            const float rem = __fmaf_rn(-q0, norm[h], v);
-            const float u = __fmaf_rn(rem, rcp[h], q0);
-            ix[e] = FAST ? count_by_cell(u, cells) : (count_thresholds_x4<L>(u, T) >> 2);
+            const float u = u2[e];
+            const uint32_t cell_off = __float_as_uint(cf2[e]) & 0xff8u;
+            if (FAST) {                                              // table word: the count of lower cells, already in place
+              constexpr int kPosStride = (kCells + 1) * static_cast<int>(sizeof(CellEntry));
+              const int pos = 4 * g0 + 2 * t + e;
+              const uint2 ce = *reinterpret_cast<const uint2*>(reinterpret_cast<const char*>(cells) + pos * kPosStride + cell_off);
+              ix[e] = ce.y + (u > __uint_as_float(ce.x) ? (1u << code_shift<BITS>(pos)) : 0u);
+            } else {
+              ix[e] = (count_thresholds_x4<L>(u, T) >> 2) << code_shift<BITS>(4 * g0 + 2 * t + e);
+            }
           }
-          const int pair = 2 * g0 + t;                               // which two of this lane's eight coordinates
-          if (BITS == 4) word += ((ix[0] << 4) + ix[1]) << (8 * pair);                      // one byte, first code on top
-          else word += ((ix[0] << 2) + ix[1]) << (8 * g0 + 4 - 4 * t);                      // half a byte, first code on top
+          word += ix[0] + ix[1];
         }
       if (ok) {
         if (BITS == 4) *reinterpret_cast<uint32_t*>(dst + 16 * w + 4 * c) = word;
@@ -254,7 +309,7 @@ template <int KB, int VB, bool FAST>
 __device__ __forceinline__ void encode_tiles(const __half* __restrict__ K, const __half* __restrict__ V,
                                              const int32_t* __restrict__ slot_mapping, uint8_t* __restrict__ cache, int64_t rows,
                                              int H_kv, int64_t num_slots, int slot_bytes, const float (*thr)[16],
-                                             const CellEntry (*cells)[kCells + 1]) {
+                                             const CellEntry* cells_k, const CellEntry* cells_v) {
   const int lane = threadIdx.x & 31, r = lane >> 2, c = lane & 3;
   constexpr int kKBytes = 16 * KB, kVBytes = 16 * VB;
   const RotFrag frag = make_rot_frag(lane);
@@ -294,7 +349,7 @@ __device__ __forceinline__ void encode_tiles(const __half* __restrict__ K, const
       rotate16(fr, frag, y);
       load_row_frags(V, row[0], row[1], c, fr);
       scale_and_pack(y, hp);
-      nk = quantize_pair<KB, FAST>(hp, thr[0], cells[0], dst[0], dst[1], c, ok[0], ok[1]);
+      nk = quantize_pair<KB, FAST>(hp, thr[0], cells_k, dst[0], dst[1], c, ok[0], ok[1]);
       rotate16(fr, frag, y);
       {
         const int64_t next = tile + tile_step;
@@ -304,7 +359,7 @@ __device__ __forceinline__ void encode_tiles(const __half* __restrict__ K, const
         }
       }
       scale_and_pack(y, hp);
-      nv = quantize_pair<VB, FAST>(hp, thr[1], cells[1], dst[0] + kKBytes, dst[1] + kKBytes, c, ok[0], ok[1]);
+      nv = quantize_pair<VB, FAST>(hp, thr[1], cells_v, dst[0] + kKBytes, dst[1] + kKBytes, c, ok[0], ok[1]);
     }
     if (c == 0) {
       if (ok[0]) *reinterpret_cast<float2*>(dst[0] + kKBytes + kVBytes) = make_float2(nk.x, nv.x);
@@ -321,7 +376,7 @@ __global__ void __launch_bounds__(256, 2) paged_encode_kernel(const __half* __re
                                                               const float* __restrict__ cb_V, int64_t rows, int H_kv,
                                                               int64_t num_slots, int slot_bytes) {
   __shared__ float s_cb[2][16], s_thr[2][16];
-  __shared__ __align__(8) CellEntry s_cell[2][kCells + 1];
+  __shared__ __align__(8) CellEntry s_cell[2][8][kCells + 1];
   if (threadIdx.x < 16) {
     s_cb[0][threadIdx.x] = threadIdx.x < (KB == 4 ? 16 : 4) ? cb_K[threadIdx.x] : 0.f;
     s_cb[1][threadIdx.x] = threadIdx.x < (VB == 4 ? 16 : 4) ? cb_V[threadIdx.x] : 0.f;
@@ -330,13 +385,13 @@ __global__ void __launch_bounds__(256, 2) paged_encode_kernel(const __half* __re
   build_thresholds<(KB == 4 ? 16 : 4)>(s_cb[0], s_thr[0], threadIdx.x);
   build_thresholds<(VB == 4 ? 16 : 4)>(s_cb[1], s_thr[1], static_cast<int>(threadIdx.x) - 32);
   __syncthreads();
-  bool crowded = build_cell<(KB == 4 ? 16 : 4)>(s_thr[0], s_cell[0], threadIdx.x);
-  crowded |= build_cell<(VB == 4 ? 16 : 4)>(s_thr[1], s_cell[1], static_cast<int>(threadIdx.x) - 127);   // threads 127 .. 255: cells 0 .. 128
+  bool crowded = build_cells_by_position<KB>(s_thr[0], s_cell[0], threadIdx.x);
+  crowded |= build_cells_by_position<VB>(s_thr[1], s_cell[1], static_cast<int>(threadIdx.x) - 127);   // threads 127 .. 255: cells 0 .. 128
   // a codebook with two thresholds in one cell keeps the four-step search (the same choice in every CTA)
   if (__syncthreads_or(crowded ? 1 : 0))
-    encode_tiles<KB, VB, false>(K, V, slot_mapping, cache, rows, H_kv, num_slots, slot_bytes, s_thr, s_cell);
+    encode_tiles<KB, VB, false>(K, V, slot_mapping, cache, rows, H_kv, num_slots, slot_bytes, s_thr, &s_cell[0][0][0], &s_cell[1][0][0]);
   else
-    encode_tiles<KB, VB, true>(K, V, slot_mapping, cache, rows, H_kv, num_slots, slot_bytes, s_thr, s_cell);
+    encode_tiles<KB, VB, true>(K, V, slot_mapping, cache, rows, H_kv, num_slots, slot_bytes, s_thr, &s_cell[0][0][0], &s_cell[1][0][0]);
 }
 
 template <int BITS>

@@ -195,12 +195,13 @@ __device__ __forceinline__ void expand_quad(uint32_t tile, uint32_t lut_lane, ui
   }
 }
 
-// One thread's 64 scores of a tile (columns s_col .. s_col + 63 of its TMEM lane), scaled by the key norms kn[0..63].
-// MASK: keys beyond q_pos (the row's diagonal) count as minus infinity.  The next 16 columns are requested before the
-// current ones are worked on (tcgen05.wait::ld covers every load issued so far).
+// One thread's 64 scores of a tile (columns s_col .. s_col + 63 of its TMEM lane), scaled by the key norms kn[0..63]
+// (16-byte aligned).  MASK: keys beyond q_pos (the row's diagonal) count as minus infinity.  The next 16 columns are
+// requested before the current ones are worked on (tcgen05.wait::ld covers every load issued so far).
 template <bool MASK>
 __device__ __forceinline__ float row_max(uint32_t s_col, const float* kn, int key0, int q_pos) {
-  float mx = -INFINITY;
+  float mx[2] = {-INFINITY, -INFINITY};
+  const ulonglong2* kn2 = reinterpret_cast<const ulonglong2*>(kn);
   uint32_t s[2][16];
   umma::tmem_ld16(s_col, s[0]);
 #pragma unroll
@@ -208,19 +209,28 @@ __device__ __forceinline__ float row_max(uint32_t s_col, const float* kn, int ke
     umma::tmem_wait_ld();
     if (ch < 3) umma::tmem_ld16(s_col + 16 * (ch + 1), s[(ch + 1) & 1]);
 #pragma unroll
-    for (int c = 0; c < 16; ++c) {
-      float x = __uint_as_float(s[ch & 1][c]) * kn[16 * ch + c];
-      if (MASK) x = key0 + 16 * ch + c > q_pos ? -INFINITY : x;
-      mx = fmaxf(mx, x);
+    for (int c = 0; c < 16; c += 4) {
+      const ulonglong2 k4 = kn2[4 * ch + c / 4];
+      float x[4];
+      f2_unpack(f2_mul(f2_pack(s[ch & 1][c], s[ch & 1][c + 1]), k4.x), x[0], x[1]);
+      f2_unpack(f2_mul(f2_pack(s[ch & 1][c + 2], s[ch & 1][c + 3]), k4.y), x[2], x[3]);
+      if (MASK) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) x[i] = key0 + 16 * ch + c + i > q_pos ? -INFINITY : x[i];
+      }
+      mx[0] = fmax3(mx[0], x[0], x[1]);
+      mx[1] = fmax3(mx[1], x[2], x[3]);
     }
   }
-  return mx;
+  return fmaxf(mx[0], mx[1]);
 }
 // exp2(score * kn - m) for the same 64 scores; P as fp16 pairs into columns s_col .. s_col + 31 (the value norms are
 // already inside the V tile).  Returns the sum of the probabilities.
 template <bool MASK>
 __device__ __forceinline__ float row_probabilities(uint32_t s_col, const float* kn, float m, int key0, int q_pos) {
-  float sum0 = 0.f, sum1 = 0.f;
+  uint64_t sum = f2_pack(0.f, 0.f);
+  const uint64_t neg_m = f2_pack(-m, -m);
+  const ulonglong2* kn2 = reinterpret_cast<const ulonglong2*>(kn);
   uint32_t s[2][16];
   umma::tmem_ld16(s_col, s[0]);
 #pragma unroll
@@ -230,21 +240,116 @@ __device__ __forceinline__ float row_probabilities(uint32_t s_col, const float* 
     if (ch < 3) umma::tmem_ld16(s_col + 16 * (ch + 1), s[(ch + 1) & 1]);
 #pragma unroll
     for (int c = 0; c < 16; c += 2) {
-      float a0 = fmaf(__uint_as_float(s[ch & 1][c]), kn[16 * ch + c], -m), a1 = fmaf(__uint_as_float(s[ch & 1][c + 1]), kn[16 * ch + c + 1], -m);
+      const ulonglong2 k4 = kn2[4 * ch + c / 4];
+      float a0, a1;
+      f2_unpack(f2_fma(f2_pack(s[ch & 1][c], s[ch & 1][c + 1]), (c & 2) ? k4.y : k4.x, neg_m), a0, a1);
       if (MASK) {
         a0 = key0 + 16 * ch + c > q_pos ? -INFINITY : a0;
         a1 = key0 + 16 * ch + c + 1 > q_pos ? -INFINITY : a1;
       }
       const float e0 = fast_exp2(a0), e1 = fast_exp2(a1);
-      sum0 += e0;
-      sum1 += e1;
+      sum = f2_add(sum, f2_pack(e0, e1));
       pk[c / 2] = pack_half2(e0, e1);
     }
     umma::tmem_st8(s_col + 8 * ch, pk);
   }
-  return sum0 + sum1;
+  float s0, s1;
+  f2_unpack(sum, s0, s1);
+  return s0 + s1;
 }
 
+// fp16 pairs times a common factor (a power of two here).
+__device__ __forceinline__ uint32_t hmul2_scalar(uint32_t pair, float f) {
+  const __half2 r = __hmul2(*reinterpret_cast<const __half2*>(&pair), __float2half2_rn(f));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+// Multiplies `chunks` 8-column pieces of fp16 pairs starting at column `col` of this thread's TMEM lane by f.
+__device__ __forceinline__ void scale_p_chunks(uint32_t col, int chunks, float f) {
+  umma::tmem_wait_st();
+#pragma unroll 1
+  for (int cc = 0; cc < chunks; ++cc) {
+    uint32_t pp[8];
+    umma::tmem_ld8(col + 8 * cc, pp);
+    umma::tmem_wait_ld();
+#pragma unroll
+    for (int i = 0; i < 8; ++i) pp[i] = hmul2_scalar(pp[i], f);
+    umma::tmem_st8(col + 8 * cc, pp);
+  }
+}
+// The one-pass form of the two functions above for every tile but a row's first: the probabilities are taken against
+// the reference m the row already has (its running maximum before this tile) instead of the tile's own maximum, which
+// saves the first read of the scores and the wait for the other half of the row.  An fp16 probability can carry 2^15;
+// whenever a chunk of 16 scores would pass 2^kSafe the thread moves its own reference up by a whole number d of
+// binary orders first (its earlier probabilities of this tile and their sum are multiplied by 2^-d).  `shift` returns
+// the total of those moves; the caller settles the two halves of a row on the larger shift before P is published.
+constexpr float kSafe = 14.0f;
+template <bool MASK>
+__device__ __forceinline__ float row_probabilities_stale(uint32_t s_col, const float* kn, float m, int key0, int q_pos, float& shift) {
+  uint64_t sum = f2_pack(0.f, 0.f);
+  uint64_t neg_ref = f2_pack(-m, -m);
+  const ulonglong2* kn2 = reinterpret_cast<const ulonglong2*>(kn);
+  shift = 0.f;
+  uint32_t s[2][16];
+  umma::tmem_ld16(s_col, s[0]);
+#pragma unroll
+  for (int ch = 0; ch < 4; ++ch) {
+    uint32_t pk[8];
+    umma::tmem_wait_ld();
+    if (ch < 3) umma::tmem_ld16(s_col + 16 * (ch + 1), s[(ch + 1) & 1]);
+    float a[16];
+#pragma unroll
+    for (int c = 0; c < 16; c += 2) {
+      const ulonglong2 k4 = kn2[4 * ch + c / 4];
+      f2_unpack(f2_fma(f2_pack(s[ch & 1][c], s[ch & 1][c + 1]), (c & 2) ? k4.y : k4.x, neg_ref), a[c], a[c + 1]);
+      if (MASK) {
+        a[c] = key0 + 16 * ch + c > q_pos ? -INFINITY : a[c];
+        a[c + 1] = key0 + 16 * ch + c + 1 > q_pos ? -INFINITY : a[c + 1];
+      }
+    }
+    float cmax = fmax3(a[0], a[1], a[2]);
+#pragma unroll
+    for (int c = 3; c < 15; c += 2) cmax = fmax3(cmax, a[c], a[c + 1]);
+    cmax = fmaxf(cmax, a[15]);
+    if (__any_sync(0xffffffffu, cmax > kSafe)) {             // rare: a score far above everything the row has seen
+      const float d = cmax > kSafe ? ceilf(fminf(cmax, 1.0e30f)) : 0.f;
+      const float f = fast_exp2(-d);
+      shift += d;
+      neg_ref = f2_pack(-(m + shift), -(m + shift));
+#pragma unroll
+      for (int c = 0; c < 16; ++c) a[c] -= d;
+      sum = f2_mul(sum, f2_pack(f, f));
+      scale_p_chunks(s_col, ch, f);                          // every lane takes part (factor 1 where d = 0)
+    }
+#pragma unroll
+    for (int c = 0; c < 16; c += 2) {
+      const float e0 = fast_exp2(a[c]), e1 = fast_exp2(a[c + 1]);
+      sum = f2_add(sum, f2_pack(e0, e1));
+      pk[c / 2] = pack_half2(e0, e1);
+    }
+    umma::tmem_st8(s_col + 8 * ch, pk);
+  }
+  float s0, s1;
+  f2_unpack(sum, s0, s1);
+  return s0 + s1;
+}
+
+// This thread's 64 fp32 columns of O times `factor`.
+__device__ __forceinline__ void rescale_o(uint32_t o_col, float factor) {
+#pragma unroll 1
+  for (int ch = 0; ch < 2; ++ch) {
+    uint32_t o[32];
+    umma::tmem_ld32(o_col + 32 * ch, o);
+    umma::tmem_wait_ld();
+#pragma unroll
+    for (int c = 0; c < 32; c += 2) {
+      float o0, o1;
+      f2_unpack(f2_mul(f2_pack(o[c], o[c + 1]), f2_pack(factor, factor)), o0, o1);
+      o[c] = __float_as_uint(o0);
+      o[c + 1] = __float_as_uint(o1);
+    }
+    umma::tmem_st32(o_col + 32 * ch, o);
+  }
+}
 // Rows of 128 fp16 parked in shared memory: 256-byte rows, 16-byte chunk c of row r at chunk position c ^ (r & 15).
 __device__ __forceinline__ uint32_t staged_chunk(uint32_t area, uint32_t row, uint32_t chunk) {
   return area + row * 256u + ((chunk ^ (row & 15u)) << 4);
@@ -435,6 +540,8 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
       const int key0 = j * kKeys + 64 * half;
       const bool diag = key0 + 63 > q_offset + p0;           // some row of the CTA masks some of these keys
 
+      if (__any_sync(0xffffffffu, m_used == -INFINITY)) {
+      // a row without a reference yet (tile 0: key 0 is never masked, so every row has one afterwards): two passes
       // pass 1: maximum of this thread's 64 scaled scores (diagonal tiles take the masking variant)
       const float mx_own = diag ? row_max<true>(s_col, kn, key0, q_pos) : row_max<false>(s_col, kn, key0, q_pos);
       float mx = mx_own;
@@ -443,27 +550,36 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
       named_barrier(bar_id, group_threads);
       mx = fmaxf(mx, xch[((j & 1) * 2 + (half ^ 1)) * kRows + t]);
       float factor = 1.0f;
-      if (mx > m_used + kLazy || m_used == -INFINITY) {      // tile 0 always lands here (key 0 is never masked)
+      if (mx > m_used + kLazy || m_used == -INFINITY) {
         const float m_new = fmaxf(m_used, mx);
         factor = m_used == -INFINITY ? 0.0f : fast_exp2(m_used - m_new);
         m_used = m_new;
         l_run *= factor;
       }
       const bool rescale = j > 0 && __any_sync(0xffffffffu, factor != 1.0f);
-      if (rescale) {
-#pragma unroll 1
-        for (int ch = 0; ch < 2; ++ch) {
-          uint32_t o[32];
-          tmem_ld32(o_col + 32 * ch, o);
-          tmem_wait_ld();
-#pragma unroll
-          for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * factor);
-          tmem_st32(o_col + 32 * ch, o);
-        }
-      }
+      if (rescale) rescale_o(o_col, factor);
       // pass 2: probabilities.  The scores are read again from TMEM, 16 columns at a time; the fp16 P of a chunk
       // (keys 2c, 2c+1 in column c) goes straight over score columns this thread has already consumed.
       l_run += diag ? row_probabilities<true>(s_col, kn, m_used, key0, q_pos) : row_probabilities<false>(s_col, kn, m_used, key0, q_pos);
+      } else {
+      // one pass against the reference the row already has; the halves of a row then settle on a common reference
+      float shift;
+      float sum = diag ? row_probabilities_stale<true>(s_col, kn, m_used, key0, q_pos, shift)
+                       : row_probabilities_stale<false>(s_col, kn, m_used, key0, q_pos, shift);
+      xch[((j & 1) * 2 + half) * kRows + t] = shift;
+      named_barrier(bar_id, group_threads);
+      const float common = fmaxf(shift, xch[((j & 1) * 2 + (half ^ 1)) * kRows + t]);
+      if (__any_sync(0xffffffffu, common > 0.f)) {           // rare: some row of this warp moved its reference
+        const float f_own = fast_exp2(shift - common);       // this half's probabilities against the common reference
+        if (__any_sync(0xffffffffu, shift != common)) scale_p_chunks(s_col, 4, f_own);
+        sum *= f_own;
+        const float f_old = fast_exp2(-common);              // what the row had before this tile
+        rescale_o(o_col, f_old);                             // O is at rest: P V of this tile waits for the arrive below
+        l_run *= f_old;
+        m_used += common;
+      }
+      l_run += sum;
+      }
       tmem_wait_st();
       tc_fence_before_sync();
       __syncwarp();
@@ -490,8 +606,11 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
         for (int c8 = 0; c8 < 4; ++c8) {
           uint32_t h[4];
 #pragma unroll
-          for (int i = 0; i < 4; ++i)
-            h[i] = pack_half2(__uint_as_float(o[8 * c8 + 2 * i]) * inv, __uint_as_float(o[8 * c8 + 2 * i + 1]) * inv);
+          for (int i = 0; i < 4; ++i) {
+            float o0, o1;
+            f2_unpack(f2_mul(f2_pack(o[8 * c8 + 2 * i], o[8 * c8 + 2 * i + 1]), f2_pack(inv, inv)), o0, o1);
+            h[i] = pack_half2(o0, o1);
+          }
           const uint32_t chunk = static_cast<uint32_t>(8 * half + ch * 4 + c8);
           sts128(base + kOffK + row * 256u + ((chunk ^ (row & 15u)) << 4), h[0], h[1], h[2], h[3]);
         }
