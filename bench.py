@@ -569,18 +569,48 @@ def run_seqsplit(args):
         gathered[rank].copy_(packed)
         ops.merge_partials(gathered, out)
 
-    step_full()
+    # The step that is timed: with more than one rank the exchange happens inside the merge kernel (peer stores over
+    # NVLink, no collective library on the data path); the NCCL form of the same step is timed beside it.
+    use_peer = world > 1 and args.exchange == "peer"
+    if use_peer:
+        from sub0_b200.sharding import PeerExchange
+        px = PeerExchange(1, H_q, dev)
+        out_nccl = torch.empty_like(out)
+
+        def step_main():
+            px.decode(Q, cache, bt, sl, out, cb_K=cb, cb_V=cb, block_size=BLOCK, local_max_seq_len=max(n_loc, 1), workspace=ws)
+
+        def step_nccl():
+            partial()
+            exchange()
+            ops.merge_partials(gathered, out_nccl)
+    else:
+        step_main = step_full
+    step_main()
     torch.cuda.synchronize()
-    g_full = graph_of(step_full, args.warmup, torch)
+    g_full = graph_of(step_main, args.warmup, torch)
     sampler = ClockSampler(local)
     sampler.start()
     per_step, total_ms = timed_replays(g_full, args.steps, barrier, torch)
     sampler.stop()
     ms_step = max_over_ranks(total_ms) / args.steps
+    ms_nccl = None
+    if use_peer:
+        step_nccl()
+        torch.cuda.synchronize()
+        g_nccl = graph_of(step_nccl, 3, torch)
+        _, tot = timed_replays(g_nccl, args.steps, barrier, torch)
+        ms_nccl = max_over_ranks(tot) / args.steps
+        out_keep = out.clone()
     g_local = graph_of(step_no_exchange, 3, torch)
     _, tot = timed_replays(g_local, args.steps, barrier, torch)
     ms_local = max_over_ranks(tot) / args.steps
-    g_full.replay()
+    if use_peer:
+        out.copy_(out_keep)
+        if ops.workspace_status(ws) & 8:
+            raise SystemExit("decode_seqsplit: a wait for another rank's row ran out of time")
+    else:
+        g_full.replay()
     torch.cuda.synchronize()
 
     # ---- parity: KV head 0 of every rank's slots on rank 0, oracle over the whole sequence -----------------------------------------
@@ -606,20 +636,26 @@ def run_seqsplit(args):
                               torch.tensor([N], dtype=torch.int32), cb_K=cb.cpu(), cb_V=cb.cpu(), group=GROUP, block_size=BLOCK)
         t_cpu = time.perf_counter() - t0
         bad, worst, max_err = violations(out[:, :GROUP].cpu(), want)
+        if use_peer:                                   # the NCCL form of the step must agree with the oracle as well
+            bad_n, worst_n, _ = violations(out_nccl[:, :GROUP].cpu(), want)
+            bad, worst = bad + bad_n, max(worst, worst_n)
         peak, peak_src = measured_peak("hbm_gbs", 6650.0)
         rank_bytes = algorithmic_bytes(1, n_loc, H_KV, H_q)
         achieved = rank_bytes / (statistics.mean(per_step) * 1e-3) / 1e9
         value = bytes_job / (ms_step * 1e-3) / 1e9
         line = {"metric": "cda_decode_seqsplit_k4v4_hbm_gbs", "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms_step, "us_per_layer_median": statistics.median(per_step) * 1e3,
-                "us_without_allgather": ms_local * 1e3, "allgather_bytes_per_rank": H_q * 130 * 4,
+                "us_without_exchange": ms_local * 1e3, "exchange_bytes_per_rank": H_q * 132 * 4 * world if use_peer else H_q * 130 * 4,
+                "exchange": "peer stores inside the merge kernel" if use_peer else ("nccl all-gather" if world > 1 else "none"),
+                "nccl_us_per_step": None if ms_nccl is None else ms_nccl * 1e3,
                 "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
                 "config": config(args, world), "frac_of_8000_gbs_nominal": value / (8000.0 * world),
                 "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": UNIT, "frac": achieved / peak,
                              "peak_source": peak_src, "traffic": None,
-                             "note": "rank-0 step = partial (split + merge-to-packed kernels) + all-gather + merge kernel over "
-                                     "this rank's key range; latency-bound at 8 ranks (17.8 us of traffic per rank at 8 TB/s)"},
-                "e2e": None, "gpu_launches": 3 * args.steps, "clocks": sampler.summary(),
+                             "note": "rank-0 step = split kernel + one merge kernel that exchanges the packed rows with the other ranks "
+                                     "(peer stores) and merges them; the NCCL form is partial + all-gather + merge (nccl_us_per_step); "
+                                     "latency-bound at 8 ranks (17.8 us of traffic per rank at 8 TB/s)"},
+                "e2e": None, "gpu_launches": (2 if use_peer else 3) * args.steps, "clocks": sampler.summary(),
                 "parity_sample": {"ok": bad == 0, "violations": bad, "worst_err_over_bound": worst, "max_abs_err": max_err,
                                   "elements": int(want.numel()),
                                   "what": "KV head 0 (its 8 query heads) over all ranks' slots against the CPU oracle",
@@ -633,9 +669,12 @@ def run_seqsplit(args):
 
     def e2e_enqueue():
         dQ.copy_(hQ, non_blocking=True)
-        ops.decode_partial(dQ, cache, bt, sl, cb_K=cb, cb_V=cb, block_size=BLOCK, max_seq_len=max(n_loc, 1), workspace=ws, out=packed)
-        exchange()
-        ops.merge_partials(gathered, out)
+        if use_peer:
+            px.decode(dQ, cache, bt, sl, out, cb_K=cb, cb_V=cb, block_size=BLOCK, local_max_seq_len=max(n_loc, 1), workspace=ws)
+        else:
+            ops.decode_partial(dQ, cache, bt, sl, cb_K=cb, cb_V=cb, block_size=BLOCK, max_seq_len=max(n_loc, 1), workspace=ws, out=packed)
+            exchange()
+            ops.merge_partials(gathered, out)
         hout.copy_(out, non_blocking=True)
 
     for _ in range(3):
@@ -656,8 +695,8 @@ def run_seqsplit(args):
     if rank == 0:
         line["e2e"] = {"value": bytes_job / (e2e_ms * 1e-3) / 1e9, "unit": UNIT, "ms_per_step": e2e_ms,
                        "h2d_bytes_per_step": hQ.numel() * 2 * world, "d2h_bytes_per_step": hout.numel() * 2 * world,
-                       "what": "pinned H2D of Q + partial + all-gather + merge + D2H of the output, one CUDA graph replayed and "
-                               "synchronised every step; the KV cache is resident state"}
+                       "what": "pinned H2D of Q + the timed step + D2H of the output, one CUDA graph replayed and synchronised "
+                               "every step; the KV cache is resident state"}
         print(json.dumps(line), flush=True)
     failed = rank == 0 and line["parity_sample"]["violations"] > 0
     if world > 1:
@@ -938,6 +977,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-sustained", action="store_true", help="skip the >= 2 s sustained replay loop")
     ap.add_argument("--no-identity-order", action="store_true", help="skip the identity-page-order figure")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="decode_seqsplit on more than one GPU: exchange inside the merge kernel (peer stores) or NCCL all-gather")
     ap.add_argument("--no-other-kernels", action="store_true",
                     help="default cell on one GPU: leave the encode / prefill figures out of the line")
     ap.add_argument("--workload", default="decode", choices=["decode", "decode_seqsplit", "encode", "prefill"],

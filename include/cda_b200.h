@@ -147,6 +147,35 @@ int cda_b200_merge_partials(const float* O, const float* m, const float* l, int 
  * (e.g. the all-gathered partials of S ranks).  Follows merge_partials, cda/algorithm/attention.py:239-272. */
 int cda_b200_merge_partials_packed(const float* packed, int S, int64_t R, void* out, int unrotate, void* stream);
 
+/* Sequence-sharded decode with the exchange inside the merge kernel (no collective library on the data path): every rank
+ * holds a different key range of the same sequences and the same Q.  One call = the split kernel over the local keys +
+ * one kernel that merges the local pieces, stores this rank's packed row (O[128], m, l, the call's tag) into EVERY rank's
+ * exchange buffer with peer stores over NVLink, waits -- at most wait_ms per row -- until every rank's row of this call
+ * has arrived in its own buffer, merges them (cda/algorithm/attention.py:239-272) and writes fp16 out (B,H_q,128).  It
+ * replaces cda_b200_decode_partial_packed + all-gather + cda_b200_merge_partials_packed; the reference leaves the path as
+ * NotImplementedError (cda_attn_v2.py:1697-1701).
+ *   peer_buffers: DEVICE array of `world` device pointers; entry p is rank p's exchange buffer of
+ *                 cda_b200_decode_exchange_bytes(B, H_q, world) bytes (entry `rank` is this rank's own), zeroed once,
+ *                 16-byte aligned, mapped into this process (CUDA IPC or VMM) with peer access enabled;
+ *   counters:     two uint64 in THIS rank's device memory, zeroed once (calls completed, rows finished);
+ * every rank of the group must make the same sequence of calls with the same B and H_q.  A row that does not arrive in
+ * time is left out of the merge and bit 3 of the workspace status word is set; nothing waits without a limit. */
+size_t cda_b200_decode_exchange_bytes(int B, int H_q, int world);
+/* Exchange buffers for cda_b200_decode_exchange: a zeroed device allocation on the current device (alloc / free), its
+ * 64-byte CUDA IPC handle (export), and the mapping of another process's handle into this process with peer access
+ * enabled on demand (import / close).  The handles are plain bytes: send them over any channel between the ranks. */
+int cda_b200_exchange_alloc(size_t nbytes, void** ptr);
+int cda_b200_exchange_free(void* ptr);
+int cda_b200_exchange_export(const void* ptr, void* handle64);
+int cda_b200_exchange_import(const void* handle64, void** ptr);
+int cda_b200_exchange_close(void* ptr);
+int cda_b200_decode_exchange(const void* Q, const void* kv_cache, const int32_t* block_table, const int32_t* seq_lens,
+                             const float* cb_K, const float* cb_V, void* out, void* workspace, size_t workspace_bytes,
+                             void* const* peer_buffers, unsigned long long* counters, int rank, int world, int wait_ms,
+                             int B, int H_q, int H_kv, int block_size, int block_table_stride, int max_seq_len,
+                             int64_t num_slots, int slot_bytes, int k_bits, int v_bits, float scale, int num_splits,
+                             void* stream);
+
 /* cda_b200_decode for callers that cannot hand over a workspace: the split-KV scratch is an 8 MiB array compiled into
  * the library (file-scope device memory; every GPU that loads the library holds it until the process exits).  Meant for
  * hosts where device allocation is off limits at call time -- a runtime whose memory pool is fixed at start-up and

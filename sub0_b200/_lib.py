@@ -38,6 +38,14 @@ PROTOTYPES = {
                                             _f, _i, _p]),
     "cda_b200_merge_partials": (_i, [_p, _p, _p, _i, _i64, _p, _i, _p]),
     "cda_b200_merge_partials_packed": (_i, [_p, _i, _i64, _p, _i, _p]),
+    "cda_b200_decode_exchange_bytes": (_sz, [_i, _i, _i]),
+    "cda_b200_exchange_alloc": (_i, [_sz, _p]),
+    "cda_b200_exchange_free": (_i, [_p]),
+    "cda_b200_exchange_export": (_i, [_p, _p]),
+    "cda_b200_exchange_import": (_i, [_p, _p]),
+    "cda_b200_exchange_close": (_i, [_p]),
+    "cda_b200_decode_exchange": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _sz, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i64,
+                                      _i, _i, _i, _f, _i, _p]),
     "cda_b200_decode_static": (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i64, _i, _i, _i, _f, _i, _p]),
     "cda_b200_decode_scalar": (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i64, _i, _i, _i, _f, _p]),
     "cda_b200_cache_to_dense_rotated": (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i64, _i, _i, _i, _p]),

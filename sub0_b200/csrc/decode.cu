@@ -36,6 +36,7 @@
 
 #include <cuda.h>   // CUtensorMap and the enums of cuTensorMapEncodeTiled (types only: the entry point is looked up at run time)
 
+#include <cstring>
 #include "common.cuh"
 
 namespace cda {
@@ -743,7 +744,19 @@ __global__ void __launch_bounds__(W * 32, 1) decode_split_kernel(const DecodePar
 //         out_m / out_l + row * out_ml_stride.
 // When chunk_groups > 0 the partials come from decode_split_kernel and row r (sequence r / rows_per_seq) owns only the
 // pieces its sequence's positions touch; pieces beyond that were never written and are not read.
+// Exchange of merged partials between the ranks of a sequence-sharded decode (mode 2 of the merge): every rank owns a
+// buffer of [2 parities][world senders][rows] exchange rows and knows the address of every other rank's buffer (peer
+// memory).  A row is 132 floats: O[128], m (log2 domain), l, the tag of the call that wrote it, one pad float.
+constexpr int kXchRowFloats = kHeadDim + 4;
+struct ExchangeParams {
+  float* const* peers;            // device array of `world` pointers: peers[p] = rank p's exchange buffer
+  unsigned long long* counters;   // this rank's [0] calls completed, [1] rows finished in the running call
+  int* status;                    // bit 3: a wait for another rank's row ran out of time
+  int rank, world;
+  unsigned long long wait_ns;
+};
 struct MergeParams {
+  ExchangeParams x;
   const float* part_o; const float* part_m; const float* part_l;
   int ml_stride, o_stride, P;
   int64_t rows;
@@ -767,8 +780,85 @@ __device__ __forceinline__ float4 merge_load4(const float* ptr, bool vec4) {
   return make_float4(a.x, a.y, b.x, b.y);
 }
 
+__device__ __forceinline__ void st_release_sys(uint32_t* ptr, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(ptr), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* ptr) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(ptr) : "memory");
+  return v;
+}
+// Mode 2: this rank's merged row (ot, mt, lt) goes to every rank's buffer with plain peer stores, followed by the call's
+// tag with release semantics; then the warp waits -- lane s for sender s, for at most wait_ns -- until every sender's
+// row of this call has arrived in its own buffer, and merges them.  Nothing here waits on another warp of this GPU: a
+// warp first sends, then waits, so the ranks cannot block one another.  A sender that does not show up in time is left
+// out and reported (status bit 3).  Two parities suffice: a rank can start call k+2 only after every rank has finished
+// reading call k (its call k+1 needs every rank's k+1 rows, which are sent after their call k kernel has ended).
+__device__ __forceinline__ void exchange_rows(const MergeParams& q, float (&ot)[4], float& lt, float& mt, int64_t row, int lane) {
+  const ExchangeParams& x = q.x;
+  const unsigned long long call = *reinterpret_cast<volatile unsigned long long*>(x.counters) + 1;   // bumped after the last row
+  const uint32_t tag = static_cast<uint32_t>(call);
+  const int64_t slot0 = static_cast<int64_t>(call & 1) * x.world;
+  const int64_t my_off = ((slot0 + x.rank) * q.rows + row) * kXchRowFloats;
+  for (int p = 0; p < x.world; ++p) {
+    float* dst = x.peers[p] + my_off;
+    *reinterpret_cast<float4*>(dst + 4 * lane) = make_float4(ot[0], ot[1], ot[2], ot[3]);
+    if (lane == 0) *reinterpret_cast<float2*>(dst + kHeadDim) = make_float2(mt, lt);
+  }
+  __threadfence_system();
+  __syncwarp();
+  if (lane < x.world) st_release_sys(reinterpret_cast<uint32_t*>(x.peers[lane] + my_off + kHeadDim + 2), tag);
+
+  const float* mine = x.peers[x.rank];
+  const float* src_row = mine + ((slot0 + (lane < x.world ? lane : 0)) * q.rows + row) * kXchRowFloats;
+  bool got = lane >= x.world;
+  unsigned long long t0;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  for (uint32_t spin = 1;; ++spin) {
+    if (!got) got = ld_acquire_sys(reinterpret_cast<const uint32_t*>(src_row + kHeadDim + 2)) == tag;
+    if (__all_sync(0xffffffffu, got)) break;
+    if ((spin & 31u) == 0u) {
+      unsigned long long t;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+      if (__any_sync(0xffffffffu, t - t0 > x.wait_ns)) {
+        if (lane == 0) atomicOr(x.status, 8);
+        break;
+      }
+    }
+  }
+  __syncwarp();
+  float ms = -INFINITY, ls = 0.f;
+  if (lane < x.world && got) {
+    const float2 ml = __ldcg(reinterpret_cast<const float2*>(src_row + kHeadDim));
+    ms = ml.x; ls = ml.y;
+  }
+  float mall = ms;
+#pragma unroll
+  for (int mask = 16; mask > 0; mask >>= 1) mall = fmaxf(mall, __shfl_xor_sync(0xffffffffu, mall, mask));
+  const float bw = ms == -INFINITY ? 0.f : fast_exp2(ms - mall);
+  lt = warp_sum(ls * bw);
+  mt = mall;
+  ot[0] = ot[1] = ot[2] = ot[3] = 0.f;
+  for (int sdr = 0; sdr < x.world; ++sdr) {
+    const float w = __shfl_sync(0xffffffffu, bw, sdr);
+    if (w == 0.f) continue;
+    const float4 o = __ldcg(reinterpret_cast<const float4*>(mine + ((slot0 + sdr) * q.rows + row) * kXchRowFloats + 4 * lane));
+    ot[0] += o.x * w; ot[1] += o.y * w; ot[2] += o.z * w; ot[3] += o.w * w;
+  }
+  if (lane == 0) {   // the last row of the call closes it
+    const unsigned long long done = atomicAdd(x.counters + 1, 1ull);
+    if (done == static_cast<unsigned long long>(q.rows) - 1) {
+      x.counters[1] = 0ull;
+      __threadfence();
+      *reinterpret_cast<volatile unsigned long long*>(x.counters) = call;
+    }
+  }
+}
+
 // Last step of a merge: lane l holds coordinates 4l .. 4l+3 of the summed row, every lane the row's l and maximum.
-__device__ __forceinline__ void merge_finish(const MergeParams& q, const float (&ot)[4], float lt, float mt, int64_t row, int lane) {
+__device__ __forceinline__ void merge_finish(const MergeParams& q, const float (&ot_in)[4], float lt, float mt, int64_t row, int lane) {
+  float ot[4] = {ot_in[0], ot_in[1], ot_in[2], ot_in[3]};
+  if (q.mode == 2) exchange_rows(q, ot, lt, mt, row, lane);
   if (q.mode == 1) {
     float* dst = q.out_o + row * q.out_o_stride + 4 * lane;
     if ((q.out_o_stride & 3) == 0) *reinterpret_cast<float4*>(dst) = make_float4(ot[0], ot[1], ot[2], ot[3]);
@@ -1223,6 +1313,7 @@ struct DecodeSink {
   __half* out; float* lse;
   float* O; float* m; float* l;
   int o_stride, ml_stride;
+  ExchangeParams x;
 };
 
 static int decode_run(const char* who, const DecodeCommon& a, const DecodeSink& sink, void* workspace, size_t workspace_bytes,
@@ -1237,6 +1328,8 @@ static int decode_run(const char* who, const DecodeCommon& a, const DecodeSink& 
   q.m_to_log2 = 1.0f; q.mode = sink.mode; q.unrotate = 1; q.out = sink.out; q.out_lse = sink.lse;
   q.out_o = sink.O; q.out_m = sink.m; q.out_l = sink.l; q.out_o_stride = sink.o_stride; q.out_ml_stride = sink.ml_stride;
   q.rows_per_seq = a.H_q; q.chunk_groups = pl.chunk_groups; q.groups_pad = pl.groups_pad;
+  q.x = sink.x;
+  q.x.status = reinterpret_cast<int*>(workspace);
   launch_merge(q, st);
   return check_launch("decode merge kernel");
 }
@@ -1262,7 +1355,7 @@ static int decode_fp16(const char* who, const DecodeCommon& a, void* out, float*
   if (!out) return fail(CDA_ERR_BAD_ARG, "%s: null output", who);
   if (reinterpret_cast<uintptr_t>(out) & 7u) return fail(CDA_ERR_BAD_ALIGN, "%s: output must be 8-byte aligned", who);
   if (num_splits < 0) return fail(CDA_ERR_BAD_ARG, "%s: negative num_splits", who);
-  const DecodeSink sink{0, static_cast<__half*>(out), lse, nullptr, nullptr, nullptr, 0, 0};
+  const DecodeSink sink{0, static_cast<__half*>(out), lse, nullptr, nullptr, nullptr, 0, 0, {}};
   return decode_run(who, a, sink, workspace, workspace_bytes, make_plan(a.B, a.H_kv, a.max_seq_len, num_splits, device_sm_count(-1)),
                     static_cast<cudaStream_t>(stream));
 }
@@ -1294,7 +1387,7 @@ static int decode_partial_any(const char* who, const DecodeCommon& a, float* O, 
   if (!O || !m || !l) return fail(CDA_ERR_BAD_ARG, "%s: null output", who);
   if (reinterpret_cast<uintptr_t>(O) & ((o_stride & 3) ? 7u : 15u)) return fail(CDA_ERR_BAD_ALIGN, "%s: O must be 16-byte aligned (packed rows: 8)", who);
   if (num_splits < 0) return fail(CDA_ERR_BAD_ARG, "%s: negative num_splits", who);
-  const DecodeSink sink{1, nullptr, nullptr, O, m, l, o_stride, ml_stride};
+  const DecodeSink sink{1, nullptr, nullptr, O, m, l, o_stride, ml_stride, {}};
   return decode_run(who, a, sink, workspace, workspace_bytes, make_plan(a.B, a.H_kv, a.max_seq_len, num_splits, device_sm_count(-1)),
                     static_cast<cudaStream_t>(stream));
 }
@@ -1319,6 +1412,74 @@ extern "C" int cda_b200_decode_partial_packed(const void* Q, const void* kv_cach
   constexpr int kPacked = kHeadDim + 2;
   return decode_partial_any("decode_partial_packed", a, packed, packed ? packed + kHeadDim : nullptr,
                             packed ? packed + kHeadDim + 1 : nullptr, kPacked, kPacked, workspace, workspace_bytes, num_splits, stream);
+}
+
+// ---- exchange buffers: plain device allocations, shared between the processes of a node by CUDA IPC handles -----------------
+extern "C" int cda_b200_exchange_alloc(size_t nbytes, void** ptr) {
+  if (!ptr || nbytes == 0) return fail(CDA_ERR_BAD_ARG, "exchange_alloc: bad argument");
+  void* p = nullptr;
+  if (cudaMalloc(&p, nbytes) != cudaSuccess || cudaMemset(p, 0, nbytes) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess) {
+    if (p) cudaFree(p);
+    return check_launch("exchange_alloc");
+  }
+  *ptr = p;
+  return CDA_OK;
+}
+extern "C" int cda_b200_exchange_free(void* ptr) {
+  if (ptr && cudaFree(ptr) != cudaSuccess) return check_launch("exchange_free");
+  return CDA_OK;
+}
+extern "C" int cda_b200_exchange_export(const void* ptr, void* handle64) {
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  if (!ptr || !handle64) return fail(CDA_ERR_BAD_ARG, "exchange_export: null pointer");
+  cudaIpcMemHandle_t h;
+  if (cudaIpcGetMemHandle(&h, const_cast<void*>(ptr)) != cudaSuccess) return check_launch("exchange_export");
+  memcpy(handle64, &h, sizeof h);
+  return CDA_OK;
+}
+extern "C" int cda_b200_exchange_import(const void* handle64, void** ptr) {
+  if (!handle64 || !ptr) return fail(CDA_ERR_BAD_ARG, "exchange_import: null pointer");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof h);
+  void* p = nullptr;
+  if (cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) return check_launch("exchange_import");
+  *ptr = p;
+  return CDA_OK;
+}
+extern "C" int cda_b200_exchange_close(void* ptr) {
+  if (ptr && cudaIpcCloseMemHandle(ptr) != cudaSuccess) return check_launch("exchange_close");
+  return CDA_OK;
+}
+
+extern "C" size_t cda_b200_decode_exchange_bytes(int B, int H_q, int world) {
+  if (B <= 0 || H_q <= 0 || world <= 0) return 0;
+  return static_cast<size_t>(2) * world * B * H_q * kXchRowFloats * sizeof(float);
+}
+
+extern "C" int cda_b200_decode_exchange(const void* Q, const void* kv_cache, const int32_t* block_table, const int32_t* seq_lens,
+                                        const float* cb_K, const float* cb_V, void* out, void* workspace, size_t workspace_bytes,
+                                        void* const* peer_buffers, unsigned long long* counters, int rank, int world, int wait_ms,
+                                        int B, int H_q, int H_kv, int block_size, int block_table_stride, int max_seq_len,
+                                        int64_t num_slots, int slot_bytes, int k_bits, int v_bits, float scale, int num_splits,
+                                        void* stream) {
+  const DecodeCommon a{Q, kv_cache, block_table, seq_lens, cb_K, cb_V, B, H_q, H_kv, block_size, block_table_stride,
+                       max_seq_len, num_slots, slot_bytes, k_bits, v_bits, scale};
+  const int rc = validate("decode_exchange", a);
+  if (rc != CDA_OK) return rc;
+  if (B == 0) return fail(CDA_ERR_BAD_ARG, "decode_exchange: B = 0 (every rank must take part in every call)");
+  if (world < 1 || world > 32 || rank < 0 || rank >= world) return fail(CDA_ERR_BAD_ARG, "decode_exchange: rank %d of %d (at most 32 ranks)", rank, world);
+  if (!out || !peer_buffers || !counters) return fail(CDA_ERR_BAD_ARG, "decode_exchange: null pointer");
+  if ((reinterpret_cast<uintptr_t>(out) & 7u) || (reinterpret_cast<uintptr_t>(counters) & 7u) || (reinterpret_cast<uintptr_t>(peer_buffers) & 7u))
+    return fail(CDA_ERR_BAD_ALIGN, "decode_exchange: out, counters and the pointer array must be 8-byte aligned");
+  if (wait_ms <= 0 || wait_ms > 10000) return fail(CDA_ERR_BAD_ARG, "decode_exchange: wait_ms must be in 1 .. 10000");
+  if (num_splits < 0) return fail(CDA_ERR_BAD_ARG, "decode_exchange: negative num_splits");
+  DecodeSink sink{2, static_cast<__half*>(out), nullptr, nullptr, nullptr, nullptr, 0, 0, {}};
+  sink.x.peers = reinterpret_cast<float* const*>(peer_buffers);
+  sink.x.counters = counters;
+  sink.x.rank = rank; sink.x.world = world;
+  sink.x.wait_ns = static_cast<unsigned long long>(wait_ms) * 1000000ull;
+  return decode_run("decode_exchange", a, sink, workspace, workspace_bytes,
+                    make_plan(a.B, a.H_kv, a.max_seq_len, num_splits, device_sm_count(-1)), static_cast<cudaStream_t>(stream));
 }
 
 static int merge_any(const char* who, const float* O, const float* m, const float* l, int o_stride, int ml_stride, int S, int64_t R,

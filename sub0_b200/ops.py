@@ -259,6 +259,35 @@ def decode_partial(Q: Tensor, kv_cache: Tensor, block_table: Tensor, seq_lens: T
     return packed
 
 
+def decode_exchange_bytes(B: int, H_q: int, world: int) -> int:
+    """Bytes of one rank's exchange buffer for :func:`decode_exchange`."""
+    return int(lib.cda_b200_decode_exchange_bytes(B, H_q, world))
+
+
+def decode_exchange(Q: Tensor, kv_cache: Tensor, block_table: Tensor, seq_lens: Tensor, output: Tensor, *, cb_K: Tensor,
+                    cb_V: Tensor, block_size: int, peer_pointers: Tensor, counters: Tensor, rank: int, world: int,
+                    scale: Optional[float] = None, max_seq_len: Optional[int] = None, num_splits: int = 0,
+                    wait_ms: int = 1000, workspace: Optional[Tensor] = None) -> None:
+    """Sequence-sharded decode step with the exchange inside the merge kernel: this rank's keys are in ``kv_cache``, ``Q``
+    is the same on every rank, ``output`` (B, H_q, 128) fp16 is the merged result on every rank.  ``peer_pointers``:
+    int64 CUDA tensor of ``world`` device addresses (every rank's exchange buffer, see
+    :class:`sub0_b200.sharding.PeerExchange`), ``counters``: two zeroed int64 on this device."""
+    a = _decode_args(Q, kv_cache, block_table, seq_lens, cb_K, cb_V, block_size, scale, max_seq_len)
+    if output.dtype != torch.float16 or output.shape != Q.shape or not output.is_contiguous() or not output.is_cuda:
+        raise ValueError("output must be a contiguous fp16 CUDA tensor shaped like Q")
+    if peer_pointers.dtype != torch.int64 or not peer_pointers.is_cuda or peer_pointers.numel() != world:
+        raise ValueError("peer_pointers must be an int64 CUDA tensor with one address per rank")
+    if counters.dtype != torch.int64 or not counters.is_cuda or counters.numel() < 2:
+        raise ValueError("counters must be an int64 CUDA tensor of two elements")
+    need = decode_workspace_bytes(a.B, a.Hq, a.Hkv, a.max_len, num_splits)
+    ws = _workspace(need, Q.device, workspace)
+    check(lib.cda_b200_decode_exchange(a.Q.data_ptr(), a.cache.data_ptr(), a.bt.data_ptr(), a.sl.data_ptr(), a.cbk.data_ptr(),
+                                       a.cbv.data_ptr(), output.data_ptr(), ws.data_ptr(), ws.numel(), peer_pointers.data_ptr(),
+                                       counters.data_ptr(), rank, world, wait_ms, a.B, a.Hq, a.Hkv, a.bs, a.bt.shape[1],
+                                       a.max_len, a.cache.shape[0], a.cache.shape[2], a.kb, a.vb, a.scale, num_splits,
+                                       _stream(Q.device)))
+
+
 def merge_partials(packed: Tensor, output: Tensor, *, unrotate: bool = True) -> None:
     """Merge (S, ..., 130) packed partials (see :func:`decode_partial`) into fp16 ``output`` (..., 128)."""
     _cuda(packed, "packed", torch.float32)

@@ -8,7 +8,8 @@
   owns a contiguous, block-aligned range of keys of every head.  Each rank produces the un-normalised partial
   ``(O, m, l)`` of its keys, one all-gather moves ``(B, H_q, 130)`` fp32 per rank, and every rank merges locally --
   the path the reference leaves as ``NotImplementedError`` (``cda_attn_v2.py:1697-1701``) with the contract of
-  ``cda/algorithm/attention.py:190-272``.
+  ``cda/algorithm/attention.py:190-272``.  :class:`PeerExchange` is the same step without a collective library: the
+  merge kernel stores its row into every GPU's memory over NVLink and merges what the others stored.
 """
 from __future__ import annotations
 
@@ -71,6 +72,69 @@ def decode_sequence_sharded(Q: Tensor, local_cache: Tensor, local_block_table: T
     packed = ops.decode_partial(Q, local_cache, local_block_table, local_seq_lens, cb_K=cb_K, cb_V=cb_V,
                                 block_size=block_size, scale=scale, max_seq_len=local_max_seq_len, workspace=workspace)
     ops.merge_partials(gather_partials(packed, group), output)
+
+
+class PeerExchange:
+    """Exchange buffers of a sequence-sharded decode group: one buffer per rank, each mapped into every process of the
+    node (CUDA IPC handles travel over the process group), so that the merge kernel can store its row straight into the
+    other GPUs' memory.  Collective: every rank of ``group`` constructs it with the same ``B`` and ``H_q``.  The
+    buffers live until :meth:`close` (collective as well); keep the object for the lifetime of the decode loop and of
+    any CUDA graph captured over :meth:`decode`."""
+
+    def __init__(self, B: int, H_q: int, device: torch.device, group: Optional[dist.ProcessGroup] = None):
+        import ctypes as C
+        from . import ops
+        from ._lib import check, lib
+        self.group = group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.B, self.H_q = B, H_q
+        self._lib, self._own, self._imported = lib, None, []
+        nbytes = ops.decode_exchange_bytes(B, H_q, self.world)
+        with torch.cuda.device(device):
+            own = C.c_void_p()
+            check(lib.cda_b200_exchange_alloc(nbytes, C.byref(own)))
+            self._own = own.value
+            raw = C.create_string_buffer(64)
+            check(lib.cda_b200_exchange_export(self._own, raw))
+            handles = [None] * self.world
+            dist.all_gather_object(handles, raw.raw, group=group)
+            addresses = []
+            for r, h in enumerate(handles):
+                if r == self.rank:
+                    addresses.append(self._own)
+                    continue
+                ptr = C.c_void_p()
+                check(lib.cda_b200_exchange_import(C.create_string_buffer(h, 64), C.byref(ptr)))
+                self._imported.append(ptr.value)
+                addresses.append(ptr.value)
+        self.counters = torch.zeros(2, dtype=torch.int64, device=device)
+        self.pointers = torch.tensor(addresses, dtype=torch.int64, device=device)
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group)                                  # nobody sends before every mapping exists
+
+    def close(self) -> None:
+        """Unmap the other ranks' buffers and free this rank's (after a barrier: nobody may still be sending)."""
+        if self._own is None:
+            return
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+        for ptr in self._imported:
+            self._lib.cda_b200_exchange_close(ptr)
+        self._lib.cda_b200_exchange_free(self._own)
+        self._own, self._imported = None, []
+
+    def decode(self, Q: Tensor, local_cache: Tensor, local_block_table: Tensor, local_seq_lens: Tensor, output: Tensor, *,
+               cb_K: Tensor, cb_V: Tensor, block_size: int, local_max_seq_len: int, scale: Optional[float] = None,
+               workspace: Optional[Tensor] = None, wait_ms: int = 1000) -> None:
+        """One decode step: split kernel over the local keys, then ONE kernel that merges, exchanges and merges again
+        (see ``cda_b200_decode_exchange``).  Same precondition on ``Q`` as :func:`decode_sequence_sharded`."""
+        from . import ops
+        if Q.shape[0] != self.B or Q.shape[1] != self.H_q:
+            raise ValueError("Q does not match the exchange buffers")
+        ops.decode_exchange(Q, local_cache, local_block_table, local_seq_lens, output, cb_K=cb_K, cb_V=cb_V,
+                            block_size=block_size, peer_pointers=self.pointers, counters=self.counters, rank=self.rank,
+                            world=self.world, scale=scale, max_seq_len=local_max_seq_len, wait_ms=wait_ms,
+                            workspace=workspace)
 
 
 def gather_heads(q_local: Tensor, H_kv: int, group: Optional[dist.ProcessGroup] = None) -> Tensor:

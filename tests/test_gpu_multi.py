@@ -1,6 +1,7 @@
 """Two-GPU checks (skipped with fewer than 2 devices): KV-head sharding reproduces the single-GPU output (same kernel,
 same bytes, no collective; only the fp32 summation order changes because fewer heads per CTA means more warps per
-head), and sequence sharding (partial -> all-gather -> merge) matches the oracle."""
+head), and sequence sharding matches the oracle both as partial -> all-gather -> merge and with the exchange inside the
+merge kernel (peer stores)."""
 import os
 import socket
 
@@ -61,6 +62,22 @@ def _rank_main(rank, world, port, q):
                                 local_max_seq_len=max(local_max, 1))
         torch.cuda.synchronize()
         ok, ratio, cos = Cs.close(out.cpu(), want)
+        # --- the same step with the exchange inside the merge kernel (peer stores, no collective): three calls, so that
+        # both parities of the exchange buffers and a re-used parity are exercised; then the status word (bit 3 = a wait
+        # for the other rank ran out of time) must be clear
+        from sub0_b200.sharding import PeerExchange
+        px = PeerExchange(2, 16, dev)
+        ws = ops.new_workspace(ops.decode_workspace_bytes(2, 16, 4, max(local_max, 1)), dev)
+        for call in range(3):
+            out_px = torch.full((2, 16, 128), float("nan"), dtype=torch.float16, device=dev)
+            px.decode(case["Q"].to(dev), case["cache"].to(dev), bt.to(dev), torch.tensor(lens, dtype=torch.int32, device=dev),
+                      out_px, cb_K=case["cb_K"].to(dev), cb_V=case["cb_V"].to(dev), block_size=16,
+                      local_max_seq_len=max(local_max, 1), workspace=ws)
+            torch.cuda.synchronize()
+            ok_px, ratio_px, _ = Cs.close(out_px.cpu(), want)
+            ok, ratio = ok and ok_px, max(ratio, ratio_px)
+        ok = ok and ops.workspace_status(ws) == 0 and int(px.counters[0]) == 3
+        px.close()
         # --- the vLLM backend's decode-context-parallel path (gathers over the default group).  The DCP group lies inside
         # the tensor-parallel group: both ranks share the two KV heads, each holds FOUR of the eight query heads of every
         # KV head (distinct queries per rank) and its own key range of every sequence.
