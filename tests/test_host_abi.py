@@ -105,6 +105,18 @@ def test_status_codes_without_gpu(lib):
                                  None) == lib.CDA_ERR_BAD_ARG
     assert L.cda_b200_merge_partials_packed(al, 0, 4, al, 1, None) == lib.CDA_ERR_BAD_ARG
     assert L.cda_b200_merge_partials_packed(al + 4, 2, 4, al, 1, None) == lib.CDA_ERR_BAD_ALIGN
+    # the exchange form of the sequence-sharded decode: sizes and argument checks (nothing is launched)
+    assert L.cda_b200_decode_exchange_bytes(1, 64, 8) == 2 * 8 * 64 * 132 * 4
+    assert L.cda_b200_decode_exchange_bytes(0, 64, 8) == 0
+    ex = lambda **kw: L.cda_b200_decode_exchange(al, al, al, al, al, al, kw.get("out", al), al, 1 << 20, kw.get("peers", al),
+                                                 kw.get("counters", al), kw.get("rank", 0), kw.get("world", 2), kw.get("wait_ms", 100),
+                                                 kw.get("B", 1), 32, 8, 16, 4, 64, 64, 144, 4, 4, 0.1, 0, None)
+    assert ex(world=0) == lib.CDA_ERR_BAD_ARG and ex(rank=2) == lib.CDA_ERR_BAD_ARG and ex(world=33) == lib.CDA_ERR_BAD_ARG
+    assert ex(peers=None) == lib.CDA_ERR_BAD_ARG and ex(counters=None) == lib.CDA_ERR_BAD_ARG and ex(B=0) == lib.CDA_ERR_BAD_ARG
+    assert ex(wait_ms=0) == lib.CDA_ERR_BAD_ARG and ex(wait_ms=60000) == lib.CDA_ERR_BAD_ARG
+    assert ex(out=al + 4) == lib.CDA_ERR_BAD_ALIGN and ex(counters=al + 4) == lib.CDA_ERR_BAD_ALIGN
+    assert L.cda_b200_exchange_export(None, al) == lib.CDA_ERR_BAD_ARG and L.cda_b200_exchange_import(al, None) == lib.CDA_ERR_BAD_ARG
+    assert L.cda_b200_exchange_free(None) == lib.CDA_OK and L.cda_b200_exchange_close(None) == lib.CDA_OK
     assert L.cda_b200_prefill_debug(0, 0) == lib.CDA_OK
 
 
