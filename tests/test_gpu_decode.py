@@ -316,3 +316,58 @@ def test_decode_returns_lse():
         _, m, l = O.cda_partial_rotated(Qr, Ks, Vs, cb_K=case["cb_K"], cb_V=case["cb_V"], group=4)
         torch.testing.assert_close(lse[b].cpu(), (m + l.log())[0, :, 0], rtol=1e-4, atol=2e-3)
     assert bool((lse[1] == float("-inf")).all())
+
+
+def _exchange_call(d, pointers, counters, rank, world, wait_ms, ws, max_len):
+    from sub0_b200 import ops
+    out = torch.full_like(d["Q"], float("nan"))
+    ops.decode_exchange(d["Q"], d["cache"], d["block_table"], d["seq_lens"], out, cb_K=d["cb_K"], cb_V=d["cb_V"], block_size=16,
+                        peer_pointers=pointers, counters=counters, rank=rank, world=world, max_seq_len=max_len, wait_ms=wait_ms,
+                        workspace=ws)
+    torch.cuda.synchronize()
+    return out
+
+
+def test_exchange_inside_the_merge_kernel_one_rank():
+    """The exchange form of the sequence-sharded decode with a group of one: the rank sends its row to itself, waits for it
+    and merges it -- the result is the plain decode, over several calls (both parities of the exchange buffer)."""
+    from sub0_b200 import ops
+    case = Cs.paged_case([1000, 0, 333], H_kv=4, group=4, seed=81)
+    d = to_dev(case)
+    buf = torch.zeros(ops.decode_exchange_bytes(3, 16, 1) // 4, dtype=torch.float32, device=DEV)
+    pointers = torch.tensor([buf.data_ptr()], dtype=torch.int64, device=DEV)
+    counters = torch.zeros(2, dtype=torch.int64, device=DEV)
+    ws = ops.new_workspace(ops.decode_workspace_bytes(3, 16, 4, 1000), torch.device(DEV))
+    want = Cs.oracle_decode(case)
+    for call in range(3):
+        out = _exchange_call(d, pointers, counters, 0, 1, 100, ws, 1000)
+        assert_close(out.cpu(), want, f"exchange, call {call}", [1000, 0, 333])
+    assert ops.workspace_status(ws) == 0 and counters.tolist() == [3, 0]
+
+
+def test_exchange_wait_that_runs_out_is_reported_and_the_kernel_returns():
+    """A group of two in which the other rank never sends (its buffer is a zeroed allocation nobody writes): every row's
+    wait runs out after 5 ms, the kernel returns, bit 3 of the status word is up, the call is counted, and the output is
+    the decode over this rank's keys alone (the missing row is left out of the merge).  The row this rank sent has
+    arrived in the other buffer with the call's tag."""
+    from sub0_b200 import ops
+    case = Cs.paged_case([700, 90], H_kv=2, group=4, seed=82)
+    d = to_dev(case)
+    words = ops.decode_exchange_bytes(2, 8, 2) // 4
+    own = torch.zeros(words, dtype=torch.float32, device=DEV)
+    silent = torch.zeros(words, dtype=torch.float32, device=DEV)
+    pointers = torch.tensor([own.data_ptr(), silent.data_ptr()], dtype=torch.int64, device=DEV)
+    counters = torch.zeros(2, dtype=torch.int64, device=DEV)
+    ws = ops.new_workspace(ops.decode_workspace_bytes(2, 8, 2, 700), torch.device(DEV))
+    out = _exchange_call(d, pointers, counters, 0, 2, 5, ws, 700)
+    assert ops.workspace_status(ws) & 8
+    assert counters.tolist() == [1, 0]
+    assert_close(out.cpu(), Cs.oracle_decode(case), "exchange with a silent rank", [700, 90])
+    rows = silent.view(2, 2, 16, 132)                                   # [parity][sender][row][132 floats]
+    assert bool((rows[1, 0, :, 130].view(torch.int32) == 1).all())      # call 1 -> parity 1, sender 0, tag 1
+    assert bool((rows[0] == 0).all()) and bool((rows[1, 1] == 0).all())
+    # the context is intact: a plain decode right after it matches
+    out2 = torch.empty_like(d["Q"])
+    ops.decode(d["Q"], d["cache"], d["block_table"], d["seq_lens"], out2, cb_K=d["cb_K"], cb_V=d["cb_V"], block_size=16, max_seq_len=700)
+    torch.cuda.synchronize()
+    assert_close(out2.cpu(), Cs.oracle_decode(case), "decode after the silent-rank call", [700, 90])
