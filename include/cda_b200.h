@@ -196,6 +196,10 @@ int cda_b200_decode_static(const void* Q, const void* kv_cache, const int32_t* b
                            const float* cb_K, const float* cb_V, void* out, int B, int H_q, int H_kv, int block_size,
                            int block_table_stride, int max_seq_len, int64_t num_slots, int slot_bytes, int k_bits,
                            int v_bits, float scale, int num_splits, void* stream);
+/* Status word of the most recent cda_b200_decode_static call on the current device (each call clears it first; same
+ * bits as the caller-owned workspace: 0 block id out of range, 1 shared-memory window too small, 2 a copy wait ran out).
+ * Synchronises the device. */
+int cda_b200_decode_static_status(int* status);
 
 /* Slow one-warp-per-query-head decode without tensor cores or splitting; decodes K/V exactly as
  * Compressor.decode does (cb[idx]*norm rounded to fp16).  A device-side cross-check, same arguments

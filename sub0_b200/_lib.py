@@ -47,6 +47,7 @@ PROTOTYPES = {
     "cda_b200_decode_exchange": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _sz, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i64,
                                       _i, _i, _i, _f, _i, _p]),
     "cda_b200_decode_static": (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i64, _i, _i, _i, _f, _i, _p]),
+    "cda_b200_decode_static_status": (_i, [_p]),
     "cda_b200_decode_scalar": (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i64, _i, _i, _i, _f, _p]),
     "cda_b200_cache_to_dense_rotated": (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i64, _i, _i, _i, _p]),
     "cda_b200_prefill_varlen": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _i, _i, _i, _i, _i, _i, _i, _i64, _i, _i,

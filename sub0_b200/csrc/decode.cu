@@ -1566,3 +1566,16 @@ extern "C" int cda_b200_decode_static(const void* Q, const void* kv_cache, const
   const DecodeSink sink{0, static_cast<__half*>(out), nullptr, nullptr, nullptr, nullptr, 0, 0};
   return decode_run("decode_static", a, sink, scratch, kStaticScratchBytes, pl, st);
 }
+
+// Status word of the most recent cda_b200_decode_static call on the current device (the call clears it first): bit 0 a
+// block id was out of range, bit 1 the shared-memory window did not fit, bit 2 a wait for a cache copy ran out of time.
+// Synchronises the device.
+extern "C" int cda_b200_decode_static_status(int* status) {
+  if (!status) return fail(CDA_ERR_BAD_ARG, "decode_static_status: null pointer");
+  uint8_t* scratch = nullptr;
+  const int rc = static_scratch_address(&scratch);
+  if (rc != CDA_OK) return rc;
+  if (cudaDeviceSynchronize() != cudaSuccess || cudaMemcpy(status, scratch, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess)
+    return check_launch("decode_static_status");
+  return CDA_OK;
+}

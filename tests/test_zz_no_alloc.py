@@ -79,3 +79,21 @@ def test_static_scratch_refuses_what_does_not_fit():
     msg = _lib.last_error()
     assert "scratch" in msg and "cda_b200_decode" in msg
     torch.cuda.synchronize()
+
+
+def test_static_status_word_reports_a_bad_block_id():
+    """The built-in scratch keeps the status word of the last call: clear after a good call, bit 0 up after a call whose
+    block table holds an id outside the cache (block 0 is read instead; nothing faults)."""
+    import ctypes as C
+    from sub0_b200 import _lib
+    L = _lib.lib
+    case = Cs.paged_case([300, 40], H_kv=2, group=4, seed=903)
+    word = C.c_int(-1)
+    both_entry_points(case, 0)
+    assert L.cda_b200_decode_static_status(C.byref(word)) == 0 and word.value == 0
+    bad = dict(case)
+    bad["block_table"] = case["block_table"].clone()
+    bad["block_table"][0, 1] = 1 << 20
+    both_entry_points(bad, 0)
+    assert L.cda_b200_decode_static_status(C.byref(word)) == 0 and word.value & 1
+    assert L.cda_b200_decode_static_status(None) == _lib.CDA_ERR_BAD_ARG
