@@ -77,7 +77,8 @@ def decode_sequence_sharded(Q: Tensor, local_cache: Tensor, local_block_table: T
 class PeerExchange:
     """Exchange buffers of a sequence-sharded decode group: one buffer per rank, each mapped into every process of the
     node (CUDA IPC handles travel over the process group), so that the merge kernel can store its row straight into the
-    other GPUs' memory.  Collective: every rank of ``group`` constructs it with the same ``B`` and ``H_q``.  The
+    other GPUs' memory.  Collective: every rank of ``group`` constructs it with the same ``B`` (the largest batch of a
+    call; smaller batches use the front of the buffers, the same size on every rank) and ``H_q``.  The
     buffers live until :meth:`close` (collective as well); keep the object for the lifetime of the decode loop and of
     any CUDA graph captured over :meth:`decode`."""
 
@@ -129,8 +130,8 @@ class PeerExchange:
         """One decode step: split kernel over the local keys, then ONE kernel that merges, exchanges and merges again
         (see ``cda_b200_decode_exchange``).  Same precondition on ``Q`` as :func:`decode_sequence_sharded`."""
         from . import ops
-        if Q.shape[0] != self.B or Q.shape[1] != self.H_q:
-            raise ValueError("Q does not match the exchange buffers")
+        if Q.shape[0] > self.B or Q.shape[1] != self.H_q:
+            raise ValueError("Q does not match the exchange buffers (at most B sequences, exactly H_q heads)")
         ops.decode_exchange(Q, local_cache, local_block_table, local_seq_lens, output, cb_K=cb_K, cb_V=cb_V,
                             block_size=block_size, peer_pointers=self.pointers, counters=self.counters, rank=self.rank,
                             world=self.world, scale=scale, max_seq_len=local_max_seq_len, wait_ms=wait_ms,
@@ -152,7 +153,7 @@ def gather_heads(q_local: Tensor, H_kv: int, group: Optional[dist.ProcessGroup] 
 def decode_context_parallel(q_local: Tensor, local_cache: Tensor, local_block_table: Tensor, local_seq_lens: Tensor,
                             output_local: Tensor, *, cb_K: Tensor, cb_V: Tensor, block_size: int, local_max_seq_len: int,
                             scale: Optional[float] = None, group: Optional[dist.ProcessGroup] = None,
-                            workspace: Optional[Tensor] = None) -> None:
+                            workspace: Optional[Tensor] = None, exchange: Optional["PeerExchange"] = None) -> None:
     """Decode step of a context-parallel group that sits inside a tensor-parallel group: the ranks share the same KV
     heads, each holds its own slice of the query heads of those KV heads and its own part of every sequence's keys.
 
@@ -161,6 +162,8 @@ def decode_context_parallel(q_local: Tensor, local_cache: Tensor, local_block_ta
     2. partial (O, m, l) rows of those heads over the local keys;
     3. one all-gather of the packed partials, local log-sum-exp merge (cda/algorithm/attention.py:239-272);
     4. keep this rank's query heads.
+    With ``exchange`` (a :class:`PeerExchange` of the same group, built for ``H_kv * world * g_local`` heads) steps 2 and 3
+    are one call: the merge kernel exchanges the rows by peer stores instead of the all-gather.
     ``q_local`` / ``output_local``: (n, H_kv * g_local, 128) fp16."""
     from . import ops
     world, rank = dist.get_world_size(group), dist.get_rank(group)
@@ -170,8 +173,12 @@ def decode_context_parallel(q_local: Tensor, local_cache: Tensor, local_block_ta
     if g_local * H_kv != h_local or g_local * world > 8:
         raise NotImplementedError(f"context-parallel decode needs world * local GQA group <= 8 (got {world} x {g_local})")
     q_all = gather_heads(q_local, H_kv, group)
-    packed = ops.decode_partial(q_all, local_cache, local_block_table, local_seq_lens, cb_K=cb_K, cb_V=cb_V,
-                                block_size=block_size, scale=scale, max_seq_len=local_max_seq_len, workspace=workspace)
     out_all = torch.empty_like(q_all)
-    ops.merge_partials(gather_partials(packed, group), out_all)
+    if exchange is not None:
+        exchange.decode(q_all, local_cache, local_block_table, local_seq_lens, out_all, cb_K=cb_K, cb_V=cb_V,
+                        block_size=block_size, local_max_seq_len=local_max_seq_len, scale=scale, workspace=workspace)
+    else:
+        packed = ops.decode_partial(q_all, local_cache, local_block_table, local_seq_lens, cb_K=cb_K, cb_V=cb_V,
+                                    block_size=block_size, scale=scale, max_seq_len=local_max_seq_len, workspace=workspace)
+        ops.merge_partials(gather_partials(packed, group), out_all)
     output_local.copy_(out_all.view(n, H_kv, world, g_local, d)[:, :, rank].reshape(n, h_local, d))

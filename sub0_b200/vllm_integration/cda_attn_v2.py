@@ -19,6 +19,7 @@ The module imports without vLLM (stand-in base classes), which is how the CPU te
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import ClassVar, Optional
 
@@ -446,6 +447,25 @@ def _build_backend_classes():
             if dst is not out:
                 out.copy_(dst)
 
+        def _dcp_exchange(self, q, group):
+            """``CDA_V2_DCP_EXCHANGE=peer``: exchange the partial rows inside the merge kernel (peer stores over NVLink)
+            instead of the all-gather.  The buffers are built once, collectively, for ``CDA_V2_DCP_MAX_BATCH`` sequences
+            (256 by default); a larger batch takes the all-gather."""
+            import torch.distributed as dist
+
+            if os.environ.get("CDA_V2_DCP_EXCHANGE", "nccl") != "peer":
+                return None
+            cap = int(os.environ.get("CDA_V2_DCP_MAX_BATCH", "256"))
+            if q.shape[0] > cap:
+                return None
+            px = getattr(self, "_px", None)
+            if px is None:
+                from ..sharding import PeerExchange
+
+                heads_all = q.shape[1] * dist.get_world_size(group)
+                px = self._px = PeerExchange(cap, heads_all, q.device, group=group)
+            return px
+
         def _forward_decode_dcp(self, q, cache, out, md) -> None:
             """Decode with the keys of every sequence sharded over the DCP group.  The group lies inside the
             tensor-parallel group: its ranks share this rank's KV heads but hold different query heads, so the queries are
@@ -465,7 +485,8 @@ def _build_backend_classes():
                 group = None                                 # plain torch.distributed default group (tests)
             dst = out if out.is_contiguous() else torch.empty_like(q)
             decode_context_parallel(q.contiguous(), flat, md.block_table, md.seq_lens, dst, cb_K=cb_K, cb_V=cb_V,
-                                    block_size=bs, local_max_seq_len=int(md.max_seq_len), scale=self.scale, group=group)
+                                    block_size=bs, local_max_seq_len=int(md.max_seq_len), scale=self.scale, group=group,
+                                    exchange=self._dcp_exchange(q, group))
             if dst is not out:
                 out.copy_(dst)
 

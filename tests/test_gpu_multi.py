@@ -105,6 +105,17 @@ def _rank_main(rank, world, port, q):
         impl.forward(None, q_local.to(dev), None, None, kv, md, output=out2)
         torch.cuda.synchronize()
         ok2, ratio2, _ = Cs.close(out2.view(2, 8, 128).cpu(), want2)
+        # the same backend call with the exchange inside the merge kernel (opt-in switch), twice
+        os.environ["CDA_V2_DCP_EXCHANGE"] = "peer"
+        os.environ["CDA_V2_DCP_MAX_BATCH"] = "4"
+        for _ in range(2):
+            out3 = torch.full((2, 8 * 128), float("nan"), dtype=torch.float16, device=dev)
+            impl.forward(None, q_local.to(dev), None, None, kv, md, output=out3)
+            torch.cuda.synchronize()
+            ok3, ratio3, _ = Cs.close(out3.view(2, 8, 128).cpu(), want2)
+            ok2, ratio2 = ok2 and ok3, max(ratio2, ratio3)
+        ok2 = ok2 and ops.workspace_status() == 0
+        impl._px.close()
         q.put((rank, same, ok and ok2, max(ratio, ratio2)))
     except Exception as exc:
         q.put((rank, False, False, repr(exc)))
