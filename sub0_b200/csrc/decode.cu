@@ -1082,7 +1082,7 @@ static int chunks_touched(int64_t lo, int64_t len, int64_t c) { return static_ca
 // chunk never goes below 128 tokens.  num_splits > 0 instead cuts every sequence into that many equal key ranges of its
 // own (chunks then never straddle two sequences).
 static Plan make_plan(int B, int H_kv, int max_seq_len, int num_splits, int sms) {
-  constexpr int kFloorGroups = 8, kFixedTokens = 360, kMaxParts = 4096, kMaxCtasPerSm = 8;
+  constexpr int kFloorGroups = 8, kFixedTokens = 360, kMaxParts = 4096, kMaxCtasPerSm = 8, kSwitchGroups = 116;
   Plan pl;
   pl.warps = kSplitWarps; pl.depth = kSplitStages;
   pl.heads_per_cta = pick_heads_per_cta(H_kv);
@@ -1124,6 +1124,15 @@ static Plan make_plan(int B, int H_kv, int max_seq_len, int num_splits, int sms)
     int64_t c = (positions + target - 1) / target;
     if (c < kFloorGroups) c = kFloorGroups;
     consider(c, ng, ng % c != 0);
+    // (c) the same with a stretch of empty positions behind every sequence, as long as a change of sequence costs a CTA
+    // (measured: 6.5 us, the streaming time of ~116 groups of one head): a chunk that holds the end of one sequence
+    // and the start of the next then carries that much less work, and all CTAs finish together
+    if (ng % c != 0) {
+      const int gap = kSwitchGroups / pl.heads_per_cta > 0 ? kSwitchGroups / pl.heads_per_cta : 1;
+      int64_t cg = (batch * (ng + gap) + target - 1) / target;
+      if (cg < kFloorGroups) cg = kFloorGroups;
+      if (cg > gap) consider(cg, ng + gap, false);
+    }
     if (c == kFloorGroups) break;
   }
   pl.chunk_groups = best_c;

@@ -133,7 +133,8 @@ def test_split_planning_properties(lib):
     # 886 groups, and a sequence of 4096 groups touches at most 6 of them
     assert L.cda_b200_decode_plan_splits(32, 8, 65536, -1) == 6
     assert L.cda_b200_decode_plan_splits(4, 8, 65536, -1) == 37       # 148 = 4 x 37: equal ranges inside each sequence
-    assert L.cda_b200_decode_plan_splits(32, 8, 4096, -1) == 4        # 128 ranges of 64 groups beat 148 straddling chunks
+    assert L.cda_b200_decode_plan_splits(32, 8, 4096, -1) == 6        # 148 chunks over a line with a gap behind every sequence
+    assert L.cda_b200_decode_plan_splits(37, 8, 4096, -1) == 4        # 37 x 4 = 148: equal ranges inside each sequence
     assert L.cda_b200_decode_plan_splits(1, 8, 4096, -1) == 32        # never below 128 tokens per chunk
     assert L.cda_b200_decode_plan_splits(0, 8, 16, -1) == lib.CDA_ERR_BAD_ARG
 
