@@ -90,7 +90,11 @@ int cda_b200_hadamard128(const void* x, void* y, int64_t rows, float scale, void
 int cda_b200_decode_plan_splits(int B, int H_kv, int max_seq_len, int device);
 
 /* Bytes of workspace the decode entry points need for these sizes (num_splits == 0: the planned
- * count).  The reference kernel allocates this scratch itself (wrappers.py:97-99); here the caller does. */
+ * count).  The reference kernel allocates this scratch itself (wrappers.py:97-99); here the caller does.
+ * The first 256 bytes are a status block that the caller zeroes once; its first int collects, over the calls that use
+ * the workspace:  bit 0 (1) a block-table entry was outside the cache and block 0 was read instead;  bit 1 (2) the
+ * kernel's shared-memory window did not fit (empty partials were written);  bit 2 (4) a bounded wait for a cache copy
+ * ran out of time;  bit 3 (8) cda_b200_decode_exchange waited in vain for another rank's row. */
 size_t cda_b200_decode_workspace_bytes(int B, int H_q, int H_kv, int max_seq_len, int num_splits, int device);
 
 /* Single-query GQA decode over the paged compressed cache: out[b,h,:] = softmax(scale * Hq.K^T) V H^T
