@@ -7,12 +7,6 @@
 // written per (token, KV head).
 #include "common.cuh"
 
-#ifndef CDA_ENC_SCALAR_CELL
-#define CDA_ENC_SCALAR_CELL 0
-#endif
-#ifndef CDA_ENC_SCALAR_BFLY
-#define CDA_ENC_SCALAR_BFLY 0
-#endif
 namespace cda {
 
 // Index selection of Compressor.quantize_unit (cda/algorithm/compression.py:298-313): upper = number of levels
@@ -198,19 +192,11 @@ __device__ __forceinline__ void rotate16(const RowFrags& a, const RotFrag& f, fl
 #pragma unroll
         for (int t = 0; t < 2; ++t)
 #pragma unroll
-#if CDA_ENC_SCALAR_BFLY
-          for (int i = 0; i < 4; ++i) {
-            const float a = y[g][t][i], b = y[g | bit][t][i];
-            y[g][t][i] = a + b;
-            y[g | bit][t][i] = a - b;
-          }
-#else
           for (int i = 0; i < 4; i += 2) {                 // two coordinates per instruction
             const uint64_t a = f2_pack(y[g][t][i], y[g][t][i + 1]), b = f2_pack(y[g | bit][t][i], y[g | bit][t][i + 1]);
             f2_unpack(f2_add(a, b), y[g][t][i], y[g][t][i + 1]);
             f2_unpack(f2_sub(a, b), y[g | bit][t][i], y[g | bit][t][i + 1]);
           }
-#endif
       }
 }
 // Scales the accumulators by 1/sqrt(128) and rounds them to fp16, as the rotation's output is: hp[g][t][h] = coordinates
@@ -291,12 +277,7 @@ __device__ __forceinline__ float2 quantize_pair(const uint32_t (&hp)[8][2][2], c
             const uint64_t rem = f2_fma(q0, f2_pack(-norm[h], -norm[h]), vv);
             const uint64_t uu = f2_fma(rem, rr, q0);
             f2_unpack(uu, u2[0], u2[1]);
-#if CDA_ENC_SCALAR_CELL
-            cf2[0] = __fmaf_rn(u2[0], 64.0f, kCellMagic);
-            cf2[1] = __fmaf_rn(u2[1], 64.0f, kCellMagic);
-#else
             f2_unpack(f2_fma(uu, f2_pack(64.0f, 64.0f), f2_pack(kCellMagic, kCellMagic)), cf2[0], cf2[1]);
-#endif
           }
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
