@@ -778,10 +778,10 @@ def run_prompt_reference(args):
 
 
 def run_prompt_workload(args):
-    print(json.dumps(prompt_workload_line(args.workload, args.steps, args.warmup, args.no_cpu_baseline)))
+    print(json.dumps(prompt_workload_line(args.workload, args.steps, args.warmup, args.no_cpu_baseline, group=args.group)))
 
 
-def prompt_workload_line(workload, steps, warmup, no_cpu_baseline):
+def prompt_workload_line(workload, steps, warmup, no_cpu_baseline, group=4):
     """`--workload encode` / `--workload prefill`: one GPU, k4v4, 8 prompts with seeded lengths in [512, 8192].
 
     encode : K, V (T, 8, 128) fp16 -> 144-byte slots scattered by a shuffled slot mapping; metric GB/s over the
@@ -795,7 +795,7 @@ def prompt_workload_line(workload, steps, warmup, no_cpu_baseline):
     from sub0_b200.kernels_cuda.wrappers import paged_encode_fused_cuda
     from sub0_b200 import ops
 
-    GROUP = 4
+    GROUP = group                                     # query heads per KV head (8 KV heads): 4, or 8 with --group 8
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
     lens = prompt_lengths()
