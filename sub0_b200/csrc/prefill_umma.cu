@@ -23,6 +23,7 @@
 // The roles hand tiles over through mbarriers; every wait is bounded (umma.cuh) and a wait that gives up sets a fault
 // flag and ends the CTA cleanly (TMEM is released).
 #include "common.cuh"
+#include <type_traits>
 #include "umma.cuh"
 #include "prefill_umma.cuh"
 
@@ -165,10 +166,10 @@ __device__ __forceinline__ void expand_quad(uint32_t tile, uint32_t lut_lane, ui
     for (int wi = 0; wi < 4; ++wi) {
       const uint32_t x = ws[wi];
       uint32_t v[4];
-      v[0] = lds32(lut_lane + (x & 0xffu) * stride);
-      v[1] = lds32(lut_lane + ((x >> 8) & 0xffu) * stride);
-      v[2] = lds32(lut_lane + ((x >> 16) & 0xffu) * stride);
-      v[3] = lds32(lut_lane + (x >> 24) * stride);
+      v[0] = lds32(lut_lane + __byte_perm(x, 0u, 0x4440) * stride);      // one byte moved to the bottom, then shift-and-add
+      v[1] = lds32(lut_lane + __byte_perm(x, 0u, 0x4441) * stride);
+      v[2] = lds32(lut_lane + __byte_perm(x, 0u, 0x4442) * stride);
+      v[3] = lds32(lut_lane + __byte_perm(x, 0u, 0x4443) * stride);
       if (SCALED) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) v[i] = hscale2(v[i], scale_hi, scale_lo);
@@ -182,7 +183,7 @@ __device__ __forceinline__ void expand_quad(uint32_t tile, uint32_t lut_lane, ui
       const uint32_t x = ws[wi];
 #pragma unroll
       for (int hb = 0; hb < 2; ++hb) {                     // two code bytes = 8 coordinates = one chunk
-        const uint32_t b0 = (x >> (16 * hb)) & 0xffu, b1 = (x >> (16 * hb + 8)) & 0xffu;
+        const uint32_t b0 = __byte_perm(x, 0u, 0x4440 + 2 * hb), b1 = __byte_perm(x, 0u, 0x4441 + 2 * hb);
         uint2 lo = lds64(lut_lane + b0 * stride), hi = lds64(lut_lane + b1 * stride);
         if (SCALED) {
           lo.x = hscale2(lo.x, scale_hi, scale_lo); lo.y = hscale2(lo.y, scale_hi, scale_lo);
@@ -720,6 +721,10 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
         vblk[it] = block_id(nl, j + 1);
       }
     };
+    // The table stride (bytes between the rows of two code bytes) is 64 with one shared table and 32 with two; the tile
+    // loop is instantiated for either, so that every gather address is "byte << 6 (or 5), plus base" with constant shifts.
+    auto produce = [&](auto stride_tag) {
+    constexpr uint32_t kStride = decltype(stride_tag)::value;
     auto expand_k = [&](int j, const KRegs& r) {
       const uint32_t tile = base + kOffK + (j & 1) * kTileBytes;
       float* kn = reinterpret_cast<float*>(sm + kOffKn) + (j & 3) * kKeys;
@@ -727,7 +732,7 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
       for (int it = 0; it < kItK; ++it) {
         const int x = pt + kProducerThreads * it, nl = x / KB, quad = x % KB;
         if (quad == 0) kn[nl] = r.n[it] * kscale;
-        expand_quad<KB, false>(tile, lutk_lane, lut_stride, r.w[it], nl, quad, 0u, 0u);
+        expand_quad<KB, false>(tile, lutk_lane, kStride, r.w[it], nl, quad, 0u, 0u);
       }
       fence_async_smem();
       __syncwarp();
@@ -743,7 +748,7 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
         // the value norm goes into the tile (fp16 products, norm as two fp16 terms), so the probabilities need no per-key factor
         const float n_hi = round_to_half(r.n[it]);
         const float n_lo = r.n[it] - n_hi;
-        expand_quad<VB, true>(base + kOffV + (j & 1) * kTileBytes, lutv_lane, lut_stride, r.w[it], nl, quad, pack_half2(n_hi, n_hi),
+        expand_quad<VB, true>(base + kOffV + (j & 1) * kTileBytes, lutv_lane, kStride, r.w[it], nl, quad, pack_half2(n_hi, n_hi),
                               pack_half2(n_lo, n_lo));
       }
       fence_async_smem();
@@ -765,6 +770,9 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
       expand_v(i, vr);
       load_v(i + 1, vr);
     }
+    };
+    if (same_cb) produce(std::integral_constant<uint32_t, 64u>{});
+    else produce(std::integral_constant<uint32_t, 32u>{});
     if (bad_block) atomicOr(&g_prefill_status, 1);
    }
   } else {
