@@ -146,12 +146,14 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
 }
 
 // ---- tensor-core rotation of 16 rows at a time --------------------------------------------------------------------------
-// The Sylvester matrix factors over the bits of the coordinate index: H128[i][j] = prod_b (-1)^(i_b j_b).  Bits {4,3,1,0}
-// ("lo", 16 values) are contracted by mma.m16n8k16 against a +-1 fp16 matrix (products exact, fp32 accumulation), bits
-// {6,5,2} ("hi", 8 values) by three in-register butterfly stages on the accumulators.  With that split lane c of a quad
-// reads, for each of the four 64-byte quarters of a row, the 16 contiguous bytes 8c .. 8c+7 (bits 4,3 = c; bit 2 picks the
-// half of the 16 bytes; bits 1,0 the fp16 inside the register pair), and ends up owning the same eight coordinates of the
-// rotated row: what it packs is one contiguous 32-bit (4-bit codes) or 16-bit (2-bit codes) piece of the slot.
+// The Sylvester matrix factors over the bits of the coordinate index: H128[i][j] = prod_b (-1)^(i_b j_b).  Four bits
+// (16 values) are contracted by mma.m16n8k16 against a +-1 fp16 matrix (products exact, fp32 accumulation), the other
+// three by in-register butterfly stages on the accumulators.  RotFrag is that 16 x 16 matrix as B fragments; it does
+// not depend on WHICH four bits the caller maps to the 16 contraction slots (k slot 2c + e, and 8 + 2c + e for the
+// fourth bit): the paged encoder contracts bits {4,3,2,0} (its A operand is one 16-byte load of one row), the staged
+// rotation of the prefill kernel bits {4,3,1,0} (two rows per lane).  Either way lane c of a quad reads, for each of the
+// four 64-byte quarters of a row, the 16 contiguous bytes 8c .. 8c+7 and ends up owning the same eight coordinates of
+// the rotated row: what it packs is one contiguous 32-bit (4-bit codes) or 16-bit (2-bit codes) piece of the slot.
 struct RotFrag {   // B operand: H16 restricted to this lane's contraction slots, for the two 8-column halves
   uint32_t b0[2], b1[2];
 };

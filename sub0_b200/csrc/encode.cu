@@ -110,7 +110,7 @@ __device__ __forceinline__ bool build_cell(const float* T, CellEntry* cells, int
   cells[t] = e;
   return crowded;
 }
-// Where the code of this lane's coordinate p = 4 g0 + 2 t + e sits in the piece of the index field that the lane writes
+// Where the code of the p-th (p = 0..7, in coordinate order) of a lane's eight coordinates of a quarter row sits in the piece of the index field the lane writes
 // (32 bits of 4-bit codes, 16 bits of 2-bit codes): the first code of a byte on top.
 template <int BITS>
 __host__ __device__ constexpr int code_shift(int p) {
@@ -174,44 +174,62 @@ __device__ __forceinline__ void load_row_frags(const __half* __restrict__ x, int
     a.hi[j] = __ldg(reinterpret_cast<const uint4*>(x + row_hi * kHeadDim + 32 * j + 8 * c));
   }
 }
-// y[g][t][i]: rotated (unscaled) coordinates 64 g2 + 32 g1 + 8c + 4 g0 + 2t + (i & 1) of the low row (i < 2) and the high
-// row (i >= 2) of the fragments, g = (g2 g1 g0).
-__device__ __forceinline__ void rotate16(const RowFrags& a, const RotFrag& f, float (&y)[8][2][4]) {
+// The 16 rows of an MMA are fed with 8 tensor rows: MMA row r takes the coordinates 8c + {0,1,4,5} of a quarter of tensor
+// row r, MMA row r + 8 the coordinates 8c + {2,3,6,7} of the SAME tensor row -- so the A operand of a product is exactly the
+// four registers of one 16-byte load (x, y, z, w), in order, and needs no register moves.  The product contracts the bits
+// {4,3,2,0} of the coordinate index; bit 1 (which of the two MMA rows) is one add/sub inside the accumulator quad, bits
+// 6 and 5 (the quarter) two butterfly stages across quads.
+// y[h][j][t][i]: rotated (unscaled) coordinate 32 j + 8c + 4t + i of row h (0: the lane's low row, 1: its high row).
+__device__ __forceinline__ void rotate16(const RowFrags& a, const RotFrag& f, float (&y)[2][4][2][4]) {
 #pragma unroll
-  for (int j = 0; j < 4; ++j)
+  for (int h = 0; h < 2; ++h)
 #pragma unroll
-    for (int t = 0; t < 2; ++t) {
-      mma_16816_zero(y[2 * j][t], a.lo[j].x, a.hi[j].x, a.lo[j].y, a.hi[j].y, f.b0[t], f.b1[t]);
-      mma_16816_zero(y[2 * j + 1][t], a.lo[j].z, a.hi[j].z, a.lo[j].w, a.hi[j].w, f.b0[t], f.b1[t]);
+    for (int j = 0; j < 4; ++j) {
+      const uint4& q = h ? a.hi[j] : a.lo[j];
+#pragma unroll
+      for (int t = 0; t < 2; ++t) mma_16816_zero(y[h][j][t], q.x, q.y, q.z, q.w, f.b0[t], f.b1[t]);
     }
 #pragma unroll
-  for (int bit = 1; bit < 8; bit <<= 1)
+  for (int h = 0; h < 2; ++h) {
 #pragma unroll
-    for (int g = 0; g < 8; ++g)
-      if (!(g & bit)) {
+    for (int j = 0; j < 4; ++j)
 #pragma unroll
-        for (int t = 0; t < 2; ++t)
-#pragma unroll
-          for (int i = 0; i < 4; i += 2) {                 // two coordinates per instruction
-            const uint64_t a = f2_pack(y[g][t][i], y[g][t][i + 1]), b = f2_pack(y[g | bit][t][i], y[g | bit][t][i + 1]);
-            f2_unpack(f2_add(a, b), y[g][t][i], y[g][t][i + 1]);
-            f2_unpack(f2_sub(a, b), y[g | bit][t][i], y[g | bit][t][i + 1]);
-          }
+      for (int t = 0; t < 2; ++t) {                         // bit 1: the quad's halves came from inputs with bit 1 clear / set
+        const uint64_t lo = f2_pack(y[h][j][t][0], y[h][j][t][1]), hi = f2_pack(y[h][j][t][2], y[h][j][t][3]);
+        f2_unpack(f2_add(lo, hi), y[h][j][t][0], y[h][j][t][1]);
+        f2_unpack(f2_sub(lo, hi), y[h][j][t][2], y[h][j][t][3]);
       }
+#pragma unroll
+    for (int bit = 1; bit < 4; bit <<= 1)                    // bits 5 and 6: across the quarters
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (!(j & bit)) {
+#pragma unroll
+          for (int t = 0; t < 2; ++t)
+#pragma unroll
+            for (int i = 0; i < 4; i += 2) {
+              const uint64_t p = f2_pack(y[h][j][t][i], y[h][j][t][i + 1]), q = f2_pack(y[h][j | bit][t][i], y[h][j | bit][t][i + 1]);
+              f2_unpack(f2_add(p, q), y[h][j][t][i], y[h][j][t][i + 1]);
+              f2_unpack(f2_sub(p, q), y[h][j | bit][t][i], y[h][j | bit][t][i + 1]);
+            }
+        }
+  }
 }
-// Scales the accumulators by 1/sqrt(128) and rounds them to fp16, as the rotation's output is: hp[g][t][h] = coordinates
-// (e = 0, 1) of row h as an fp16 pair.  Half the registers of y, so that the next fragments can be in flight meanwhile.
-__device__ __forceinline__ void scale_and_pack(const float (&y)[8][2][4], uint32_t (&hp)[8][2][2]) {
+// Scales the accumulators by 1/sqrt(128) and rounds them to fp16, as the rotation's output is: hp[h][j][t][k] = coordinates
+// 32 j + 8c + 4t + 2k + {0, 1} of row h as an fp16 pair.  Half the registers of y, so that the next fragments can be in flight.
+__device__ __forceinline__ void scale_and_pack(const float (&y)[2][4][2][4], uint32_t (&hp)[2][4][2][2]) {
 #pragma unroll
-  for (int g = 0; g < 8; ++g)
+  for (int h = 0; h < 2; ++h)
 #pragma unroll
-    for (int t = 0; t < 2; ++t)
+    for (int j = 0; j < 4; ++j)
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        float s0, s1;
-        f2_unpack(f2_mul(f2_pack(y[g][t][2 * h], y[g][t][2 * h + 1]), f2_pack(kRsqrtD, kRsqrtD)), s0, s1);
-        hp[g][t][h] = pack_half2(s0, s1);
-      }
+      for (int t = 0; t < 2; ++t)
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          float s0, s1;
+          f2_unpack(f2_mul(f2_pack(y[h][j][t][2 * k], y[h][j][t][2 * k + 1]), f2_pack(kRsqrtD, kRsqrtD)), s0, s1);
+          hp[h][j][t][k] = pack_half2(s0, s1);
+        }
 }
 // Quantises the two rows held in hp and writes this lane's pieces of their index fields.  Returns the two norms (the same in the four lanes of a quad).
 //
@@ -221,22 +239,24 @@ __device__ __forceinline__ void scale_and_pack(const float (&y)[8][2][4], uint32
 // a zero loses its sign (-0 comes out as +0), which no comparison below can see.
 // FAST: take the indices from the cell table; otherwise from the four-step search.
 template <int BITS, bool FAST>
-__device__ __forceinline__ float2 quantize_pair(const uint32_t (&hp)[8][2][2], const float* T, const CellEntry* cells,
+__device__ __forceinline__ float2 quantize_pair(const uint32_t (&hp)[2][4][2][2], const float* T, const CellEntry* cells,
                                                 uint8_t* dst_lo, uint8_t* dst_hi, int c, bool ok_lo, bool ok_hi) {
   constexpr int L = BITS == 4 ? 16 : 4;
   float ss[2];
   {
     uint64_t acc[2] = {f2_pack(0.f, 0.f), f2_pack(0.f, 0.f)};      // even and odd coordinates summed side by side
 #pragma unroll
-    for (int g = 0; g < 8; ++g)
+    for (int h = 0; h < 2; ++h)
 #pragma unroll
-      for (int t = 0; t < 2; ++t)
+      for (int j = 0; j < 4; ++j)
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const float2 v = __half22float2(*reinterpret_cast<const __half2*>(&hp[g][t][h]));
-          const uint64_t vv = f2_pack(v.x, v.y);
-          acc[h] = f2_fma(vv, vv, acc[h]);
-        }
+        for (int t = 0; t < 2; ++t)
+#pragma unroll
+          for (int k = 0; k < 2; ++k) {
+            const float2 v = __half22float2(*reinterpret_cast<const __half2*>(&hp[h][j][t][k]));
+            const uint64_t vv = f2_pack(v.x, v.y);
+            acc[h] = f2_fma(vv, vv, acc[h]);
+          }
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       float even, odd;
@@ -260,13 +280,13 @@ __device__ __forceinline__ float2 quantize_pair(const uint32_t (&hp)[8][2][2], c
     uint8_t* dst = h ? dst_hi : dst_lo;
     const bool ok = h ? ok_hi : ok_lo;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) {                                    // quarter of the row: g2 g1 = w
+    for (int w = 0; w < 4; ++w) {                                    // quarter of the row
       uint32_t word = 0;
 #pragma unroll
-      for (int g0 = 0; g0 < 2; ++g0)
+      for (int t = 0; t < 2; ++t)
 #pragma unroll
-        for (int t = 0; t < 2; ++t) {
-          const float2 v2 = __half22float2(*reinterpret_cast<const __half2*>(&hp[2 * w + g0][t][h]));
+        for (int k = 0; k < 2; ++k) {                                // coordinates 8c + 4t + 2k + {0, 1} of the quarter
+          const float2 v2 = __half22float2(*reinterpret_cast<const __half2*>(&hp[h][w][t][k]));
           uint32_t ix[2];                                            // the indices of coordinates e = 0, 1
           // the division step and the cell index on both coordinates at once (each lane rounded as the scalar form;
           // q * (-norm) is the same product as (-q) * norm)
@@ -285,11 +305,11 @@ __device__ __forceinline__ float2 quantize_pair(const uint32_t (&hp)[8][2][2], c
             const uint32_t cell_off = __float_as_uint(cf2[e]) & 0xff8u;
             if (FAST) {                                              // table word: the count of lower cells, already in place
               constexpr int kPosStride = (kCells + 1) * static_cast<int>(sizeof(CellEntry));
-              const int pos = 4 * g0 + 2 * t + e;
+              const int pos = 4 * t + 2 * k + e;
               const uint2 ce = *reinterpret_cast<const uint2*>(reinterpret_cast<const char*>(cells) + pos * kPosStride + cell_off);
               ix[e] = ce.y + (u > __uint_as_float(ce.x) ? (1u << code_shift<BITS>(pos)) : 0u);
             } else {
-              ix[e] = (count_thresholds_x4<L>(u, T) >> 2) << code_shift<BITS>(4 * g0 + 2 * t + e);
+              ix[e] = (count_thresholds_x4<L>(u, T) >> 2) << code_shift<BITS>(4 * t + 2 * k + e);
             }
           }
           word += ix[0] + ix[1];
@@ -344,8 +364,8 @@ __device__ __forceinline__ void encode_tiles(const __half* __restrict__ K, const
     if (first) { load_row_frags(K, row[0], row[1], c, fr); first = false; }
     float2 nk, nv;
     {
-      float y[8][2][4];
-      uint32_t hp[8][2][2];
+      float y[2][4][2][4];
+      uint32_t hp[2][4][2][2];
       rotate16(fr, frag, y);
       load_row_frags(V, row[0], row[1], c, fr);
       scale_and_pack(y, hp);
