@@ -106,3 +106,29 @@ def test_fused_compressed_kv_attention_flat_and_paged():
     with pytest.raises(NotImplementedError):
         flash_attn_varlen_compressed_kv_fused_func(q, k_idx, k_norm, v_idx, v_norm, cb.to(DEV), cb.to(DEV), max(lens), cu,
                                                    max(lens), cu, causal=False)
+
+
+def test_operator_namespace_calls_match_the_functions():
+    """torch.ops._cda_vllm_fa2_fork_C.* with the positional argument lists of the reference's wrappers
+    (interface.py:154-161, 433-460) give what the package's functions give."""
+    import sub0_b200.kernels_vllm_fa2_fork._ops  # noqa: F401  (registers the namespace)
+    from sub0_b200.kernels_vllm_fa2_fork.interface import dequantize_compressed_kv, flash_attn_varlen_compressed_kv_fused_func
+    ns = torch.ops._cda_vllm_fa2_fork_C
+    gen = torch.Generator().manual_seed(13)
+    cb = Cs.cb_for(4)
+    n, H_kv, group = 90, 2, 4
+    ke, ve = O.encode(Cs.rows(gen, 1, H_kv, n, outliers=True), cb), O.encode(Cs.rows(gen, 1, H_kv, n), cb)
+    k_idx, v_idx = ke.idx[0].transpose(0, 1).contiguous().to(DEV), ve.idx[0].transpose(0, 1).contiguous().to(DEV)
+    k_norm, v_norm = ke.norm[0].transpose(0, 1).contiguous().to(DEV), ve.norm[0].transpose(0, 1).contiguous().to(DEV)
+    cbd = cb.to(DEV)
+    kd, vd = ns.dequantize_compressed_kv(k_idx, k_norm, v_idx, v_norm, cbd, cbd)
+    kd2, vd2 = dequantize_compressed_kv(k_idx, k_norm, v_idx, v_norm, cbd, cbd)
+    assert torch.equal(kd, kd2) and torch.equal(vd, vd2)
+    q = Cs.rows(gen, 1, H_kv * group, n)[0].transpose(0, 1).contiguous().to(DEV)
+    cu = torch.tensor([0, n], dtype=torch.int32, device=DEV)
+    out, lse = ns.varlen_fwd_compressed_kv_fused(q, k_idx, k_norm, v_idx, v_norm, cbd, cbd, None, cu, cu, None, None, None, n, n,
+                                                 0.0, 128 ** -0.5, False, True, -1, -1, 0.0, False, 0, False, None)
+    want = flash_attn_varlen_compressed_kv_fused_func(q, k_idx, k_norm, v_idx, v_norm, cbd, cbd, n, cu, n, cu,
+                                                      softmax_scale=128 ** -0.5, causal=True)
+    torch.cuda.synchronize()
+    assert torch.equal(out, want) and lse.numel() == 0
