@@ -1149,9 +1149,13 @@ static Plan make_plan(int B, int H_kv, int max_seq_len, int num_splits, int sms)
   return pl;
 }
 
+// Workspace layout: 256-byte status block, the (m, l) pairs of every partial row, then the O rows.  The O rows are
+// written and read 16 bytes at a time, so the (m, l) area is padded to a multiple of 16 (an odd number of rows --
+// e.g. 13 sequences x 3 query heads x an odd number of parts -- would otherwise leave them 8 bytes off).
+static size_t ws_ml_bytes(size_t rows) { return (rows * 2 * sizeof(float) + 15) & ~size_t(15); }
 static size_t ws_bytes(const Plan& pl, int B, int H_q) {
   const size_t rows = static_cast<size_t>(pl.parts) * B * H_q;
-  return 256 + rows * 2 * sizeof(float) + rows * kHeadDim * sizeof(float);
+  return 256 + ws_ml_bytes(rows) + rows * kHeadDim * sizeof(float);
 }
 
 struct DecodeCommon {
@@ -1271,7 +1275,7 @@ static int run_split(const char* who, const DecodeCommon& a, void* workspace, si
   p.block_table = a.bt; p.seq_lens = a.sl; p.cb_k = a.cbk; p.cb_v = a.cbv;
   p.status = reinterpret_cast<int*>(ws);
   p.part_ml = reinterpret_cast<float*>(ws + 256);
-  p.part_o = reinterpret_cast<float*>(ws + 256 + rows * 2 * sizeof(float));
+  p.part_o = reinterpret_cast<float*>(ws + 256 + ws_ml_bytes(rows));
   p.B = a.B; p.H_q = a.H_q; p.H_kv = a.H_kv; p.group = a.H_q / a.H_kv;
   p.heads_per_cta = pl.heads_per_cta;
   p.block_size = a.block_size; p.bt_stride = a.bt_stride;

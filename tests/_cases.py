@@ -78,6 +78,14 @@ RTOL, ATOL = 2e-3, 1e-3          # the tolerance stated for this path: |got - wa
 STATS = []                         # one record per comparison of this session (written out by conftest on request)
 
 
+def cosine(g: torch.Tensor, w: torch.Tensor) -> float:
+    """Cosine of two tensors in float64 (torch's fp32 ``cosine_similarity`` drifts by 1e-4 and more over millions of
+    elements, in either direction)."""
+    a, b = g.double().flatten(), w.double().flatten()
+    den = float(a.norm() * b.norm())
+    return float(a @ b) / den if den > 0 else (1.0 if float(a.norm()) == float(b.norm()) else 0.0)
+
+
 def violations(got: torch.Tensor, want: torch.Tensor, rtol=RTOL, atol=ATOL):
     """(number of elements outside |got - want| <= atol + rtol |want|, worst |err| / bound, number of elements)."""
     g, w = got.float().cpu(), want.float().cpu()
@@ -91,7 +99,7 @@ def strict(got: torch.Tensor, want: torch.Tensor, what: str = ""):
     """The stated tolerance, element-wise, no exceptions: returns (ok, count of violating elements, worst ratio, cosine)."""
     g, w = got.float().cpu(), want.float().cpu()
     bad, worst, n = violations(g, w)
-    cos = float(torch.nn.functional.cosine_similarity(g.flatten(), w.flatten(), dim=0)) if n else 1.0
+    cos = cosine(g, w) if n else 1.0
     STATS.append({"what": what, "form": "strict", "elements": n, "violations": bad, "worst_ratio": worst, "cosine": cos})
     return bad == 0, bad, worst, cos
 
@@ -132,7 +140,7 @@ def close(got: torch.Tensor, want: torch.Tensor, rtol=RTOL, atol=ATOL, strict_ro
         mask = mask | (torch.ones_like(mask) if strict_rows is True else strict_rows)
     if bool(mask.any()):
         ratio = max(ratio, float(elem[mask].max()))                          # condition 3
-    cos = float(torch.nn.functional.cosine_similarity(g.flatten(), w.flatten(), dim=0))
+    cos = cosine(g, w)
     STATS.append({"what": what, "form": "row-max", "elements": g.numel(), "violations": n_bad,
                   "worst_ratio": float(elem.max()), "row_ratio": ratio, "cosine": cos})
     return ratio <= 1.0, ratio, cos

@@ -298,6 +298,17 @@ def test_decode_chunks_straddle_sequences():
         assert_close(run_decode(case, num_splits=splits), want, f"ragged batch, {splits} ranges per sequence", lens)
 
 
+def test_decode_odd_number_of_partial_rows():
+    """13 sequences x 3 query heads (one per KV head): the number of partial rows is odd for an odd number of parts, and
+    the O rows of the workspace must still sit on 16-byte boundaries (they are stored and merged 16 bytes at a time)."""
+    lens = [687, 291, 512, 4839, 36, 414, 178, 691, 1408, 521, 168, 403, 31]
+    for kb, vb, bs in [(4, 2, 128), (4, 4, 16)]:
+        case = Cs.paged_case(lens, H_kv=3, group=1, k_bits=kb, v_bits=vb, block_size=bs, seed=1007857332)
+        want = Cs.oracle_decode(case)
+        for splits in (0, 1, 3, 5):
+            assert_close(run_decode(case, num_splits=splits), want, f"k{kb}v{vb} block {bs}, {splits} parts", lens)
+
+
 def test_decode_returns_lse():
     """Log-sum-exp of the scaled scores (natural log) next to the output: against the oracle's partial (m + log l)."""
     from sub0_b200 import ops

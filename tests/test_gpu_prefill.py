@@ -263,6 +263,53 @@ def test_whole_long_prompt_vs_oracle():
     assert_close(run_prefill(case, Q, cu, lens), want, "whole 6200-token prompt", visible_keys(lens, lens))
 
 
+def _random_prefill_cases(seed, count):
+    """Seeded random shapes: code widths, group sizes 1 .. 8, 1 .. 8 KV heads, cache blocks of 16 .. 128 slots (powers of
+    two and not), batches of 1 .. 33 ragged prompts, whole prompts and chunks with a compressed past."""
+    import random
+    rng = random.Random(seed)
+    for _ in range(count):
+        kb, vb = rng.choice([(4, 4), (4, 4), (4, 2), (2, 2)])
+        group, H_kv = rng.choice([1, 2, 4, 4, 8, 8]), rng.choice([1, 2, 3, 4, 8])
+        bs = rng.choice([16, 16, 32, 48, 64, 80, 128])
+        B = rng.choice([1, 2, 3, 5, 8, 13, 33])
+        cap = max(40, min(5000, int((3e7 / (B * H_kv * group)) ** 0.5)))      # bounds the oracle's score matrix
+        lens = [rng.choice([1, 15, 16, 17, 127, 128, 129]) if rng.random() < 0.15 else rng.randint(1, cap) for _ in range(B)]
+        whole = rng.random() < 0.4
+        q_lens = [n if whole else rng.randint(1, n) for n in lens]
+        yield dict(kb=kb, vb=vb, group=group, H_kv=H_kv, bs=bs, lens=lens, q_lens=q_lens, seed=rng.randint(0, 1 << 30))
+
+
+def test_random_shapes_match_the_model_of_the_kernels_roundings():
+    """The kernel against ``tests/_kernel_model.py`` -- the reference algorithm with the kernel's documented roundings
+    (fp16 code tables with the norm outside the K tile, two-term fp16 norm inside the V tile, fp16 probabilities against
+    the first tile's maximum) -- on random shapes.  The two agree up to single fp16 rounding flips of the rotated row:
+    no element may leave the path's stated tolerance (measured over 11 shapes and 75 M elements: one element, 1.33 x),
+    whereas the distance to the oracle itself is several times larger on prompts of a few hundred tokens and is capped
+    below at twice what these shapes show (up to 4.4e-4 of the elements outside 1e-3 + 2e-3 |want|, worst 5.2 x: the
+    fp16 rounding of the 16 or 4 code levels is the same for every key that uses a level, and the reference rounds
+    level * norm to fp16 where the kernel keeps the norm in fp32 -- neither averages out on rows that see few keys)."""
+    from tests import _kernel_model as KM
+    total = bad_model = bad_oracle = 0
+    for d in _random_prefill_cases(20260, 12):
+        case = Cs.paged_case(d["lens"], H_kv=d["H_kv"], group=d["group"], k_bits=d["kb"], v_bits=d["vb"], block_size=d["bs"],
+                             seed=d["seed"])
+        Q, cu = prefill_inputs(case, d["q_lens"], d["seed"] + 1)
+        kw = dict(cb_K=case["cb_K"], cb_V=case["cb_V"], group=d["group"], block_size=d["bs"], k_bits=d["kb"], v_bits=d["vb"])
+        got = run_prefill(case, Q, cu, d["q_lens"], k4v2=(d["kb"], d["vb"]) == (4, 2))
+        assert not bool(got.isnan().any()), f"{d}: NaN in output"
+        model = KM.paged_prefill_model(Q, case["cache"], case["block_table"], cu, case["seq_lens"], **kw)
+        want = O.paged_prefill(Q, case["cache"], case["block_table"], cu, case["seq_lens"], **kw)
+        bm, wm, n = Cs.violations(got, model)
+        bo, wo, _ = Cs.violations(got, want)
+        assert bm <= n // 2_000_000 and wm <= 1.5, f"{d}: {bm} of {n} elements off the model (worst x{wm:.2f})"
+        assert bo <= 1e-3 * n and wo <= 8.0 and Cs.cosine(got, want) >= 0.9999, \
+            f"{d}: {bo} of {n} elements outside 1e-3 + 2e-3|want| of the oracle (worst x{wo:.2f})"
+        total += n; bad_model += bm; bad_oracle += bo
+    Cs.STATS.append({"what": "random prefill shapes", "form": "strict", "elements": total, "violations": bad_oracle,
+                     "violations_vs_model": bad_model})
+
+
 def _exact_norm_prefill(Q, case, cu, group):
     """Causal attention with the arithmetic of the fused kernel spelled out in float64: scores = (fp16 rotated query . fp16
     codebook levels) x fp32 key norm x scale, values = levels x norm, result rounded to fp16 before and after the inverse

@@ -134,6 +134,11 @@ def test_split_planning_properties(lib):
     assert L.cda_b200_decode_plan_splits(32, 8, 65536, -1) == 6
     assert L.cda_b200_decode_plan_splits(4, 8, 65536, -1) == 37       # 148 = 4 x 37: equal ranges inside each sequence
     assert L.cda_b200_decode_plan_splits(32, 8, 4096, -1) == 6        # 148 chunks over a line with a gap behind every sequence
+    # an odd number of partial rows (13 sequences x 3 query heads x 1 or 3 parts): the (m, l) pairs are padded to a
+    # multiple of 16 bytes so that the O rows behind them stay 16-byte aligned
+    for parts in (1, 3):
+        rows = parts * 13 * 3
+        assert L.cda_b200_decode_workspace_bytes(13, 3, 3, 5000, parts, -1) == 256 + (rows * 8 + 8) + rows * 512
     assert L.cda_b200_decode_plan_splits(37, 8, 4096, -1) == 4        # 37 x 4 = 148: equal ranges inside each sequence
     assert L.cda_b200_decode_plan_splits(1, 8, 4096, -1) == 32        # never below 128 tokens per chunk
     assert L.cda_b200_decode_plan_splits(0, 8, 16, -1) == lib.CDA_ERR_BAD_ARG
