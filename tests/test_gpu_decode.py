@@ -309,6 +309,42 @@ def test_decode_odd_number_of_partial_rows():
             assert_close(run_decode(case, num_splits=splits), want, f"k{kb}v{vb} block {bs}, {splits} parts", lens)
 
 
+def test_decode_random_shapes():
+    """Seeded random shapes through the plain decode and through partials of randomly cut shards merged again: code
+    widths, 1 .. 8 query heads per KV head, 1 .. 8 KV heads, cache blocks of 16 .. 128 slots (powers of two and not),
+    1 .. 33 ragged sequences with empty and one-token ones, planned and forced split counts."""
+    import random
+    from sub0_b200 import ops
+    rng = random.Random(4242)
+    for i in range(30):
+        kb, vb = rng.choice([(4, 4), (4, 4), (4, 2), (2, 2)])
+        group, H_kv = rng.choice([1, 2, 4, 4, 8, 8]), rng.choice([1, 2, 3, 4, 5, 8])
+        bs = rng.choice([16, 16, 32, 48, 64, 80, 128])
+        B = rng.choice([1, 2, 3, 5, 8, 13, 33])
+        lens = [rng.choice([0, 1, 15, 16, 17, 128]) if rng.random() < 0.15 else rng.randint(1, 40000 // (B * H_kv)) for _ in range(B)]
+        what = f"k{kb}v{vb} g{group} H{H_kv} block {bs} lens {lens}"
+        case = Cs.paged_case(lens, H_kv=H_kv, group=group, k_bits=kb, v_bits=vb, block_size=bs, seed=rng.randint(0, 1 << 30))
+        want = Cs.oracle_decode(case)
+        got = run_decode(case, num_splits=rng.choice([0, 0, 1, 3, 5, 16, 200]))
+        assert_close(got, want, what, lens)
+        assert all(bool((got[b] == 0).all()) for b, n in enumerate(lens) if n == 0), what
+        if i % 3:
+            continue
+        d = to_dev(case)                                          # shards of the block table, one partial each, merged
+        nblk = d["block_table"].shape[1]
+        edges = [0] + sorted(rng.randint(0, nblk) for _ in range(rng.choice([1, 2]))) + [nblk]
+        parts = []
+        for lo, hi in zip(edges[:-1], edges[1:]):
+            bt = d["block_table"][:, lo:max(hi, lo + 1)].contiguous()
+            sl = (d["seq_lens"] - lo * bs).clamp(0, (hi - lo) * bs).to(torch.int32)
+            parts.append(ops.decode_partial(d["Q"], d["cache"], bt, sl, cb_K=d["cb_K"], cb_V=d["cb_V"], block_size=bs,
+                                            max_seq_len=max(int(sl.max()), 1), num_splits=rng.choice([0, 1, 3])))
+        out = torch.full_like(d["Q"], float("nan"))
+        ops.merge_partials(torch.stack(parts), out)
+        torch.cuda.synchronize()
+        assert_close(out.cpu(), want, what + f" shards {edges}", lens)
+
+
 def test_decode_returns_lse():
     """Log-sum-exp of the scaled scores (natural log) next to the output: against the oracle's partial (m + log l)."""
     from sub0_b200 import ops
