@@ -189,7 +189,7 @@ int cda_b200_decode_exchange(const void* Q, const void* kv_cache, const int32_t*
  *   num_splits   0 = planned decomposition; whatever is asked, the number of partials per row is lowered until they
  *                fit in 8 MiB.
  *   returns      CDA_ERR_WORKSPACE (with the sizes in the message) when even one partial per row does not fit, i.e.
- *                when B * H_q * 520 B + 256 exceeds 8 MiB.
+ *                when B * H_q * 520 B + 256 (+ 8 when B * H_q is odd: the O rows stay 16-byte aligned) exceeds 8 MiB.
  * The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device current);
  * make that first call at start-up and outside any stream capture: with lazy module loading that first call is also
  * when the driver reserves the 8 MiB on that device, so it must come before the host hands out all device memory.  All calls share the one array and it keeps the previous call's
