@@ -43,6 +43,13 @@ __device__ int g_prefill_status = 0;
 static unsigned long long g_wait_limit_ns = umma::kWaitLimitNs;
 static int g_withhold_first_k = 0;
 
+#ifndef CDA_PF_EXACT_V
+#define CDA_PF_EXACT_V 1
+#endif
+#ifndef CDA_PF_UNIFORM_KN
+#define CDA_PF_UNIFORM_KN 1
+#endif
+
 namespace pfu {
 
 constexpr int kRows = 128;            // rows of one block (one tcgen05.mma M)
@@ -196,13 +203,69 @@ __device__ __forceinline__ void expand_quad(uint32_t tile, uint32_t lut_lane, ui
   }
 }
 
+// ---- 4-bit codes: exact rows from a per-key table held in registers -----------------------------------------------------
+// The reference decodes a row as fp16(level * norm) (fp32 product, one rounding; compression.py:337-361).  A key has only
+// 16 such values, so the producer computes them once per key -- 16 fp32 products and roundings -- and keeps them as byte
+// planes: lo[k] holds the low bytes of the values of levels 4k .. 4k + 3, hi[k] the high bytes.  A code then selects its
+// value with byte permutes (the low three bits of the code pick one of eight bytes, its top bit picks the register pair),
+// four codes per instruction, and the tile holds exactly the reference's fp16 rows: no table in shared memory, no gather,
+// no per-level or per-norm rounding of its own.
+struct LevelPlanes { uint32_t lo[4], hi[4]; };
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t d;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+// cb_addr: shared address of the 16 fp32 levels (16-byte aligned; every thread reads the same words).
+__device__ __forceinline__ LevelPlanes level_planes(uint32_t cb_addr, float norm) {
+  LevelPlanes t;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const uint4 c = lds128(cb_addr + 16u * k);
+    float p0, p1, p2, p3;                            // packed fp32 products: each half rounds as the scalar multiply does
+    f2_unpack(f2_mul(f2_pack(c.x, c.y), f2_pack(norm, norm)), p0, p1);
+    f2_unpack(f2_mul(f2_pack(c.z, c.w), f2_pack(norm, norm)), p2, p3);
+    const uint32_t h0 = pack_half2(p0, p1), h1 = pack_half2(p2, p3);
+    t.lo[k] = prmt(h0, h1, 0x6420u);
+    t.hi[k] = prmt(h0, h1, 0x7531u);
+  }
+  return t;
+}
+// 16 bytes of 4-bit codes (32 coordinates of token row `nl`, piece `quad` of its 64 code bytes) into the tile.  A code byte
+// holds coordinate 2j in its high nibble and 2j + 1 in its low nibble (compression.py:163-188), so the selector nibbles of
+// two bytes pick (1, 0, 3, 2); the last two permutes put the bytes back in order while pairing low and high bytes.
+__device__ __forceinline__ void expand_quad_exact(uint32_t tile, const LevelPlanes& t, const uint4& w, int nl, int quad) {
+  const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+  for (int wi = 0; wi < 4; ++wi) {
+    const uint32_t x = ws[wi];
+    const uint32_t m = x & 0x77777777u;            // low three bits of every code: byte selectors
+    const uint32_t y = x & 0x88888888u, a = y << 4;   // top bit of every code, as the sign bit of a byte of y or a
+    uint32_t v[4];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {                  // two code bytes = four coordinates per turn
+      const uint32_t sel = h ? m >> 16 : m;
+      const uint32_t upper = prmt(a, y, h ? 0xFBEAu : 0xD9C8u);   // 0xFF in the bytes whose code is 8 .. 15
+      const uint32_t la = prmt(t.lo[0], t.lo[1], sel), lb = prmt(t.lo[2], t.lo[3], sel);
+      const uint32_t ha = prmt(t.hi[0], t.hi[1], sel), hb = prmt(t.hi[2], t.hi[3], sel);
+      const uint32_t lo = (lb & upper) | (la & ~upper), hi = (hb & upper) | (ha & ~upper);
+      v[2 * h] = prmt(lo, hi, 0x4051u);
+      v[2 * h + 1] = prmt(lo, hi, 0x6273u);
+    }
+    const int c16 = quad * 4 + wi;                 // 16-byte chunk of the row: 8 coordinates
+    sts128(tile + (c16 >> 3) * kColBlockBytes + sw128(nl, c16 & 7), v[0], v[1], v[2], v[3]);
+  }
+}
+
 // One thread's 64 scores of a tile (columns s_col .. s_col + 63 of its TMEM lane), scaled by the key norms kn[0..63]
 // (16-byte aligned).  MASK: keys beyond q_pos (the row's diagonal) count as minus infinity.  The next 16 columns are
 // requested before the current ones are worked on (tcgen05.wait::ld covers every load issued so far).
-template <bool MASK>
+// UNI: every key has the same factor (kn[0]): the rows in the tile already carry their norm.
+template <bool MASK, bool UNI>
 __device__ __forceinline__ float row_max(uint32_t s_col, const float* kn, int key0, int q_pos) {
   float mx[2] = {-INFINITY, -INFINITY};
   const ulonglong2* kn2 = reinterpret_cast<const ulonglong2*>(kn);
+  const uint64_t ku = f2_pack(kn[0], kn[0]);
   uint32_t s[2][16];
   umma::tmem_ld16(s_col, s[0]);
 #pragma unroll
@@ -211,7 +274,7 @@ __device__ __forceinline__ float row_max(uint32_t s_col, const float* kn, int ke
     if (ch < 3) umma::tmem_ld16(s_col + 16 * (ch + 1), s[(ch + 1) & 1]);
 #pragma unroll
     for (int c = 0; c < 16; c += 4) {
-      const ulonglong2 k4 = kn2[4 * ch + c / 4];
+      const ulonglong2 k4 = UNI ? make_ulonglong2(ku, ku) : kn2[4 * ch + c / 4];
       float x[4];
       f2_unpack(f2_mul(f2_pack(s[ch & 1][c], s[ch & 1][c + 1]), k4.x), x[0], x[1]);
       f2_unpack(f2_mul(f2_pack(s[ch & 1][c + 2], s[ch & 1][c + 3]), k4.y), x[2], x[3]);
@@ -227,11 +290,12 @@ __device__ __forceinline__ float row_max(uint32_t s_col, const float* kn, int ke
 }
 // exp2(score * kn - m) for the same 64 scores; P as fp16 pairs into columns s_col .. s_col + 31 (the value norms are
 // already inside the V tile).  Returns the sum of the probabilities.
-template <bool MASK>
+template <bool MASK, bool UNI>
 __device__ __forceinline__ float row_probabilities(uint32_t s_col, const float* kn, float m, int key0, int q_pos) {
   uint64_t sum = f2_pack(0.f, 0.f);
   const uint64_t neg_m = f2_pack(-m, -m);
   const ulonglong2* kn2 = reinterpret_cast<const ulonglong2*>(kn);
+  const uint64_t ku = f2_pack(kn[0], kn[0]);
   uint32_t s[2][16];
   umma::tmem_ld16(s_col, s[0]);
 #pragma unroll
@@ -241,7 +305,7 @@ __device__ __forceinline__ float row_probabilities(uint32_t s_col, const float* 
     if (ch < 3) umma::tmem_ld16(s_col + 16 * (ch + 1), s[(ch + 1) & 1]);
 #pragma unroll
     for (int c = 0; c < 16; c += 2) {
-      const ulonglong2 k4 = kn2[4 * ch + c / 4];
+      const ulonglong2 k4 = UNI ? make_ulonglong2(ku, ku) : kn2[4 * ch + c / 4];
       float a0, a1;
       f2_unpack(f2_fma(f2_pack(s[ch & 1][c], s[ch & 1][c + 1]), (c & 2) ? k4.y : k4.x, neg_m), a0, a1);
       if (MASK) {
@@ -284,11 +348,12 @@ __device__ __forceinline__ void scale_p_chunks(uint32_t col, int chunks, float f
 // binary orders first (its earlier probabilities of this tile and their sum are multiplied by 2^-d).  `shift` returns
 // the total of those moves; the caller settles the two halves of a row on the larger shift before P is published.
 constexpr float kSafe = 14.0f;
-template <bool MASK>
+template <bool MASK, bool UNI>
 __device__ __forceinline__ float row_probabilities_stale(uint32_t s_col, const float* kn, float m, int key0, int q_pos, float& shift) {
   uint64_t sum = f2_pack(0.f, 0.f);
   uint64_t neg_ref = f2_pack(-m, -m);
   const ulonglong2* kn2 = reinterpret_cast<const ulonglong2*>(kn);
+  const uint64_t ku = f2_pack(kn[0], kn[0]);
   shift = 0.f;
   uint32_t s[2][16];
   umma::tmem_ld16(s_col, s[0]);
@@ -300,7 +365,7 @@ __device__ __forceinline__ float row_probabilities_stale(uint32_t s_col, const f
     float a[16];
 #pragma unroll
     for (int c = 0; c < 16; c += 2) {
-      const ulonglong2 k4 = kn2[4 * ch + c / 4];
+      const ulonglong2 k4 = UNI ? make_ulonglong2(ku, ku) : kn2[4 * ch + c / 4];
       f2_unpack(f2_fma(f2_pack(s[ch & 1][c], s[ch & 1][c + 1]), (c & 2) ? k4.y : k4.x, neg_ref), a[c], a[c + 1]);
       if (MASK) {
         a[c] = key0 + 16 * ch + c > q_pos ? -INFINITY : a[c];
@@ -465,14 +530,20 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
   __shared__ int s_idx[64];
   float alpha_k = 1.0f, alpha_v = 1.0f;
   if constexpr (!kDense) find_table_scales<kLevK, kLevV>(p.cb_k, p.cb_v, s_err, s_idx, alpha_k, alpha_v);
-  // One table serves both sides when the codebooks are the same (then their scales are the same too).
+  // 4-bit sides expand exact rows from the fp32 levels (kept in s_levels); 2-bit sides go through a table of fp16
+  // levels.  One table owns the whole table area when only one side needs one, or when both sides' codebooks are the
+  // same (then their scales are the same too); else each side's table takes half.
+  constexpr bool kExactK = KB == 4, kExactV = VB == 4 && CDA_PF_EXACT_V;
+  constexpr bool kUni = (kExactK || kDense) && CDA_PF_UNIFORM_KN;   // every key's score factor is the softmax scale
+  __shared__ __align__(16) float s_levels[2][16];
   bool same_cb = KB == VB;
   if (KB == VB && !kDense) {
 #pragma unroll
     for (int i = 0; i < kLevK; ++i) same_cb = same_cb && __ldg(p.cb_k + i) == __ldg(p.cb_v + i);
   }
-  const uint32_t lut_stride = same_cb ? 64u : 32u;
-  const uint32_t lutv_off = same_cb ? 0u : static_cast<uint32_t>(kLutBytes / 2);
+  const bool one_table = kExactK || kExactV || same_cb;
+  const uint32_t lut_stride = one_table ? 64u : 32u;
+  const uint32_t lutv_off = one_table ? 0u : static_cast<uint32_t>(kLutBytes / 2);
 
   // ---- set-up: barriers, TMEM, tables, rotated queries -----------------------------------------------------------------
   if (tid == 0) {
@@ -491,8 +562,10 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
     tmem_relinquish();
   }
   if constexpr (!kDense) {
-    fill_code_table<KB>(sm + kOffLut, lut_stride, p.cb_k, 1.0f / alpha_k, tid, kThreads);
-    if (!same_cb) fill_code_table<VB>(sm + kOffLut + lutv_off, lut_stride, p.cb_v, 1.0f / alpha_v, tid, kThreads);
+    if (kExactK) { if (tid < 16) s_levels[0][tid] = __ldg(p.cb_k + tid); }
+    else fill_code_table<KB>(sm + kOffLut, lut_stride, p.cb_k, 1.0f / alpha_k, tid, kThreads);
+    if (kExactV) { if (tid >= 32 && tid < 48) s_levels[1][tid - 32] = __ldg(p.cb_v + tid - 32); }
+    else if (kExactK || !same_cb) fill_code_table<VB>(sm + kOffLut + lutv_off, lut_stride, p.cb_v, 1.0f / alpha_v, tid, kThreads);
   }
   // Q: park the raw rows; then warps 0..15 rotate 16 rows each and store them as the A operand of Q K^T (K-major,
   // 128-byte swizzle)
@@ -544,7 +617,7 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
       if (__any_sync(0xffffffffu, m_used == -INFINITY)) {
       // a row without a reference yet (tile 0: key 0 is never masked, so every row has one afterwards): two passes
       // pass 1: maximum of this thread's 64 scaled scores (diagonal tiles take the masking variant)
-      const float mx_own = diag ? row_max<true>(s_col, kn, key0, q_pos) : row_max<false>(s_col, kn, key0, q_pos);
+      const float mx_own = diag ? row_max<true, kUni>(s_col, kn, key0, q_pos) : row_max<false, kUni>(s_col, kn, key0, q_pos);
       float mx = mx_own;
       // the row maximum needs the other half's keys
       xch[((j & 1) * 2 + half) * kRows + t] = mx;
@@ -561,12 +634,12 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
       if (rescale) rescale_o(o_col, factor);
       // pass 2: probabilities.  The scores are read again from TMEM, 16 columns at a time; the fp16 P of a chunk
       // (keys 2c, 2c+1 in column c) goes straight over score columns this thread has already consumed.
-      l_run += diag ? row_probabilities<true>(s_col, kn, m_used, key0, q_pos) : row_probabilities<false>(s_col, kn, m_used, key0, q_pos);
+      l_run += diag ? row_probabilities<true, kUni>(s_col, kn, m_used, key0, q_pos) : row_probabilities<false, kUni>(s_col, kn, m_used, key0, q_pos);
       } else {
       // one pass against the reference the row already has; the halves of a row then settle on a common reference
       float shift;
-      float sum = diag ? row_probabilities_stale<true>(s_col, kn, m_used, key0, q_pos, shift)
-                       : row_probabilities_stale<false>(s_col, kn, m_used, key0, q_pos, shift);
+      float sum = diag ? row_probabilities_stale<true, kUni>(s_col, kn, m_used, key0, q_pos, shift)
+                       : row_probabilities_stale<false, kUni>(s_col, kn, m_used, key0, q_pos, shift);
       xch[((j & 1) * 2 + half) * kRows + t] = shift;
       named_barrier(bar_id, group_threads);
       const float common = fmaxf(shift, xch[((j & 1) * 2 + (half ^ 1)) * kRows + t]);
@@ -694,19 +767,27 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
     };
     struct KRegs { uint4 w[kItK]; float n[kItK]; };
     struct VRegs { uint4 w[kItV]; float n[kItV]; };
+    // Which 16-byte piece of which key a producer thread expands in turn `it`.  2-bit side (one turn): two threads per key,
+    // one piece each.  4-bit side (two turns): thread t takes key t mod 128 and the pieces 2 (t / 128) + it -- both turns on
+    // the same key, whose table of exact values is built once, and a warp stores to 32 different rows of the swizzled tile.
+    auto piece_of = [&](bool exact, int bits, int it, int& nl, int& quad) {
+      if (exact) { nl = pt & (kKeys - 1); quad = 2 * (pt >> 7) + it; }
+      else { const int x = pt + kProducerThreads * it; nl = x / bits; quad = x % bits; }
+    };
     int kblk[kItK], vblk[kItV];                               // block ids of the next tile to fetch
 #pragma unroll
-    for (int it = 0; it < kItK; ++it) kblk[it] = block_id((pt + kProducerThreads * it) / KB, 0);
+    for (int it = 0; it < kItK; ++it) { int nl, quad; piece_of(kExactK, KB, it, nl, quad); kblk[it] = block_id(nl, 0); }
 #pragma unroll
-    for (int it = 0; it < kItV; ++it) vblk[it] = block_id((pt + kProducerThreads * it) / VB, 0);
+    for (int it = 0; it < kItV; ++it) { int nl, quad; piece_of(kExactV, VB, it, nl, quad); vblk[it] = block_id(nl, 0); }
     auto load_k = [&](int j, KRegs& r) {
       if (j >= n_tiles) return;
 #pragma unroll
       for (int it = 0; it < kItK; ++it) {
-        const int x = pt + kProducerThreads * it, nl = x / KB, quad = x % KB;
+        int nl, quad;
+        piece_of(kExactK, KB, it, nl, quad);
         const uint8_t* src = slot_ptr(kblk[it], nl, j);
         r.w[it] = __ldg(reinterpret_cast<const uint4*>(src + 16 * quad));
-        if (quad == 0) r.n[it] = __ldg(reinterpret_cast<const float*>(src + 16 * KB + 16 * VB));
+        if (kExactK ? it == 0 : quad == 0) r.n[it] = __ldg(reinterpret_cast<const float*>(src + 16 * KB + 16 * VB));
         kblk[it] = block_id(nl, j + 1);
       }
     };
@@ -714,10 +795,11 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
       if (j >= n_tiles) return;
 #pragma unroll
       for (int it = 0; it < kItV; ++it) {
-        const int x = pt + kProducerThreads * it, nl = x / VB, quad = x % VB;
+        int nl, quad;
+        piece_of(kExactV, VB, it, nl, quad);
         const uint8_t* src = slot_ptr(vblk[it], nl, j);
         r.w[it] = __ldg(reinterpret_cast<const uint4*>(src + 16 * KB + 16 * quad));
-        r.n[it] = __ldg(reinterpret_cast<const float*>(src + 16 * KB + 16 * VB + 4));
+        if (!kExactV || it == 0) r.n[it] = __ldg(reinterpret_cast<const float*>(src + 16 * KB + 16 * VB + 4));
         vblk[it] = block_id(nl, j + 1);
       }
     };
@@ -728,11 +810,23 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
     auto expand_k = [&](int j, const KRegs& r) {
       const uint32_t tile = base + kOffK + (j & 1) * kTileBytes;
       float* kn = reinterpret_cast<float*>(sm + kOffKn) + (j & 3) * kKeys;
+      if constexpr (kExactK) {   // the key norm is inside the exact rows: every key's score factor is the softmax scale
+        const LevelPlanes t = level_planes(smem_addr(s_levels[0]), r.n[0]);
 #pragma unroll
-      for (int it = 0; it < kItK; ++it) {
-        const int x = pt + kProducerThreads * it, nl = x / KB, quad = x % KB;
-        if (quad == 0) kn[nl] = r.n[it] * kscale;
-        expand_quad<KB, false>(tile, lutk_lane, kStride, r.w[it], nl, quad, 0u, 0u);
+        for (int it = 0; it < kItK; ++it) {
+          int nl, quad;
+          piece_of(kExactK, KB, it, nl, quad);
+          if (quad == 0) kn[nl] = p.scale_log2;
+          expand_quad_exact(tile, t, r.w[it], nl, quad);
+        }
+      } else {
+#pragma unroll
+        for (int it = 0; it < kItK; ++it) {
+          int nl, quad;
+          piece_of(kExactK, KB, it, nl, quad);
+          if (quad == 0) kn[nl] = r.n[it] * kscale;
+          expand_quad<KB, false>(tile, lutk_lane, kStride, r.w[it], nl, quad, 0u, 0u);
+        }
       }
       fence_async_smem();
       __syncwarp();
@@ -742,14 +836,25 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
       }
     };
     auto expand_v = [&](int j, const VRegs& r) {
+      if constexpr (kExactV) {
+        const LevelPlanes t = level_planes(smem_addr(s_levels[1]), r.n[0]);
 #pragma unroll
-      for (int it = 0; it < kItV; ++it) {
-        const int x = pt + kProducerThreads * it, nl = x / VB, quad = x % VB;
-        // the value norm goes into the tile (fp16 products, norm as two fp16 terms), so the probabilities need no per-key factor
-        const float n_hi = round_to_half(r.n[it]);
-        const float n_lo = r.n[it] - n_hi;
-        expand_quad<VB, true>(base + kOffV + (j & 1) * kTileBytes, lutv_lane, kStride, r.w[it], nl, quad, pack_half2(n_hi, n_hi),
-                              pack_half2(n_lo, n_lo));
+        for (int it = 0; it < kItV; ++it) {
+          int nl, quad;
+          piece_of(kExactV, VB, it, nl, quad);
+          expand_quad_exact(base + kOffV + (j & 1) * kTileBytes, t, r.w[it], nl, quad);
+        }
+      } else {
+#pragma unroll
+        for (int it = 0; it < kItV; ++it) {
+          int nl, quad;
+          piece_of(kExactV, VB, it, nl, quad);
+          // the value norm goes into the tile (fp16 products, norm as two fp16 terms), so the probabilities need no per-key factor
+          const float n_hi = round_to_half(r.n[it]);
+          const float n_lo = r.n[it] - n_hi;
+          expand_quad<VB, true>(base + kOffV + (j & 1) * kTileBytes, lutv_lane, kStride, r.w[it], nl, quad, pack_half2(n_hi, n_hi),
+                                pack_half2(n_lo, n_lo));
+        }
       }
       fence_async_smem();
       __syncwarp();
@@ -771,7 +876,7 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
       load_v(i + 1, vr);
     }
     };
-    if (same_cb) produce(std::integral_constant<uint32_t, 64u>{});
+    if (one_table) produce(std::integral_constant<uint32_t, 64u>{});
     else produce(std::integral_constant<uint32_t, 32u>{});
     if (bad_block) atomicOr(&g_prefill_status, 1);
    }

@@ -5,10 +5,11 @@ differs in four documented places, and this model restates exactly those, so tha
 bound several times tighter than the path's stated tolerance against the model -- a wrong tile, mask or scale shows up
 there even where the comparison with the oracle would still be inside its (wider) bound:
 
-  1. K tile entries are fp16(level / alpha_k) -- no norm inside; the score is multiplied by
-     norm_k * scale * log2(e) * alpha_k in fp32.
-  2. V tile entries are fp16 arithmetic on fp16(level / alpha_v): e * hi + fp16(e * lo) with hi = fp16(norm_v),
-     lo = fp16(norm_v - hi), one rounding at the end; alpha_v multiplies the final normalisation.
+  1. K tile entries of a 2-bit side are fp16(level / alpha_k) -- no norm inside; the score is multiplied by
+     norm_k * scale * log2(e) * alpha_k in fp32.  (A 4-bit side holds the reference's own rows, fp16(level * norm).)
+  2. V tile entries of a 2-bit side are fp16 arithmetic on fp16(level / alpha_v): e * hi + fp16(e * lo) with
+     hi = fp16(norm_v), lo = fp16(norm_v - hi), one rounding at the end; alpha_v multiplies the final normalisation.
+     (A 4-bit side: the reference's own rows.)
   3. Probabilities are exp2(score - m) with m the largest score among the row's first 128 keys, rounded to fp16 for the
      P V product (later tiles move the reference by whole powers of two only, which does not change the rounding); the
      row sum adds the unrounded values.
@@ -51,19 +52,25 @@ def round_mantissa_to_fp16(x: torch.Tensor) -> torch.Tensor:
 
 
 def kernel_tiles(slot_k, slot_v, cb_K, cb_V, k_bits, v_bits):
-    """K levels (fp32 tensor of fp16 values, norm not applied), the per-key score factor without the softmax scale, and the
-    V rows as the producers store them (fp32 tensor of fp16 values); alpha_v is returned for the final normalisation."""
-    ak, av = table_scale(cb_K), table_scale(cb_V)
-    ki = O.unpack_indices(slot_k.idx, k_bits).long()
+    """K tile rows (fp32 tensor of fp16 values), the per-key score factor without the softmax scale, alpha_k, the V rows as
+    the producers store them (fp32 tensor of fp16 values) and alpha_v for the final normalisation."""
+    if k_bits == 4:
+        k_rows, k_factor, ak = O.decode_rotated(slot_k, cb_K).float(), torch.ones_like(slot_k.norm.float()), 1.0
+    else:
+        ak = table_scale(cb_K)
+        ki = O.unpack_indices(slot_k.idx, k_bits).long()
+        k_rows, k_factor = (cb_K.float() * np.float32(1.0 / np.float32(ak))).half().float()[ki], slot_k.norm.float()
+    if v_bits == 4:
+        return k_rows, k_factor, ak, O.decode_rotated(slot_v, cb_V).float(), 1.0
+    av = table_scale(cb_V)
     vi = O.unpack_indices(slot_v.idx, v_bits).long()
-    k_lev = (cb_K.float() * np.float32(1.0 / np.float32(ak))).half().float()[ki]
     v_lev = (cb_V.float() * np.float32(1.0 / np.float32(av))).half().float()[vi]
     n = slot_v.norm.float().unsqueeze(-1)
     hi = n.half().float()
     lo = (n - hi).half().float()
     t = (v_lev * lo).half().float()
     v_rows = (v_lev.double() * hi.double() + t.double()).half().float()          # fma.rn.f16x2: one rounding
-    return k_lev, slot_k.norm.float(), ak, v_rows, av
+    return k_rows, k_factor, ak, v_rows, av
 
 
 def paged_prefill_model(Q, flat_cache, block_table, cu_seqlens_q, seq_lens, *, cb_K, cb_V, group, block_size,
