@@ -8,17 +8,17 @@
 // of one KV head, so that a dequantised key/value tile serves the whole GQA group and both blocks.  Keys are processed
 // 128 at a time; the two blocks run half a step apart, so one block's softmax overlaps the other's matrix products:
 //
-//   producer warps (8)    cache slots -> registers (one tile ahead) -> unit-level fp16 tiles in shared memory (128-byte
-//                         swizzled rows, the layout tcgen05.mma reads; V rows already times their norm), key norms to a
-//                         side array
+//   producer warps (8)    cache slots -> registers (one tile ahead) -> fp16 tiles in shared memory (128-byte swizzled
+//                         rows, the layout tcgen05.mma reads).  A tile row is the reference's decoded row, fp16(level x
+//                         norm): each key's 16 (or 4) values are computed once and selected per code with byte permutes
 //   MMA warp (1 thread)   per block: S = Q K^T (128x128x128, Q and K from shared memory) and O += P V (128x128x128, P from
 //                         tensor memory, V from shared memory)
-//   softmax warps (2 x 8) two threads per row (64 keys each): TMEM -> registers, scale by the key norm, mask, online
+//   softmax warps (2 x 8) two threads per row (64 keys each): TMEM -> registers, softmax scale, mask, online
 //                         maximum with lazy rescaling of O, exp2, fp16 P -> TMEM over the thread's own score columns
 //
 // Tensor memory (512 columns): S of block b at [128 b, 128 b + 128), O of block b at [256 + 128 b, ...).  P of the keys
 // [64 h, 64 h + 64) lives in the first 32 columns of the same thread's scores, [128 b + 64 h, + 32).
-// Shared memory (217 KB): Q 64 KB, K 2 x 32 KB, V 2 x 32 KB, code tables 16 KB, norms, exchange words, barriers.
+// Shared memory (198 KB): Q 64 KB, K 2 x 32 KB, V 2 x 32 KB, exchange words, barriers.
 //
 // The roles hand tiles over through mbarriers; every wait is bounded (umma.cuh) and a wait that gives up sets a fault
 // flag and ends the CTA cleanly (TMEM is released).
@@ -43,13 +43,6 @@ __device__ int g_prefill_status = 0;
 static unsigned long long g_wait_limit_ns = umma::kWaitLimitNs;
 static int g_withhold_first_k = 0;
 
-#ifndef CDA_PF_EXACT_V
-#define CDA_PF_EXACT_V 1
-#endif
-#ifndef CDA_PF_UNIFORM_KN
-#define CDA_PF_UNIFORM_KN 1
-#endif
-
 namespace pfu {
 
 constexpr int kRows = 128;            // rows of one block (one tcgen05.mma M)
@@ -67,28 +60,14 @@ constexpr int kOffQ = 0;                       // 2 blocks x (2 column blocks x 
 constexpr int kOffK = 65536;                   // 2 stages x (2 column blocks x 128 rows x 128 B); also stages the O rows
 constexpr int kOffV = 131072;                  // 2 stages x (2 column blocks x 128 rows x 128 B)
 constexpr int kTileBytes = 32768, kColBlockBytes = 16384;
-constexpr int kOffLut = 196608;                // 16 KB of code tables
-constexpr int kLutBytes = 16384;
-constexpr int kOffKn = kOffLut + kLutBytes;    // 4 x 128 floats: key norm * softmax scale * log2(e) * alpha_k
-constexpr int kOffXch = kOffKn + 2048;         // 2 blocks x 2 parities x 2 halves x 128 floats: row maxima / sums of the two threads of a row
+constexpr int kOffXch = 196608;                // 2 blocks x 2 parities x 2 halves x 128 floats: row maxima / sums of the two threads of a row
 constexpr int kOffBar = kOffXch + 4096;        // mbarriers, TMEM address, flags
 constexpr int kSmemBytes = kOffBar + 256 + 1024;   // + slack for the 1024-byte alignment
 
 // barrier slots (8 bytes each) inside kOffBar
-constexpr int kBarKFull = 0, kBarKEmpty = 2, kBarVFull = 4, kBarVEmpty = 6, kBarSFull = 8, kBarPFull = 10, kBarPvDone = 12,
-              kBarNorms = 14;   // 18 barriers
+constexpr int kBarKFull = 0, kBarKEmpty = 2, kBarVFull = 4, kBarVEmpty = 6, kBarSFull = 8, kBarPFull = 10, kBarPvDone = 12;   // 14 barriers
 constexpr int kOffTmemAddr = 160, kOffOutcome = 168, kOffAbort = 192;   // outcome words: 2 per waiting group (3 groups); WaitState (16 B)
 
-__device__ __forceinline__ uint32_t lds32(uint32_t a) {
-  uint32_t v;
-  asm("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(a));
-  return v;
-}
-__device__ __forceinline__ uint2 lds64(uint32_t a) {
-  uint2 v;
-  asm("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
-  return v;
-}
 __device__ __forceinline__ uint4 lds128(uint32_t a) {
   uint4 v;
   asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
@@ -99,11 +78,6 @@ __device__ __forceinline__ void sts64(uint32_t a, uint32_t x, uint32_t y) {
 }
 __device__ __forceinline__ void sts128(uint32_t a, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
-}
-__device__ __forceinline__ void unpack_half4(const uint2& raw, float (&v)[4]) {
-  const __half2 a = *reinterpret_cast<const __half2*>(&raw.x), b = *reinterpret_cast<const __half2*>(&raw.y);
-  const float2 fa = __half22float2(a), fb = __half22float2(b);
-  v[0] = fa.x; v[1] = fa.y; v[2] = fb.x; v[3] = fb.y;
 }
 // A group of warps waits for an mbarrier phase: only lane 0 of the group's first warp polls, the others are parked on
 // a named hardware barrier (a parked warp takes no issue slots from the warps that are working).  The poller always
@@ -130,77 +104,6 @@ constexpr int kBarIdSoftmax = 1, kBarIdProducer = 3;   // named barriers 1 and 2
 
 __device__ __forceinline__ uint32_t sw128(uint32_t row, uint32_t chunk) {   // byte offset inside a block of 128-byte rows
   return (row >> 3) * 1024u + (row & 7u) * 128u + ((chunk ^ (row & 7u)) << 4);
-}
-
-// Code tables.  One entry per code byte: 4-bit codes -> 2 levels (4 bytes), 2-bit codes -> 4 levels (8 bytes).  An entry
-// is stored `stride / entry bytes` times in a row of `stride` bytes (64 when one table serves both sides and owns the
-// whole 16 KB, else 32), and lane l reads copy l mod copies, which spreads the lanes of a gather over the banks.
-template <int BITS>
-__device__ __forceinline__ void fill_code_table(uint8_t* lut, int stride, const float* __restrict__ cb, float inv_alpha, int tid,
-                                                int nthreads) {
-  const int words = stride / 4;                    // 32-bit words per entry row
-  for (int i = tid; i < 256 * words; i += nthreads) {
-    const int e = i / words, w = i - e * words;
-    uint32_t val;
-    if (BITS == 4) {
-      val = pack_half2(__ldg(cb + (e >> 4)) * inv_alpha, __ldg(cb + (e & 15)) * inv_alpha);
-    } else {
-      val = (w & 1) ? pack_half2(__ldg(cb + ((e >> 2) & 3)) * inv_alpha, __ldg(cb + (e & 3)) * inv_alpha)
-                    : pack_half2(__ldg(cb + ((e >> 6) & 3)) * inv_alpha, __ldg(cb + ((e >> 4) & 3)) * inv_alpha);
-    }
-    reinterpret_cast<uint32_t*>(lut)[i] = val;
-  }
-}
-
-// Expand 16 bytes of codes (one quad of a slot) of token row `nl` into fp16 chunks of a 128-row tile.
-// tile: shared address of column block 0 (block 1 is kColBlockBytes further).  quad: index of the 16 bytes in the row's codes.
-// lut_lane: table address + this lane's copy; stride: bytes per entry row.
-// scale_hi / scale_lo (SCALED only): the row's norm as two fp16 terms, each duplicated into a half2 -- hi = fp16(norm),
-// lo = fp16(norm - hi).  Every expanded pair becomes pair * hi + pair * lo.  A single fp16 factor would put the SAME relative
-// rounding error of the norm (up to 2^-11) on all 128 coordinates of that key, which the inverse Hadamard transform does not
-// average out; with the second term only per-element rounding is left.
-__device__ __forceinline__ uint32_t hscale2(uint32_t a, uint32_t hi, uint32_t lo) {
-  uint32_t d;
-  asm("{\n\t.reg .b32 t;\n\tmul.rn.f16x2 t, %1, %3;\n\tfma.rn.f16x2 %0, %1, %2, t;\n\t}" : "=r"(d) : "r"(a), "r"(hi), "r"(lo));
-  return d;
-}
-template <int BITS, bool SCALED>
-__device__ __forceinline__ void expand_quad(uint32_t tile, uint32_t lut_lane, uint32_t stride, const uint4& w, int nl, int quad, uint32_t scale_hi,
-                                            uint32_t scale_lo) {
-  const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
-  if (BITS == 4) {
-#pragma unroll
-    for (int wi = 0; wi < 4; ++wi) {
-      const uint32_t x = ws[wi];
-      uint32_t v[4];
-      v[0] = lds32(lut_lane + __byte_perm(x, 0u, 0x4440) * stride);      // one byte moved to the bottom, then shift-and-add
-      v[1] = lds32(lut_lane + __byte_perm(x, 0u, 0x4441) * stride);
-      v[2] = lds32(lut_lane + __byte_perm(x, 0u, 0x4442) * stride);
-      v[3] = lds32(lut_lane + __byte_perm(x, 0u, 0x4443) * stride);
-      if (SCALED) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) v[i] = hscale2(v[i], scale_hi, scale_lo);
-      }
-      const int c16 = quad * 4 + wi;                       // 16-byte chunk of the row: 8 coordinates
-      sts128(tile + (c16 >> 3) * kColBlockBytes + sw128(nl, c16 & 7), v[0], v[1], v[2], v[3]);
-    }
-  } else {
-#pragma unroll
-    for (int wi = 0; wi < 4; ++wi) {
-      const uint32_t x = ws[wi];
-#pragma unroll
-      for (int hb = 0; hb < 2; ++hb) {                     // two code bytes = 8 coordinates = one chunk
-        const uint32_t b0 = __byte_perm(x, 0u, 0x4440 + 2 * hb), b1 = __byte_perm(x, 0u, 0x4441 + 2 * hb);
-        uint2 lo = lds64(lut_lane + b0 * stride), hi = lds64(lut_lane + b1 * stride);
-        if (SCALED) {
-          lo.x = hscale2(lo.x, scale_hi, scale_lo); lo.y = hscale2(lo.y, scale_hi, scale_lo);
-          hi.x = hscale2(hi.x, scale_hi, scale_lo); hi.y = hscale2(hi.y, scale_hi, scale_lo);
-        }
-        const int c16 = quad * 8 + wi * 2 + hb;
-        sts128(tile + (c16 >> 3) * kColBlockBytes + sw128(nl, c16 & 7), lo.x, lo.y, hi.x, hi.y);
-      }
-    }
-  }
 }
 
 // ---- 4-bit codes: exact rows from a per-key table held in registers -----------------------------------------------------
@@ -257,15 +160,45 @@ __device__ __forceinline__ void expand_quad_exact(uint32_t tile, const LevelPlan
   }
 }
 
-// One thread's 64 scores of a tile (columns s_col .. s_col + 63 of its TMEM lane), scaled by the key norms kn[0..63]
+// 2-bit codes: a key has four values; their low bytes sit in one register, their high bytes in another.
+struct LevelPlanes2 { uint32_t lo, hi; };
+__device__ __forceinline__ LevelPlanes2 level_planes2(uint32_t cb_addr, float norm) {
+  const uint4 c = lds128(cb_addr);
+  float p0, p1, p2, p3;
+  f2_unpack(f2_mul(f2_pack(c.x, c.y), f2_pack(norm, norm)), p0, p1);
+  f2_unpack(f2_mul(f2_pack(c.z, c.w), f2_pack(norm, norm)), p2, p3);
+  const uint32_t h0 = pack_half2(p0, p1), h1 = pack_half2(p2, p3);
+  return LevelPlanes2{prmt(h0, h1, 0x6420u), prmt(h0, h1, 0x7531u)};
+}
+// 16 bytes of 2-bit codes (64 coordinates of token row `nl`, piece `quad` of its 32 code bytes) into the tile.  A code byte
+// holds coordinates 4j .. 4j + 3 from its top bit pair down (compression.py:375-386).  Two bytes are spread to eight
+// nibbles -- coordinates 3, 2, 1, 0 of the first byte, then of the second -- which select the value bytes four at a time.
+__device__ __forceinline__ void expand_quad_exact2(uint32_t tile, const LevelPlanes2& t, const uint4& w, int nl, int quad) {
+  const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+  for (int wi = 0; wi < 4; ++wi) {
+#pragma unroll
+    for (int hb = 0; hb < 2; ++hb) {               // two code bytes = 8 coordinates = one 16-byte chunk
+      uint32_t s = hb ? ws[wi] >> 16 : ws[wi] & 0xFFFFu;
+      s = (s | (s << 8)) & 0x00FF00FFu;
+      s = (s | (s << 4)) & 0x0F0F0F0Fu;
+      s = (s | (s << 2)) & 0x33333333u;
+      const uint32_t l0 = prmt(t.lo, t.lo, s), h0 = prmt(t.hi, t.hi, s);
+      const uint32_t l1 = prmt(t.lo, t.lo, s >> 16), h1 = prmt(t.hi, t.hi, s >> 16);
+      const int c16 = quad * 8 + wi * 2 + hb;
+      sts128(tile + (c16 >> 3) * kColBlockBytes + sw128(nl, c16 & 7), prmt(l0, h0, 0x6273u), prmt(l0, h0, 0x4051u),
+             prmt(l1, h1, 0x6273u), prmt(l1, h1, 0x4051u));
+    }
+  }
+}
+
+// One thread's 64 scores of a tile (columns s_col .. s_col + 63 of its TMEM lane), times the factor kf (softmax scale x log2 e)
 // (16-byte aligned).  MASK: keys beyond q_pos (the row's diagonal) count as minus infinity.  The next 16 columns are
 // requested before the current ones are worked on (tcgen05.wait::ld covers every load issued so far).
-// UNI: every key has the same factor (kn[0]): the rows in the tile already carry their norm.
-template <bool MASK, bool UNI>
-__device__ __forceinline__ float row_max(uint32_t s_col, const float* kn, int key0, int q_pos) {
+template <bool MASK>
+__device__ __forceinline__ float row_max(uint32_t s_col, float kf, int key0, int q_pos) {
   float mx[2] = {-INFINITY, -INFINITY};
-  const ulonglong2* kn2 = reinterpret_cast<const ulonglong2*>(kn);
-  const uint64_t ku = f2_pack(kn[0], kn[0]);
+  const uint64_t ku = f2_pack(kf, kf);
   uint32_t s[2][16];
   umma::tmem_ld16(s_col, s[0]);
 #pragma unroll
@@ -274,10 +207,9 @@ __device__ __forceinline__ float row_max(uint32_t s_col, const float* kn, int ke
     if (ch < 3) umma::tmem_ld16(s_col + 16 * (ch + 1), s[(ch + 1) & 1]);
 #pragma unroll
     for (int c = 0; c < 16; c += 4) {
-      const ulonglong2 k4 = UNI ? make_ulonglong2(ku, ku) : kn2[4 * ch + c / 4];
       float x[4];
-      f2_unpack(f2_mul(f2_pack(s[ch & 1][c], s[ch & 1][c + 1]), k4.x), x[0], x[1]);
-      f2_unpack(f2_mul(f2_pack(s[ch & 1][c + 2], s[ch & 1][c + 3]), k4.y), x[2], x[3]);
+      f2_unpack(f2_mul(f2_pack(s[ch & 1][c], s[ch & 1][c + 1]), ku), x[0], x[1]);
+      f2_unpack(f2_mul(f2_pack(s[ch & 1][c + 2], s[ch & 1][c + 3]), ku), x[2], x[3]);
       if (MASK) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) x[i] = key0 + 16 * ch + c + i > q_pos ? -INFINITY : x[i];
@@ -290,12 +222,11 @@ __device__ __forceinline__ float row_max(uint32_t s_col, const float* kn, int ke
 }
 // exp2(score * kn - m) for the same 64 scores; P as fp16 pairs into columns s_col .. s_col + 31 (the value norms are
 // already inside the V tile).  Returns the sum of the probabilities.
-template <bool MASK, bool UNI>
-__device__ __forceinline__ float row_probabilities(uint32_t s_col, const float* kn, float m, int key0, int q_pos) {
+template <bool MASK>
+__device__ __forceinline__ float row_probabilities(uint32_t s_col, float kf, float m, int key0, int q_pos) {
   uint64_t sum = f2_pack(0.f, 0.f);
   const uint64_t neg_m = f2_pack(-m, -m);
-  const ulonglong2* kn2 = reinterpret_cast<const ulonglong2*>(kn);
-  const uint64_t ku = f2_pack(kn[0], kn[0]);
+  const uint64_t ku = f2_pack(kf, kf);
   uint32_t s[2][16];
   umma::tmem_ld16(s_col, s[0]);
 #pragma unroll
@@ -305,9 +236,8 @@ __device__ __forceinline__ float row_probabilities(uint32_t s_col, const float* 
     if (ch < 3) umma::tmem_ld16(s_col + 16 * (ch + 1), s[(ch + 1) & 1]);
 #pragma unroll
     for (int c = 0; c < 16; c += 2) {
-      const ulonglong2 k4 = UNI ? make_ulonglong2(ku, ku) : kn2[4 * ch + c / 4];
       float a0, a1;
-      f2_unpack(f2_fma(f2_pack(s[ch & 1][c], s[ch & 1][c + 1]), (c & 2) ? k4.y : k4.x, neg_m), a0, a1);
+      f2_unpack(f2_fma(f2_pack(s[ch & 1][c], s[ch & 1][c + 1]), ku, neg_m), a0, a1);
       if (MASK) {
         a0 = key0 + 16 * ch + c > q_pos ? -INFINITY : a0;
         a1 = key0 + 16 * ch + c + 1 > q_pos ? -INFINITY : a1;
@@ -348,12 +278,11 @@ __device__ __forceinline__ void scale_p_chunks(uint32_t col, int chunks, float f
 // binary orders first (its earlier probabilities of this tile and their sum are multiplied by 2^-d).  `shift` returns
 // the total of those moves; the caller settles the two halves of a row on the larger shift before P is published.
 constexpr float kSafe = 14.0f;
-template <bool MASK, bool UNI>
-__device__ __forceinline__ float row_probabilities_stale(uint32_t s_col, const float* kn, float m, int key0, int q_pos, float& shift) {
+template <bool MASK>
+__device__ __forceinline__ float row_probabilities_stale(uint32_t s_col, float kf, float m, int key0, int q_pos, float& shift) {
   uint64_t sum = f2_pack(0.f, 0.f);
   uint64_t neg_ref = f2_pack(-m, -m);
-  const ulonglong2* kn2 = reinterpret_cast<const ulonglong2*>(kn);
-  const uint64_t ku = f2_pack(kn[0], kn[0]);
+  const uint64_t ku = f2_pack(kf, kf);
   shift = 0.f;
   uint32_t s[2][16];
   umma::tmem_ld16(s_col, s[0]);
@@ -365,8 +294,7 @@ __device__ __forceinline__ float row_probabilities_stale(uint32_t s_col, const f
     float a[16];
 #pragma unroll
     for (int c = 0; c < 16; c += 2) {
-      const ulonglong2 k4 = UNI ? make_ulonglong2(ku, ku) : kn2[4 * ch + c / 4];
-      f2_unpack(f2_fma(f2_pack(s[ch & 1][c], s[ch & 1][c + 1]), (c & 2) ? k4.y : k4.x, neg_ref), a[c], a[c + 1]);
+      f2_unpack(f2_fma(f2_pack(s[ch & 1][c], s[ch & 1][c + 1]), ku, neg_ref), a[c], a[c + 1]);
       if (MASK) {
         a[c] = key0 + 16 * ch + c > q_pos ? -INFINITY : a[c];
         a[c + 1] = key0 + 16 * ch + c + 1 > q_pos ? -INFINITY : a[c + 1];
@@ -526,24 +454,12 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
       q_raw[k] = __ldg(reinterpret_cast<const uint4*>(p.q + (static_cast<int64_t>(q_begin + pos) * p.H_q + kvh * g + hl) * kHeadDim) + chunk);
   }
 
-  __shared__ float s_err[64];
-  __shared__ int s_idx[64];
-  float alpha_k = 1.0f, alpha_v = 1.0f;
-  if constexpr (!kDense) find_table_scales<kLevK, kLevV>(p.cb_k, p.cb_v, s_err, s_idx, alpha_k, alpha_v);
-  // 4-bit sides expand exact rows from the fp32 levels (kept in s_levels); 2-bit sides go through a table of fp16
-  // levels.  One table owns the whole table area when only one side needs one, or when both sides' codebooks are the
-  // same (then their scales are the same too); else each side's table takes half.
-  constexpr bool kExactK = KB == 4, kExactV = VB == 4 && CDA_PF_EXACT_V;
-  constexpr bool kUni = (kExactK || kDense) && CDA_PF_UNIFORM_KN;   // every key's score factor is the softmax scale
+  // The fp32 code levels of both sides: the producers turn them into each key's exact fp16 values.
   __shared__ __align__(16) float s_levels[2][16];
-  bool same_cb = KB == VB;
-  if (KB == VB && !kDense) {
-#pragma unroll
-    for (int i = 0; i < kLevK; ++i) same_cb = same_cb && __ldg(p.cb_k + i) == __ldg(p.cb_v + i);
+  if constexpr (!kDense) {
+    if (tid < kLevK) s_levels[0][tid] = __ldg(p.cb_k + tid);
+    else if (tid >= 32 && tid < 32 + kLevV) s_levels[1][tid - 32] = __ldg(p.cb_v + tid - 32);
   }
-  const bool one_table = kExactK || kExactV || same_cb;
-  const uint32_t lut_stride = one_table ? 64u : 32u;
-  const uint32_t lutv_off = one_table ? 0u : static_cast<uint32_t>(kLutBytes / 2);
 
   // ---- set-up: barriers, TMEM, tables, rotated queries -----------------------------------------------------------------
   if (tid == 0) {
@@ -552,7 +468,6 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
       mbar_init(bar(kBarVFull + i), kProducerWarps); mbar_init(bar(kBarVEmpty + i), 1);
       mbar_init(bar(kBarSFull + i), 1); mbar_init(bar(kBarPFull + i), kSoftmaxWarpsPerBlock); mbar_init(bar(kBarPvDone + i), 1);
     }
-    for (int i = 0; i < 4; ++i) mbar_init(bar(kBarNorms + i), kProducerWarps);
     abort_flag->abort = 0;
     abort_flag->limit_ns = p.wait_limit_ns;
     mbar_init_fence();
@@ -560,12 +475,6 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
   if (warp == kMmaWarp) {
     tmem_alloc(base + kOffBar + kOffTmemAddr, kTmemCols);
     tmem_relinquish();
-  }
-  if constexpr (!kDense) {
-    if (kExactK) { if (tid < 16) s_levels[0][tid] = __ldg(p.cb_k + tid); }
-    else fill_code_table<KB>(sm + kOffLut, lut_stride, p.cb_k, 1.0f / alpha_k, tid, kThreads);
-    if (kExactV) { if (tid >= 32 && tid < 48) s_levels[1][tid - 32] = __ldg(p.cb_v + tid - 32); }
-    else if (kExactK || !same_cb) fill_code_table<VB>(sm + kOffLut + lutv_off, lut_stride, p.cb_v, 1.0f / alpha_v, tid, kThreads);
   }
   // Q: park the raw rows; then warps 0..15 rotate 16 rows each and store them as the A operand of Q K^T (K-major,
   // 128-byte swizzle)
@@ -600,14 +509,12 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
     float* xch = reinterpret_cast<float*>(sm + kOffXch) + blk * 4 * kRows;   // [2 parities][2 halves][128 rows]
     const int bar_id = kBarIdSoftmax + blk, group_threads = kSoftmaxWarpsPerBlock * 32;
     float m_used = -INFINITY, l_run = 0.f;
+    const float kf = p.scale_log2;                         // the tiles hold whole rows (norm included): one factor for every key
     bool alive = true;
     GroupWaiter gw{reinterpret_cast<volatile int*>(sm + kOffBar + kOffOutcome + 8 * blk), abort_flag, bar_id, group_threads, 0, w == 0 && lane == 0};
 #pragma unroll 1
     for (int j = 0; j < n_tiles; ++j) {
-      const float* kn = reinterpret_cast<const float*>(sm + kOffKn) + (j & 3) * kKeys + 64 * half;
-      // the norms come straight from the producers (slot j & 3 is rewritten only for tile j + 4), the scores from the MMA;
       // Q K^T of tile j was issued behind P V of tile j - 1 of this block, so its O is at rest as well
-      if (gw.leader && !umma::mbar_wait(bar(kBarNorms + (j & 3)), (j >> 2) & 1, abort_flag)) {}   // (a failure shows in the next outcome)
       alive = gw.wait(bar(kBarSFull + blk), j & 1);
       if (!alive) break;
       tc_fence_after_sync();
@@ -617,7 +524,7 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
       if (__any_sync(0xffffffffu, m_used == -INFINITY)) {
       // a row without a reference yet (tile 0: key 0 is never masked, so every row has one afterwards): two passes
       // pass 1: maximum of this thread's 64 scaled scores (diagonal tiles take the masking variant)
-      const float mx_own = diag ? row_max<true, kUni>(s_col, kn, key0, q_pos) : row_max<false, kUni>(s_col, kn, key0, q_pos);
+      const float mx_own = diag ? row_max<true>(s_col, kf, key0, q_pos) : row_max<false>(s_col, kf, key0, q_pos);
       float mx = mx_own;
       // the row maximum needs the other half's keys
       xch[((j & 1) * 2 + half) * kRows + t] = mx;
@@ -634,12 +541,12 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
       if (rescale) rescale_o(o_col, factor);
       // pass 2: probabilities.  The scores are read again from TMEM, 16 columns at a time; the fp16 P of a chunk
       // (keys 2c, 2c+1 in column c) goes straight over score columns this thread has already consumed.
-      l_run += diag ? row_probabilities<true, kUni>(s_col, kn, m_used, key0, q_pos) : row_probabilities<false, kUni>(s_col, kn, m_used, key0, q_pos);
+      l_run += diag ? row_probabilities<true>(s_col, kf, m_used, key0, q_pos) : row_probabilities<false>(s_col, kf, m_used, key0, q_pos);
       } else {
       // one pass against the reference the row already has; the halves of a row then settle on a common reference
       float shift;
-      float sum = diag ? row_probabilities_stale<true, kUni>(s_col, kn, m_used, key0, q_pos, shift)
-                       : row_probabilities_stale<false, kUni>(s_col, kn, m_used, key0, q_pos, shift);
+      float sum = diag ? row_probabilities_stale<true>(s_col, kf, m_used, key0, q_pos, shift)
+                       : row_probabilities_stale<false>(s_col, kf, m_used, key0, q_pos, shift);
       xch[((j & 1) * 2 + half) * kRows + t] = shift;
       named_barrier(bar_id, group_threads);
       const float common = fmaxf(shift, xch[((j & 1) * 2 + (half ^ 1)) * kRows + t]);
@@ -669,7 +576,7 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
     }
     if (alive) {
       tc_fence_after_sync();
-      const float inv = alpha_v / fmaxf(l_run, 1e-30f);
+      const float inv = 1.0f / fmaxf(l_run, 1e-30f);
       const uint32_t row = static_cast<uint32_t>(blk * kRows + t);
 #pragma unroll 1
       for (int ch = 0; ch < 2; ++ch) {
@@ -710,10 +617,6 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
     const int64_t row_halfs = static_cast<int64_t>(p.H_kv) * kHeadDim;
     const __half* k_src = p.k_dense + (static_cast<int64_t>(p.cu_k[b]) * p.H_kv + kvh) * kHeadDim;
     const __half* v_src = p.v_dense + (static_cast<int64_t>(p.cu_k[b]) * p.H_kv + kvh) * kHeadDim;
-    {   // every key's norm factor is the softmax scale
-      float* kn = reinterpret_cast<float*>(sm + kOffKn);
-      for (int i = pt; i < 4 * kKeys; i += kProducerThreads) kn[i] = p.scale_log2;
-    }
     auto copy_tile = [&](const __half* src, uint32_t tile, int j) {
 #pragma unroll
       for (int it = 0; it < 8; ++it) {
@@ -732,10 +635,7 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
       cp_async_wait<1>();
       fence_async_smem();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(bar(kBarNorms + (i & 3)));
-        if (!(p.withhold_first_k && i == 0)) mbar_arrive(bar(kBarKFull + (i & 1)));
-      }
+      if (lane == 0 && !(p.withhold_first_k && i == 0)) mbar_arrive(bar(kBarKFull + (i & 1)));
       cp_async_wait<0>();
       fence_async_smem();
       __syncwarp();
@@ -743,122 +643,60 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
     }
     cp_async_wait<0>();
    } else {
-    const uint32_t k_copies = lut_stride / (KB == 4 ? 4u : 8u), v_copies = lut_stride / (VB == 4 ? 4u : 8u);
-    const uint32_t lutk_lane = base + kOffLut + (lane & (k_copies - 1)) * (KB == 4 ? 4u : 8u);
-    const uint32_t lutv_lane = base + kOffLut + lutv_off + (lane & (v_copies - 1)) * (VB == 4 ? 4u : 8u);
+    const int nl = pt & (kKeys - 1);                         // this thread's key (row of the tile)
     const int32_t* bt_row = p.block_table + static_cast<int64_t>(b) * p.bt_stride;
     const int64_t row_stride = static_cast<int64_t>(p.H_kv) * kSlotBytes;
-    const float kscale = p.scale_log2 * alpha_k;
     bool bad_block = false;
     GroupWaiter gw{reinterpret_cast<volatile int*>(sm + kOffBar + kOffOutcome + 16), abort_flag, kBarIdProducer, kProducerThreads, 0, pt == 0};
 
     // Block ids are read one fetch ahead of the slots they address, slot words one tile ahead of their expansion:
     // neither global-memory latency sits on the tile-to-tile chain.
-    auto block_id = [&](int nl, int tile) -> int {
+    auto block_id = [&](int tile) -> int {
       const int n = min(tile * kKeys + nl, seq_len - 1);     // keys past the end are masked later; read a valid slot
       const int bi = p.bs_shift >= 0 ? n >> p.bs_shift : n / p.block_size;
       return __ldg(bt_row + bi);
     };
-    auto slot_ptr = [&](int blk, int nl, int tile) -> const uint8_t* {
+    auto slot_ptr = [&](int blk, int tile) -> const uint8_t* {
       const int n = min(tile * kKeys + nl, seq_len - 1);
       const int in_block = p.bs_shift >= 0 ? n & (p.block_size - 1) : n % p.block_size;
       if (static_cast<unsigned>(blk) >= static_cast<unsigned>(p.num_blocks)) { bad_block = true; blk = 0; }
       return p.cache + (static_cast<int64_t>(blk) * p.block_size + in_block) * row_stride + kvh * kSlotBytes;
     };
-    struct KRegs { uint4 w[kItK]; float n[kItK]; };
-    struct VRegs { uint4 w[kItV]; float n[kItV]; };
-    // Which 16-byte piece of which key a producer thread expands in turn `it`.  2-bit side (one turn): two threads per key,
-    // one piece each.  4-bit side (two turns): thread t takes key t mod 128 and the pieces 2 (t / 128) + it -- both turns on
-    // the same key, whose table of exact values is built once, and a warp stores to 32 different rows of the swizzled tile.
-    auto piece_of = [&](bool exact, int bits, int it, int& nl, int& quad) {
-      if (exact) { nl = pt & (kKeys - 1); quad = 2 * (pt >> 7) + it; }
-      else { const int x = pt + kProducerThreads * it; nl = x / bits; quad = x % bits; }
-    };
-    int kblk[kItK], vblk[kItV];                               // block ids of the next tile to fetch
-#pragma unroll
-    for (int it = 0; it < kItK; ++it) { int nl, quad; piece_of(kExactK, KB, it, nl, quad); kblk[it] = block_id(nl, 0); }
-#pragma unroll
-    for (int it = 0; it < kItV; ++it) { int nl, quad; piece_of(kExactV, VB, it, nl, quad); vblk[it] = block_id(nl, 0); }
+    // Producer thread t works on key t mod 128 of every tile: it reads that key's slot (the 16-byte code pieces
+    // (t / 128) kIt + it of either side, and its norm), builds the key's exact values once per side and expands its
+    // pieces; the lanes of a warp store to 32 different rows of the swizzled tile (no bank conflicts).
+    struct KRegs { uint4 w[kItK]; float n; };
+    struct VRegs { uint4 w[kItV]; float n; };
+    int blk_k = block_id(0), blk_v = blk_k;                   // block id of this key's row in the next tile to fetch
     auto load_k = [&](int j, KRegs& r) {
       if (j >= n_tiles) return;
+      const uint8_t* src = slot_ptr(blk_k, j);
 #pragma unroll
-      for (int it = 0; it < kItK; ++it) {
-        int nl, quad;
-        piece_of(kExactK, KB, it, nl, quad);
-        const uint8_t* src = slot_ptr(kblk[it], nl, j);
-        r.w[it] = __ldg(reinterpret_cast<const uint4*>(src + 16 * quad));
-        if (kExactK ? it == 0 : quad == 0) r.n[it] = __ldg(reinterpret_cast<const float*>(src + 16 * KB + 16 * VB));
-        kblk[it] = block_id(nl, j + 1);
-      }
+      for (int it = 0; it < kItK; ++it) r.w[it] = __ldg(reinterpret_cast<const uint4*>(src + 16 * ((pt >> 7) * kItK + it)));
+      r.n = __ldg(reinterpret_cast<const float*>(src + 16 * KB + 16 * VB));
+      blk_k = block_id(j + 1);
     };
     auto load_v = [&](int j, VRegs& r) {
       if (j >= n_tiles) return;
+      const uint8_t* src = slot_ptr(blk_v, j);
 #pragma unroll
-      for (int it = 0; it < kItV; ++it) {
-        int nl, quad;
-        piece_of(kExactV, VB, it, nl, quad);
-        const uint8_t* src = slot_ptr(vblk[it], nl, j);
-        r.w[it] = __ldg(reinterpret_cast<const uint4*>(src + 16 * KB + 16 * quad));
-        if (!kExactV || it == 0) r.n[it] = __ldg(reinterpret_cast<const float*>(src + 16 * KB + 16 * VB + 4));
-        vblk[it] = block_id(nl, j + 1);
-      }
+      for (int it = 0; it < kItV; ++it) r.w[it] = __ldg(reinterpret_cast<const uint4*>(src + 16 * KB + 16 * ((pt >> 7) * kItV + it)));
+      r.n = __ldg(reinterpret_cast<const float*>(src + 16 * KB + 16 * VB + 4));
+      blk_v = block_id(j + 1);
     };
-    // The table stride (bytes between the rows of two code bytes) is 64 with one shared table and 32 with two; the tile
-    // loop is instantiated for either, so that every gather address is "byte << 6 (or 5), plus base" with constant shifts.
-    auto produce = [&](auto stride_tag) {
-    constexpr uint32_t kStride = decltype(stride_tag)::value;
-    auto expand_k = [&](int j, const KRegs& r) {
-      const uint32_t tile = base + kOffK + (j & 1) * kTileBytes;
-      float* kn = reinterpret_cast<float*>(sm + kOffKn) + (j & 3) * kKeys;
-      if constexpr (kExactK) {   // the key norm is inside the exact rows: every key's score factor is the softmax scale
-        const LevelPlanes t = level_planes(smem_addr(s_levels[0]), r.n[0]);
+    auto expand_side = [&](auto bits_tag, uint32_t tile, uint32_t levels, const uint4* w, float norm) {
+      constexpr int kBits = decltype(bits_tag)::value, kIt = kBits / 2;
+      if constexpr (kBits == 4) {
+        const LevelPlanes t = level_planes(levels, norm);
 #pragma unroll
-        for (int it = 0; it < kItK; ++it) {
-          int nl, quad;
-          piece_of(kExactK, KB, it, nl, quad);
-          if (quad == 0) kn[nl] = p.scale_log2;
-          expand_quad_exact(tile, t, r.w[it], nl, quad);
-        }
+        for (int it = 0; it < kIt; ++it) expand_quad_exact(tile, t, w[it], nl, (pt >> 7) * kIt + it);
       } else {
+        const LevelPlanes2 t = level_planes2(levels, norm);
 #pragma unroll
-        for (int it = 0; it < kItK; ++it) {
-          int nl, quad;
-          piece_of(kExactK, KB, it, nl, quad);
-          if (quad == 0) kn[nl] = r.n[it] * kscale;
-          expand_quad<KB, false>(tile, lutk_lane, kStride, r.w[it], nl, quad, 0u, 0u);
-        }
+        for (int it = 0; it < kIt; ++it) expand_quad_exact2(tile, t, w[it], nl, (pt >> 7) * kIt + it);
       }
       fence_async_smem();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(bar(kBarNorms + (j & 3)));
-        if (!(p.withhold_first_k && j == 0)) mbar_arrive(bar(kBarKFull + (j & 1)));
-      }
-    };
-    auto expand_v = [&](int j, const VRegs& r) {
-      if constexpr (kExactV) {
-        const LevelPlanes t = level_planes(smem_addr(s_levels[1]), r.n[0]);
-#pragma unroll
-        for (int it = 0; it < kItV; ++it) {
-          int nl, quad;
-          piece_of(kExactV, VB, it, nl, quad);
-          expand_quad_exact(base + kOffV + (j & 1) * kTileBytes, t, r.w[it], nl, quad);
-        }
-      } else {
-#pragma unroll
-        for (int it = 0; it < kItV; ++it) {
-          int nl, quad;
-          piece_of(kExactV, VB, it, nl, quad);
-          // the value norm goes into the tile (fp16 products, norm as two fp16 terms), so the probabilities need no per-key factor
-          const float n_hi = round_to_half(r.n[it]);
-          const float n_lo = r.n[it] - n_hi;
-          expand_quad<VB, true>(base + kOffV + (j & 1) * kTileBytes, lutv_lane, kStride, r.w[it], nl, quad, pack_half2(n_hi, n_hi),
-                                pack_half2(n_lo, n_lo));
-        }
-      }
-      fence_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(kBarVFull + (j & 1)));
     };
     // Tile i is expanded from registers that were filled while tile i-1 was being expanded; its K stage is free once
     // Q K^T of tile i-2 is done for both blocks, its V stage once P V of tile i-2 is done for both blocks.
@@ -869,15 +707,14 @@ __global__ void __launch_bounds__(pfu::kThreads, 1) prefill_umma_kernel(const Pr
 #pragma unroll 1
     for (int i = 0; i < n_tiles; ++i) {
       if (i >= 2 && !gw.wait(bar(kBarKEmpty + (i & 1)), ((i - 2) >> 1) & 1)) break;
-      expand_k(i, kr);
+      expand_side(std::integral_constant<int, KB>{}, base + kOffK + (i & 1) * kTileBytes, smem_addr(s_levels[0]), kr.w, kr.n);
+      if (lane == 0 && !(p.withhold_first_k && i == 0)) mbar_arrive(bar(kBarKFull + (i & 1)));
       load_k(i + 1, kr);
       if (i >= 2 && !gw.wait(bar(kBarVEmpty + (i & 1)), ((i - 2) >> 1) & 1)) break;
-      expand_v(i, vr);
+      expand_side(std::integral_constant<int, VB>{}, base + kOffV + (i & 1) * kTileBytes, smem_addr(s_levels[1]), vr.w, vr.n);
+      if (lane == 0) mbar_arrive(bar(kBarVFull + (i & 1)));
       load_v(i + 1, vr);
     }
-    };
-    if (one_table) produce(std::integral_constant<uint32_t, 64u>{});
-    else produce(std::integral_constant<uint32_t, 32u>{});
     if (bad_block) atomicOr(&g_prefill_status, 1);
    }
   } else {
