@@ -1,9 +1,12 @@
 """GPU parity of the prefill path (dense loader, fused causal varlen attention) against the CPU oracle.
 
 Tolerance: query rows that see at least 4096 keys are held to |got - want| <= 1e-3 + 2e-3 |want| element by element
-(``tests/_cases.strict``), with the share of elements outside it capped at 5e-5 (measured 1.3e-5) and the worst excess at
-2 x; rows with fewer visible keys -- the first tokens of a prompt, where the softmax is peaked -- take the row-max form of
-the same bound (``tests/_cases.close``).  Cosine >= 0.9999 everywhere."""
+(``tests/_cases.strict``), with the share of elements outside it capped at 1e-5 (measured: 0 of 1 077 760 on a whole
+6200-token prompt, worst 0.86 x the bound) and the worst excess at 2 x; rows with fewer visible keys -- the first tokens of
+a prompt, where the softmax is peaked -- take the row-max form of the same bound (``tests/_cases.close``; measured at most
+0.41 x) with at most 1e-4 of their elements outside the element-wise bound (measured at most 5.4e-6).  Cosine >= 0.9999
+everywhere.  The K and V tiles of the kernel hold the reference's own decoded rows, so what is left is the fp16 rounding of
+the probabilities."""
 import pytest
 import torch
 
@@ -24,16 +27,16 @@ def visible_keys(q_lens, seq_lens):
 
 
 STRICT_FROM = 4096
-MAX_BAD_FRAC = 5e-3            # rows with few visible keys: cap on the share of elements outside the element-wise bound
-MAX_LONG_BAD_FRAC = 5e-5       # rows with >= 4096 keys: measured 1.3e-5 (14 of 1 077 760 elements), worst 1.51 x the bound
+MAX_BAD_FRAC = 1e-4            # rows with few visible keys: cap on the share of elements outside the element-wise bound
+MAX_LONG_BAD_FRAC = 1e-5       # rows with >= 4096 keys: measured 0 of 1 077 760 elements, worst 0.86 x the bound
 MAX_LONG_WORST = 2.0
 
 
 def assert_close(got, want, what="", keys=None):
     """``keys``: number of keys each query row sees.  Rows with >= STRICT_FROM keys are checked element-wise against
-    1e-3 + 2e-3 |want|: the share of elements outside it and the worst excess are capped at measured figures (a few per
-    million exceed it by construction of the reference's fp16 rounding before the inverse rotation -- see the module
-    docstring of ``tests/_cases.py``); the other rows take the row-max form."""
+    1e-3 + 2e-3 |want|: the share of elements outside it and the worst excess are capped (a few per ten million exceed it
+    by construction of the reference's fp16 rounding before the inverse rotation -- see the module docstring of
+    ``tests/_cases.py``); the other rows take the row-max form."""
     assert not bool(got.isnan().any()), f"{what}: NaN in output"
     long_rows = keys >= STRICT_FROM if keys is not None else torch.zeros(got.shape[0], dtype=torch.bool)
     if bool(long_rows.any()):
@@ -42,7 +45,8 @@ def assert_close(got, want, what="", keys=None):
         assert bad <= max(1, int(MAX_LONG_BAD_FRAC * n)) and worst <= MAX_LONG_WORST and cos >= 0.9999, \
             f"{what}: {bad} of {n} elements outside 1e-3 + 2e-3|want| (worst x{worst:.2f}), cosine {cos:.6f}"
     if bool((~long_rows).any()):
-        ok, ratio, cos = Cs.close(got[~long_rows], want[~long_rows], max_bad_frac=MAX_BAD_FRAC, what=what)
+        short = got[~long_rows]
+        ok, ratio, cos = Cs.close(short, want[~long_rows], max_bad_frac=max(MAX_BAD_FRAC, 3.0 / short.numel()), what=what)
         assert ok and cos >= 0.9999, f"{what}: worst error/tolerance {ratio:.3f}, cosine {cos:.6f}"
 
 
@@ -281,14 +285,11 @@ def _random_prefill_cases(seed, count):
 
 
 def test_random_shapes_match_the_model_of_the_kernels_roundings():
-    """The kernel against ``tests/_kernel_model.py`` -- the reference algorithm with the kernel's documented roundings
-    (fp16 code tables with the norm outside the K tile, two-term fp16 norm inside the V tile, fp16 probabilities against
-    the first tile's maximum) -- on random shapes.  The two agree up to single fp16 rounding flips of the rotated row:
-    no element may leave the path's stated tolerance (measured over 11 shapes and 75 M elements: one element, 1.33 x),
-    whereas the distance to the oracle itself is several times larger on prompts of a few hundred tokens and is capped
-    below at twice what these shapes show (up to 4.4e-4 of the elements outside 1e-3 + 2e-3 |want|, worst 5.2 x: the
-    fp16 rounding of the 16 or 4 code levels is the same for every key that uses a level, and the reference rounds
-    level * norm to fp16 where the kernel keeps the norm in fp32 -- neither averages out on rows that see few keys)."""
+    """Random shapes against the oracle and against ``tests/_kernel_model.py`` -- the reference algorithm with the one
+    rounding the kernel adds (fp16 probabilities against the first tile's maximum).  The kernel and the model agree up to
+    single fp16 rounding flips of the rotated row: no element may leave the path's stated tolerance (measured over 11
+    shapes and 75 M elements: none, worst 0.58 x).  Against the oracle a few elements per ten million do (measured on
+    these twelve shapes: 50 of 42.5 M, worst 1.5 x); the cap is 2 + 2e-5 of a shape's elements, none beyond 3 x."""
     from tests import _kernel_model as KM
     total = bad_model = bad_oracle = 0
     for d in _random_prefill_cases(20260, 12):
@@ -303,7 +304,7 @@ def test_random_shapes_match_the_model_of_the_kernels_roundings():
         bm, wm, n = Cs.violations(got, model)
         bo, wo, _ = Cs.violations(got, want)
         assert bm <= n // 2_000_000 and wm <= 1.5, f"{d}: {bm} of {n} elements off the model (worst x{wm:.2f})"
-        assert bo <= 1e-3 * n and wo <= 8.0 and Cs.cosine(got, want) >= 0.9999, \
+        assert bo <= 2 + 2e-5 * n and wo <= 3.0 and Cs.cosine(got, want) >= 0.9999, \
             f"{d}: {bo} of {n} elements outside 1e-3 + 2e-3|want| of the oracle (worst x{wo:.2f})"
         total += n; bad_model += bm; bad_oracle += bo
     Cs.STATS.append({"what": "random prefill shapes", "form": "strict", "elements": total, "violations": bad_oracle,
