@@ -90,6 +90,29 @@ def test_full_prompt_prefill(kb, vb, group, H_kv):
     assert_close(out.cpu(), want, f"k{kb}v{vb} g{group}", visible_keys(lens, lens))
 
 
+@pytest.mark.parametrize("kb,vb,group,H_kv", [(4, 4, 4, 3), (4, 2, 8, 2), (2, 2, 4, 2), (2, 2, 1, 5)])
+def test_fused_equals_dense_route_every_code_width(kb, vb, group, H_kv):
+    """The fused kernel expands the codes into the same fp16 rows the dense loader writes (fp16(level x norm), one
+    rounding) and then runs the same tile loop as the dense-source instance: identical bits, for 4-bit and 2-bit sides,
+    whole prompts and chunks, lengths around the tile edges."""
+    from sub0_b200 import ops
+    from sub0_b200.kernels_cuda import fa2_cda
+    lens, q_lens = [1, 127, 128, 129, 700, 333, 2049], [1, 127, 100, 129, 700, 33, 1500]
+    case = Cs.paged_case(lens, H_kv=H_kv, group=group, k_bits=kb, v_bits=vb, seed=31 * kb + vb + group)
+    Q, cu = prefill_inputs(case, q_lens, 12)
+    fused = run_prefill(case, Q, cu, q_lens, k4v2=(kb, vb) == (4, 2))
+    d = to_dev(case)
+    max_len = -(-max(lens) // 16) * 16
+    k_rot, v_rot = fa2_cda.paged_cache_to_dense_rotated(d["cache"], d["block_table"], d["seq_lens"], cb_K=d["cb_K"], cb_V=d["cb_V"],
+                                                        block_size=16, max_seq_len=max_len, k4v2=(kb, vb) == (4, 2))
+    dense = torch.full_like(Q, float("nan"), device=DEV)
+    cu_k = torch.arange(len(lens) + 1, dtype=torch.int32, device=DEV) * max_len
+    ops.varlen_fwd_hadamard(Q.to(DEV), k_rot, v_rot, dense, cu.to(DEV), cu_k, d["seq_lens"], max(q_lens), max_len, 1.0 / 128 ** 0.5)
+    torch.cuda.synchronize()
+    assert not bool(fused.isnan().any())
+    assert torch.equal(fused, dense.cpu()), f"k{kb}v{vb}: {int((fused != dense.cpu()).sum())} elements differ"
+
+
 def test_long_prompt_prefill_strict_rows():
     """A longer prompt (2500 keys, 40 K/V tiles per row block) crossing many tile and page boundaries."""
     from sub0_b200.kernels_cuda.fa2_cda import fa2_cda_prefill_varlen_v1
